@@ -1,0 +1,57 @@
+"""Trace replay against the plain implementation, in float32 and bfloat16: whole
+requests, a decoded tail, portions of changing size, and a mix of up to four live
+requests with so few pages that they are used again."""
+import pytest
+import torch
+
+import replay_util as R
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"a": [5, 17, 33, 70, 128, 101], "b": [1 + 8, 40, 70, 150, 256, 93], "c": [37, 129, 300, 64, 211, 450]}
+
+
+def _requests(name, config):
+    return {f"r{i}": R.random_tokens(config["vocab_size"], n, seed=1000 + 17 * i + ord(name))
+            for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_replay_all_cuts(name, dtype, model_dirs, plain_models, tmp_path):
+    path, config, page = model_dirs[name]
+    requests = _requests(name, config)
+    steps, alias = [], {}
+
+    def add(kind, make):
+        renamed = {f"{kind}-{rid}": tokens for rid, tokens in requests.items()}
+        for rid in requests:
+            alias[f"{kind}-{rid}"] = rid
+        steps.extend(make(renamed))
+
+    add("whole", R.whole_steps)
+    add("tail", R.tail_steps)
+    add("portion", R.portion_steps)
+    add("mixed", lambda reqs: R.mixed_steps(reqs, seed=3))
+    steps = R.number(steps)
+    # the pool is what the mixed part needs, so the other parts reuse its pages too
+    max_tokens = R.max_live_tokens(steps)
+    replayer = R.run_in_process(path, dtype, steps, max_tokens, page, tmp_path)
+    rows = R.collect(steps, tmp_path, config["vocab_size"])
+    assert len(rows) == 4 * sum(len(t) for t in requests.values())
+    worst = R.compare_with_plain(rows, requests, plain_models[name], dtype, alias=lambda rid: alias[rid])
+    pool = replayer.runner.cache.groups[0].pool
+    assert pool.available() == pool.num_pages, "pages were lost"
+    print(f"{name} {dtype}: worst error {worst:.3e} of the largest logit")
+
+
+def test_trace_run_binary(model_dirs, plain_models, tmp_path):
+    """The program itself: line protocol, files, exit code; pages used again."""
+    path, config, page = model_dirs["b"]
+    requests = {f"q{i}": R.random_tokens(config["vocab_size"], n, seed=50 + i) for i, n in enumerate([70, 40, 33, 90, 64])}
+    steps = R.number(R.mixed_steps(requests, seed=11))
+    max_tokens = R.max_live_tokens(steps)
+    assert max_tokens < sum(R.roundup64(len(t)) for t in requests.values())
+    R.run_binary(path, "float32", steps, max_tokens, tmp_path, page_size=page)
+    rows = R.collect(steps, tmp_path, config["vocab_size"])
+    R.compare_with_plain(rows, requests, plain_models["b"], "float32")

@@ -1,0 +1,120 @@
+// After the fused QKV projection, in one pass over each token's heads:
+//   q heads: per-head RMSNorm (optional) -> rotation (optional) -> q_out
+//   k heads: per-head RMSNorm (optional) -> rotation (optional) -> key cache slot
+//   v heads: copied to the value cache slot
+// Formulas: kernels/triton_kernels/qk_norm.py:40-95 (norm over head_dim with one
+// weight shared by all heads, before the rotation), rope.py:78-101 (half-split pairs),
+// store_kv_cache.py:75-120 (row t goes to slot_mapping[t]; slot -1 writes nothing).
+// The reference rounds to bf16 between the norm and the rotation; this kernel keeps
+// float32 there and rounds once at the store.
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_PAIRS_PER_LANE = 8;  // head_dim <= 512
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache,
+                T* __restrict__ v_cache, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
+                int norm_w_is_f32, float eps, const float* __restrict__ cos_table,
+                const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
+                const int* __restrict__ slot_mapping, int64_t num_slots, int nq, int nkv, int d,
+                unsigned* status) {
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int half = d >> 1;
+  const int heads = nq + 2 * nkv;
+  const int64_t in_base = (int64_t)t * heads * d;
+
+  int pos = positions ? positions[t] : 0;
+  if (cos_table && (pos < 0 || pos >= max_positions)) {
+    if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
+    pos = 0;
+  }
+  int64_t slot = -1;
+  if (nkv > 0 && slot_mapping) {
+    slot = slot_mapping[t];
+    if (slot >= num_slots || slot < -1) {
+      if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+      slot = -1;
+    }
+  }
+
+  for (int h = warp; h < heads; h += nwarps) {
+    const T* src = qkv + in_base + (int64_t)h * d;
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((int64_t)t * nq + h) * d;
+    } else {
+      if (slot < 0) continue;
+      const int g = is_k ? h - nq : h - nq - nkv;
+      dst = (is_k ? k_cache : v_cache) + (slot * nkv + g) * d;
+    }
+    if (!is_q && !is_k) {  // value head: plain copy
+      for (int i = lane; i < d; i += 32) dst[i] = src[i];
+      continue;
+    }
+    float x1[MAX_PAIRS_PER_LANE], x2[MAX_PAIRS_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
+      const int i = lane + 32 * j;
+      if (i < half) {
+        x1[j] = to_f32(src[i]);
+        x2[j] = to_f32(src[i + half]);
+        ss += x1[j] * x1[j] + x2[j] * x2[j];
+      } else {
+        x1[j] = x2[j] = 0.f;
+      }
+    }
+    const void* w = is_q ? q_norm_w : k_norm_w;
+    float rrms = 1.f;
+    if (w) rrms = rsqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+    for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
+      const int i = lane + 32 * j;
+      if (i >= half) continue;
+      float a = x1[j], b = x2[j];
+      if (w) {
+        a = a * rrms * load_flex(w, norm_w_is_f32, i);
+        b = b * rrms * load_flex(w, norm_w_is_f32, i + half);
+      }
+      if (cos_table) {
+        const float c = cos_table[(int64_t)pos * half + i], s = sin_table[(int64_t)pos * half + i];
+        const float ra = a * c - b * s, rb = b * c + a * s;
+        a = ra;
+        b = rb;
+      }
+      dst[i] = from_f32<T>(a);
+      dst[i + half] = from_f32<T>(b);
+    }
+  }
+}
+}  // namespace
+
+// qkv: [tokens, (nq + 2*nkv) * d]; q_out: [tokens, nq * d]; caches: [num_slots, nkv, d].
+// nkv == 0: the input holds query heads only and nothing is stored.
+// q_norm_w / k_norm_w null: no head norm. cos/sin null: no rotation; else float32
+// tables [max_positions, d/2].
+VOSTI_API int vosti_qkv_post(const void* qkv, void* q_out, void* k_cache, void* v_cache, const void* q_norm_w,
+                             const void* k_norm_w, int norm_w_is_f32, float eps, const float* cos_table,
+                             const float* sin_table, int max_positions, const int* positions,
+                             const int* slot_mapping, int64_t num_slots, int tokens, int nq, int nkv, int d,
+                             int is_f32, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && d > 0, "qkv_post: bad sizes");
+  VOSTI_REQUIRE(d % 2 == 0 && d / 2 <= 32 * MAX_PAIRS_PER_LANE, "qkv_post: head_dim %d must be even and <= %d", d,
+                64 * MAX_PAIRS_PER_LANE);
+  VOSTI_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "qkv_post: cos and sin go together");
+  VOSTI_REQUIRE(cos_table == nullptr || positions != nullptr, "qkv_post: rotation needs positions");
+  if (tokens == 0) return VOSTI_OK;
+  if (is_f32)
+    qkv_post_kernel<float><<<tokens, 128, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_cache,
+        (float*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
+        slot_mapping, num_slots, nq, nkv, d, status);
+  else
+    qkv_post_kernel<bf16><<<tokens, 128, 0, stream>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+        (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
+        slot_mapping, num_slots, nq, nkv, d, status);
+  VOSTI_LAUNCH_CHECK();
+}

@@ -1,0 +1,112 @@
+// Row-wise kernels: embedding gather, (residual-fused) RMSNorm, SiLU(gate)*up.
+// Formulas as the reference computes them: kernels/triton_kernels/embedding.py:62-84,
+// rmsnorm.py:63-93, rmsnorm_residual.py:86-125, silu_mul.py:66-87. All arithmetic in
+// float32; T is the storage type of activations (float or bf16).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 T* __restrict__ out, int hidden, int vocab, unsigned* status) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_TOKEN_RANGE);
+    id = 0;
+  }
+  const T* src = table + (int64_t)id * hidden;
+  T* dst = out + (int64_t)t * hidden;
+  const int bytes = hidden * (int)sizeof(T);
+  if (bytes % 16 == 0) {
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    int4* d4 = reinterpret_cast<int4*>(dst);
+    for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) d4[i] = bad ? make_int4(0, 0, 0, 0) : s4[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = bad ? from_f32<T>(0.f) : src[i];
+  }
+}
+
+VOSTI_API int vosti_embedding(const int* ids, const void* table, void* out, int tokens, int hidden,
+                              int vocab, int is_f32, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d",
+                tokens, hidden, vocab);
+  if (tokens == 0) return VOSTI_OK;
+  if (is_f32)
+    embedding_kernel<float><<<tokens, 128, 0, stream>>>(ids, (const float*)table, (float*)out, hidden, vocab, status);
+  else
+    embedding_kernel<bf16><<<tokens, 128, 0, stream>>>(ids, (const bf16*)table, (bf16*)out, hidden, vocab, status);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One block per row. With a residual: h = x + r in float32, residual_out = round(h),
+// the variance and the scaling use the unrounded h. Without: h = x.
+// The row is read twice (the second read hits L1/L2) so that any width works.
+template <typename T, int BLOCK>
+__global__ void __launch_bounds__(BLOCK)
+rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, const void* __restrict__ weight,
+               int weight_is_f32, T* __restrict__ out, T* __restrict__ residual_out, int width, float eps) {
+  __shared__ float scratch[32];
+  const int64_t base = (int64_t)blockIdx.x * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += BLOCK) {
+    float h = to_f32(x[base + i]);
+    if (residual) h += to_f32(residual[base + i]);
+    ss += h * h;
+  }
+  const float total = block_sum(ss, scratch);
+  const float rrms = rsqrtf(total / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += BLOCK) {
+    float h = to_f32(x[base + i]);
+    if (residual) h += to_f32(residual[base + i]);
+    if (residual_out) residual_out[base + i] = from_f32<T>(h);
+    out[base + i] = from_f32<T>(h * rrms * load_flex(weight, weight_is_f32, i));
+  }
+}
+
+// `residual` may be null (plain norm). `residual_out` may be `residual` or `x` itself:
+// a thread owns the same elements in both passes and reads each before it writes it.
+// `out` must be a buffer of its own.
+VOSTI_API int vosti_rmsnorm(const void* x, const void* residual, const void* weight, int weight_is_f32,
+                            void* out, void* residual_out, int rows, int width, float eps, int is_f32,
+                            cudaStream_t stream) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", rows, width);
+  VOSTI_REQUIRE(eps > 0.f, "rmsnorm: eps must be positive");
+  if (rows == 0) return VOSTI_OK;
+  VOSTI_REQUIRE(out != x && out != residual && out != residual_out, "rmsnorm: out must not alias another operand");
+  if (is_f32)
+    rmsnorm_kernel<float, 256><<<rows, 256, 0, stream>>>((const float*)x, (const float*)residual, weight,
+                                                        weight_is_f32, (float*)out, (float*)residual_out, width, eps);
+  else
+    rmsnorm_kernel<bf16, 256><<<rows, 256, 0, stream>>>((const bf16*)x, (const bf16*)residual, weight,
+                                                       weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+// in: [rows, 2*inter] with the gate half first; out: [rows, inter].
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int inter) {
+  const int64_t n = rows * inter;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / inter;
+    const int c = (int)(i - r * inter);
+    const float g = to_f32(gate_up[r * 2 * inter + c]);
+    const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
+    out[i] = from_f32<T>(g * (1.f / (1.f + expf(-g))) * u);
+  }
+}
+
+VOSTI_API int vosti_silu_mul(const void* gate_up, void* out, int rows, int inter, int is_f32,
+                             cudaStream_t stream) {
+  VOSTI_REQUIRE(rows >= 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
+  if (rows == 0) return VOSTI_OK;
+  const int64_t n = (int64_t)rows * inter;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (is_f32)
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, rows, inter);
+  else
+    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, rows, inter);
+  VOSTI_LAUNCH_CHECK();
+}

@@ -1,0 +1,121 @@
+// Sampling over float32 logits rows, one block per row.
+//   temperature <= 0: greedy, the lowest index of the maximum (the reference samples
+//   with torch.argmax over the row only: python/vosti_kernels/kernels.py:1088-1104).
+//   temperature  > 0: weights w_i = exp((l_i - max) / T); the token is the first whose
+//   inclusive cumulative weight exceeds u * total, u being a 24-bit uniform in [0,1)
+//   from a counter-based generator keyed by (seed, index of the token being drawn).
+// A row's result depends on its own logits, seed and index only, so it is independent of
+// what else is in the batch.
+#include "common.cuh"
+
+namespace {
+constexpr int THREADS = 1024;
+
+__device__ __forceinline__ float uniform24(unsigned long long seed, unsigned long long index) {
+  unsigned long long z = seed * 0x9E3779B97F4A7C15ull + (index + 1ull) * 0xBF58476D1CE4E5B9ull;
+  z ^= z >> 30;
+  z *= 0xBF58476D1CE4E5B9ull;
+  z ^= z >> 27;
+  z *= 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, const float* __restrict__ temperature,
+              const long long* __restrict__ seeds, const long long* __restrict__ counters, int* __restrict__ out) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  __shared__ float s_scan[THREADS + 1];
+  __shared__ int s_token;
+  const float* row = logits + (int64_t)blockIdx.x * row_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // ---- maximum and its lowest index (needed by both modes)
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = tid; i < vocab; i += THREADS) {
+    const float v = row[i];
+    if (v > best || (v == best && i < best_i)) {
+      best = v;
+      best_i = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) {
+      best = ov;
+      best_i = oi;
+    }
+  }
+  if (lane == 0) {
+    s_val[warp] = best;
+    s_idx[warp] = best_i;
+  }
+  __syncthreads();
+  best = s_val[0];
+  best_i = s_idx[0];
+  for (int w = 1; w < THREADS / 32; ++w) {
+    if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) {
+      best = s_val[w];
+      best_i = s_idx[w];
+    }
+  }
+  const float temp = temperature ? temperature[blockIdx.x] : 0.f;
+  if (!(temp > 0.f)) {
+    if (tid == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+    return;
+  }
+
+  // ---- temperature: contiguous chunk per thread, fixed-order scan
+  const int chunk = (vocab + THREADS - 1) / THREADS;
+  const int begin = min(tid * chunk, vocab), end = min(begin + chunk, vocab);
+  const float inv_t = 1.f / temp;
+  float local = 0.f;
+  for (int i = begin; i < end; ++i) local += expf((row[i] - best) * inv_t);
+  s_scan[tid + 1] = local;
+  if (tid == 0) {
+    s_scan[0] = 0.f;
+    s_token = vocab - 1;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float run = 0.f;
+    for (int i = 1; i <= THREADS; ++i) {
+      run += s_scan[i];
+      s_scan[i] = run;
+    }
+  }
+  __syncthreads();
+  const float total = s_scan[THREADS];
+  const float u = uniform24((unsigned long long)seeds[blockIdx.x], (unsigned long long)counters[blockIdx.x]);
+  const float target = u * total;
+  const float before = s_scan[tid];
+  if (target >= before && target < s_scan[tid + 1]) {
+    float run = 0.f;
+    for (int i = begin; i < end; ++i) {
+      run += expf((row[i] - best) * inv_t);
+      if (before + run > target) {
+        s_token = i;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) out[blockIdx.x] = s_token;
+}
+}  // namespace
+
+// logits: float32 [rows, vocab] with `row_stride` elements between rows; temperature:
+// float32[rows] or null (all greedy); seeds, counters: int64[rows] (may be null if all greedy).
+VOSTI_API int vosti_sample(const float* logits, int rows, int vocab, int64_t row_stride, const float* temperature,
+                           const long long* seeds, const long long* counters, int* out, cudaStream_t stream) {
+  VOSTI_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+  VOSTI_REQUIRE(temperature == nullptr || (seeds != nullptr && counters != nullptr),
+                "sample: temperature sampling needs seeds and counters");
+  if (rows == 0) return VOSTI_OK;
+  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, row_stride, temperature, seeds, counters, out);
+  VOSTI_LAUNCH_CHECK();
+}

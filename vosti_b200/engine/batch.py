@@ -1,0 +1,163 @@
+"""The flat batch one step runs: what the parts see of it (`StepContext`) and how it
+is laid out for a single host-to-device copy.
+
+The reference describes a step to its model by the same flat index tensors
+(input_ids, positions, slot_mapping, block_table, cu_seqlens_q/k:
+src/exec/cache_scheduler/mod.rs:824-930, python/vosti_kernels/kernels.py:519-626) and
+builds each with its own copy; here all of them are sections of one pinned int32
+buffer that is copied once.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them whose
+    logits are wanted."""
+
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class GroupView:
+    """One cache group as the step sees it."""
+
+    block_table: torch.Tensor     # int32 [requests, max_pages]
+    slot_mapping: torch.Tensor    # int32 [tokens]
+    page_size: int
+    max_pages: int
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_requests: int
+    tokens: torch.Tensor          # int32 [T]
+    positions: torch.Tensor       # int32 [T], absolute position of each token
+    request_of: torch.Tensor      # int32 [T], row of the request each token belongs to
+    cu_q: torch.Tensor            # int32 [B+1], cumulative token counts
+    kv_len: torch.Tensor          # int32 [B], keys of each request after this step
+    state_slots: torch.Tensor     # int32 [B], per-request state slot
+    want_rows: torch.Tensor       # int32 [W], flat token indices whose logits are wanted
+    groups: List[GroupView]
+    status: torch.Tensor          # int32 [1], device fault bits
+    dtype: torch.dtype
+    device: torch.device
+    # host copies, for parts that loop over requests on the host
+    host_q_lens: List[int] = field(default_factory=list)
+    host_kv_lens: List[int] = field(default_factory=list)
+    host_state_slots: List[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_kv_len: int = 0
+    all_decode: bool = False
+
+    def group(self, index: int) -> GroupView:
+        return self.groups[index]
+
+
+class StagingBuffer:
+    """Pinned host memory and its device twin, grown on demand."""
+
+    def __init__(self, device: torch.device, capacity: int = 1 << 16):
+        self.device = device
+        self.copied = None          # event after the last host-to-device copy
+        self._alloc(capacity)
+
+    def _alloc(self, capacity: int) -> None:
+        self.capacity = capacity
+        self.host = torch.empty(capacity, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
+
+    def reserve(self, count: int) -> None:
+        """Make room for `count` ints; waits until the previous copy has left the host
+        buffer before it may be overwritten."""
+        if self.copied is not None:
+            self.copied.synchronize()
+        if count > self.capacity:
+            torch.cuda.current_stream(self.device).synchronize()
+            self._alloc(max(count, 2 * self.capacity))
+
+    def upload(self, count: int) -> None:
+        self.dev[:count].copy_(self.host[:count], non_blocking=True)
+        if self.copied is None:
+            self.copied = torch.cuda.Event()
+        self.copied.record()
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return (value + multiple - 1) // multiple * multiple
+
+
+def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: Sequence[int],
+                  slots_per_group: Sequence[Sequence[Sequence[int]]], block_rows: Sequence[Sequence[Sequence[int]]],
+                  state_slots: Sequence[int], page_size: int, status: torch.Tensor, dtype: torch.dtype) -> StepContext:
+    """Lay the batch out and copy it. `starts[i]` is the position of entry i's first token;
+    `slots_per_group[g][i]` the cache slots of its tokens in group g; `block_rows[g][i]` its
+    page ids in group g."""
+    B = len(entries)
+    q_lens = [len(e.tokens) for e in entries]
+    T = sum(q_lens)
+    W = sum(len(e.want) for e in entries)
+    G = len(slots_per_group)
+    max_pages = [_round_up(max((len(r) for r in block_rows[g]), default=1) or 1, 4) for g in range(G)]
+    # sections are padded to 4 ints so that every section starts 16-byte aligned
+    sizes = [T, T, T, B + 1, B, B, W] + [x for g in range(G) for x in (T, B * max_pages[g])]
+    offsets, total = [], 0
+    for s in sizes:
+        offsets.append(total)
+        total += _round_up(max(s, 1), 4)
+    staging.reserve(total)
+    buf = staging.host_np
+    o_tok, o_pos, o_req, o_cu, o_kv, o_slot, o_want = offsets[:7]
+    cursor, wcursor = 0, 0
+    buf[o_cu] = 0
+    kv_lens = []
+    for i, e in enumerate(entries):
+        n = q_lens[i]
+        buf[o_tok + cursor:o_tok + cursor + n] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
+        buf[o_pos + cursor:o_pos + cursor + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+        buf[o_req + cursor:o_req + cursor + n] = i
+        for w in e.want:
+            if not 0 <= w < n:
+                raise ValueError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
+            buf[o_want + wcursor] = cursor + w
+            wcursor += 1
+        cursor += n
+        buf[o_cu + i + 1] = cursor
+        buf[o_kv + i] = starts[i] + n
+        kv_lens.append(starts[i] + n)
+        buf[o_slot + i] = state_slots[i]
+    group_offsets = []
+    for g in range(G):
+        o_sm, o_bt = offsets[7 + 2 * g], offsets[8 + 2 * g]
+        cursor = 0
+        for i in range(B):
+            n = q_lens[i]
+            buf[o_sm + cursor:o_sm + cursor + n] = slots_per_group[g][i]
+            cursor += n
+            row = block_rows[g][i]
+            base = o_bt + i * max_pages[g]
+            buf[base:base + len(row)] = row
+            buf[base + len(row):base + max_pages[g]] = 0
+        group_offsets.append((o_sm, o_bt))
+    staging.upload(total)
+    dev = staging.dev
+    groups = [GroupView(block_table=dev[o_bt:o_bt + B * max_pages[g]].view(B, max_pages[g]),
+                        slot_mapping=dev[o_sm:o_sm + T], page_size=page_size, max_pages=max_pages[g])
+              for g, (o_sm, o_bt) in enumerate(group_offsets)]
+    return StepContext(
+        num_tokens=T, num_requests=B, tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T],
+        request_of=dev[o_req:o_req + T], cu_q=dev[o_cu:o_cu + B + 1], kv_len=dev[o_kv:o_kv + B],
+        state_slots=dev[o_slot:o_slot + B], want_rows=dev[o_want:o_want + W], groups=groups, status=status,
+        dtype=dtype, device=staging.device, host_q_lens=q_lens, host_kv_lens=kv_lens,
+        host_state_slots=list(state_slots), max_q_len=max(q_lens, default=0),
+        max_kv_len=max(kv_lens, default=0), all_decode=all(n == 1 for n in q_lens))

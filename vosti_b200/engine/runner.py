@@ -1,0 +1,149 @@
+"""The step function: run a batch of (request, its next tokens) from the cache and
+return the logits at the wanted places.
+
+A step holds portions of prompts beside single decoded tokens, cut anywhere; it runs
+only the tokens it is given. The model, the cache manager and the kernels here are the
+ones generation uses; trace replay drives this same object.
+
+Order inside a step as in the reference (src/exec/engine.rs:2781-2782, 3315-3333;
+src/exec/dense_swiglu_decoder.rs:253-320): every layer stores the step's keys and values
+before its attention reads the cache.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache import CacheManager, OutOfPages
+from ..config import model_spec_from_dir, ModelSpec
+from ..models import build_model
+from ..weights import check_tensors, load_weights
+from .batch import StagingBuffer, StepContext, StepEntry, build_context
+
+_FAULTS = {
+    1: "token id outside the vocabulary", 2: "cache slot outside the pool",
+    4: "block-table entry outside the pool", 8: "position beyond the rotation table",
+    16: "a bounded device wait gave up", 32: "gathered row outside the input",
+}
+
+
+class DeviceFault(RuntimeError):
+    pass
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name in (torch.bfloat16, torch.float32):
+            return name
+    table = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+             "fp32": torch.float32, "f32": torch.float32}
+    if str(name) in table:
+        return table[str(name)]
+    raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}")
+
+
+class ModelRunner:
+    def __init__(self, model_dir: Optional[str | Path] = None, *, dtype="bfloat16", device="cuda:0",
+                 num_pages: int, page_size: int = 16, max_requests: int = 64, prefix_reuse: bool = False,
+                 spec: Optional[ModelSpec] = None, tensors: Optional[Dict[str, torch.Tensor]] = None):
+        self.device = torch.device(device)
+        self.dtype = parse_dtype(dtype)
+        ops.require_device(self.device)
+        ops.library()
+        torch.cuda.set_device(self.device)
+        if torch.backends.cuda.matmul.allow_tf32:
+            torch.backends.cuda.matmul.allow_tf32 = False
+        self.spec = spec if spec is not None else model_spec_from_dir(model_dir)
+        self.model = build_model(self.spec)
+        expected = self.model.expected_weights()
+        if tensors is None:
+            tensors = load_weights(model_dir, expected, device=self.device, dtype=self.dtype,
+                                   ignore=self.model.ignorable_weights())
+        else:
+            check_tensors(tensors, expected, ignore=self.model.ignorable_weights())
+            if self.dtype == torch.float32:
+                tensors = {k: (v.float() if v.is_floating_point() else v) for k, v in tensors.items()}
+        self.model.load(tensors, self.dtype)
+        cache_specs = [b.mixer.cache_spec() for b in self.model.blocks]
+        state_specs = [b.mixer.state_spec() for b in self.model.blocks]
+        self.cache = CacheManager(cache_specs, state_specs, num_pages=num_pages, page_size=page_size,
+                                  max_requests=max_requests, device=self.device, dtype=self.dtype,
+                                  prefix_reuse=prefix_reuse)
+        self.staging = StagingBuffer(self.device)
+        # word 0: device fault bits; the rest: sampled tokens of a step
+        self.result = torch.zeros(1 + max(max_requests, 1), dtype=torch.int32, device=self.device)
+        self.result_host = torch.zeros(1 + max(max_requests, 1), dtype=torch.int32, pin_memory=True)
+        self.status = self.result[:1]
+        self.steps = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------ requests
+    def begin(self, request_id, prompt_for_reuse: Optional[Sequence[int]] = None):
+        return self.cache.begin(request_id, prompt_for_reuse)
+
+    def finish(self, request_id) -> None:
+        self.cache.finish(request_id)
+
+    # ------------------------------------------------------------ the step
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserve cache entries for the step's tokens (all requests or none) and copy the
+        batch to the device."""
+        cache = self.cache
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if e.request_id not in cache.live:
+                raise KeyError(f"request {e.request_id!r} is not live")
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+        for g, group in enumerate(cache.groups):
+            need = 0
+            for e in entries:
+                res = cache.live[e.request_id]
+                need += max(0, cache.pages_for(res.length + len(e.tokens)) - len(res.pages[g]))
+            if need > group.pool.available():
+                raise OutOfPages(f"step needs {need} pages in group {g}, {group.pool.available()} available")
+        starts = [cache.length(e.request_id) for e in entries]
+        limit = self.spec.max_positions
+        for e, start in zip(entries, starts):
+            if start + len(e.tokens) > limit:
+                raise ValueError(f"request {e.request_id!r} would reach position {start + len(e.tokens)}, "
+                                 f"the model's limit is {limit}")
+        slots = [cache.extend(e.request_id, len(e.tokens)) for e in entries]
+        G = len(cache.groups)
+        slots_per_group = [[slots[i][g] for i in range(len(entries))] for g in range(G)]
+        block_rows = [[cache.block_row(e.request_id, g) for e in entries] for g in range(G)]
+        state_slots = [cache.slot(e.request_id) for e in entries]
+        return build_context(self.staging, entries, starts, slots_per_group, block_rows, state_slots,
+                             cache.page_size, self.status, self.dtype)
+
+    def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """The model over the prepared batch; float32 logits [wanted, vocab] or None."""
+        final = self.model.forward(ctx, self.cache.layer_caches)
+        self.steps += 1
+        if ctx.want_rows.shape[0] == 0:
+            return None
+        return self.model.logits(ctx, final, ctx.want_rows)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        ctx = self.prepare(entries)
+        logits = self.run(ctx)
+        for e in entries:
+            self.cache.trim(e.request_id)
+        return logits
+
+    # ------------------------------------------------------------ status
+    def check_status(self) -> None:
+        """Read the device fault word (synchronises) and raise if a kernel set a bit."""
+        bits = int(self.status.item())
+        if bits:
+            self.status.zero_()
+            names = [text for bit, text in _FAULTS.items() if bits & bit]
+            raise DeviceFault("device reported: " + "; ".join(names))

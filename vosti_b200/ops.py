@@ -1,0 +1,203 @@
+"""Python face of the CUDA kernels: one function per kernel, taking torch tensors
+that live on the GPU and launching on torch's current stream.
+
+There is no CPU fallback and no library stand-in: if the compiled library is
+missing it is built, and if that fails, or the device is not sm_100, the call
+raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+_LIB = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The compiled kernel library, built at the first call."""
+    global _LIB
+    if _LIB is None:
+        lib = ctypes.CDLL(str(_build.library_path()))
+        lib.vosti_last_error.restype = ctypes.c_char_p
+        _LIB = lib
+    return _LIB
+
+
+_CHECKED_DEVICES = set()
+
+
+def require_device(device: torch.device) -> None:
+    """Fail loudly unless `device` is a CUDA device of compute capability 10.x."""
+    if device.type != "cuda":
+        raise KernelError(f"vosti_b200 kernels run on a CUDA device, got '{device}'")
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index in _CHECKED_DEVICES:
+        return
+    major, minor = torch.cuda.get_device_capability(index)
+    if major != 10:
+        raise KernelError(f"vosti_b200 kernels are built for sm_100a; device {index} is sm_{major}{minor}")
+    _CHECKED_DEVICES.add(index)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {library().vosti_last_error().decode()} (code {code})")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _is_f32(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 1
+    if t.dtype == torch.bfloat16:
+        return 0
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _same_dtype(*tensors: torch.Tensor) -> int:
+    flag = _is_f32(tensors[0])
+    for t in tensors[1:]:
+        if t is not None and _is_f32(t) != flag:
+            raise KernelError("activation tensors of one call must share a dtype")
+    return flag
+
+
+def _contig(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_contiguous():
+            raise KernelError("kernels take contiguous tensors")
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    _contig(ids, table)
+    out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+    _check(library().vosti_embedding(_p(ids), _p(table), _p(out), ids.shape[0], table.shape[1],
+                                     table.shape[0], _is_f32(table), _p(status), _stream()), "embedding")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+            residual: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None):
+    """out = rmsnorm(x [+ residual]) * weight; with `residual` the sum is written to
+    `residual_out` (which may be `residual` itself). Returns (out, residual_out)."""
+    _contig(x, weight, residual, residual_out)
+    flag = _same_dtype(x, residual, residual_out)
+    out = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _check(library().vosti_rmsnorm(_p(x), _p(residual), _p(weight), _is_f32(weight), _p(out),
+                                   _p(residual_out), rows, x.shape[-1], ctypes.c_float(eps), flag,
+                                   _stream()), "rmsnorm")
+    return out, residual_out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    _contig(gate_up)
+    inter = gate_up.shape[-1] // 2
+    out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(library().vosti_silu_mul(_p(gate_up), _p(out), gate_up.shape[0], inter, _is_f32(gate_up),
+                                    _stream()), "silu_mul")
+    return out
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, *,
+              out_dtype: Optional[torch.dtype] = None,
+              row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x[row_index] @ w.T with float32 arithmetic on the CUDA cores."""
+    _contig(x, w, row_index)
+    rows = x.shape[0] if row_index is None else row_index.shape[0]
+    out = torch.empty((rows, w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+    if x.shape[1] != w.shape[1]:
+        raise KernelError(f"gemm: inner sizes differ ({x.shape[1]} vs {w.shape[1]})")
+    _check(library().vosti_gemm_simt(_p(x), _p(w), _p(out), _p(row_index), rows, x.shape[0], w.shape[0],
+                                     x.shape[1], _is_f32(x), _is_f32(w), _is_f32(out), _p(status),
+                                     _stream()), "gemm_simt")
+    return out
+
+
+def qkv_post(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *,
+             nq: int, nkv: int, head_dim: int, q_norm_w: Optional[torch.Tensor],
+             k_norm_w: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+             sin: Optional[torch.Tensor], positions: Optional[torch.Tensor],
+             slot_mapping: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:
+    """Head norm, rotation and cache store after the QKV projection; returns q [T, nq*d]."""
+    _contig(qkv, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, positions, slot_mapping)
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * head_dim:
+        raise KernelError("qkv_post: input width does not match the head counts")
+    flag = _same_dtype(qkv, k_cache, v_cache)
+    q_out = torch.empty((tokens, nq * head_dim), dtype=qkv.dtype, device=qkv.device)
+    num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * head_dim)
+    norm_flag = 0
+    if q_norm_w is not None:
+        norm_flag = _is_f32(q_norm_w)
+        if k_norm_w is not None and _is_f32(k_norm_w) != norm_flag:
+            raise KernelError("qkv_post: q and k norm weights must share a dtype")
+    elif k_norm_w is not None:
+        norm_flag = _is_f32(k_norm_w)
+    max_positions = 0 if cos is None else cos.shape[0]
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != head_dim // 2):
+        raise KernelError("qkv_post: rotation tables must be float32 [positions, head_dim/2]")
+    _check(library().vosti_qkv_post(
+        _p(qkv), _p(q_out), _p(k_cache), _p(v_cache), _p(q_norm_w), _p(k_norm_w), norm_flag,
+        ctypes.c_float(eps), _p(cos), _p(sin), max_positions, _p(positions), _p(slot_mapping),
+        ctypes.c_int64(num_slots), tokens, nq, nkv, head_dim, flag, _p(status), _stream()), "qkv_post")
+    return q_out
+
+
+def attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, positions: torch.Tensor,
+                   request_of: torch.Tensor, block_table: torch.Tensor, page_size: int, nq: int, nkv: int,
+                   head_dim: int, scale: float, window: int, status: torch.Tensor) -> torch.Tensor:
+    _contig(q, k_cache, v_cache, positions, request_of, block_table)
+    flag = _same_dtype(q, k_cache, v_cache)
+    tokens = q.shape[0]
+    out = torch.empty_like(q)
+    num_pages = k_cache.numel() // (page_size * nkv * head_dim)
+    _check(library().vosti_attention_simt(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(positions), _p(request_of), _p(block_table),
+        block_table.shape[1], page_size, num_pages, tokens, nq, nkv, head_dim, ctypes.c_float(scale),
+        window, flag, _p(status), _stream()), "attention")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tokens (int32[rows]) from float32 logits [rows, vocab]."""
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 [rows, vocab] with unit inner stride")
+    _contig(temperature, seeds, counters)
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _check(library().vosti_sample(_p(logits), logits.shape[0], logits.shape[1],
+                                  ctypes.c_int64(logits.stride(0)), _p(temperature), _p(seeds),
+                                  _p(counters), _p(out), _stream()), "sample")
+    return out
+
+
+def gemm_tc_supported(n: int, k: int) -> bool:
+    """Whether the tensor-core product takes a [n, k] bfloat16 weight."""
+    return False
+
+
+def gemm_tc(x, w, status, *, out_dtype=None, row_index=None):
+    raise KernelError("tensor-core product is not available")
+
+
+def attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,
+              head_dim: int, scale: float, window: int) -> torch.Tensor:
+    """Attention of every query row of the batch over its request's cached keys."""
+    return attention_simt(q, k_cache, v_cache, positions=ctx.positions, request_of=ctx.request_of,
+                          block_table=group.block_table, page_size=group.page_size, nq=nq, nkv=nkv,
+                          head_dim=head_dim, scale=scale, window=window, status=ctx.status)

@@ -1,0 +1,93 @@
+"""Grouped-query attention over the paged cache, with optional per-head q/k RMSNorm
+and an optional rotation, as one mixer.
+
+Order of operations (src/exec/dense_swiglu_decoder.rs:171-367): q, k, v projections
+without bias; per-head norm of q and k (not v) before the rotation; keys (normed and
+rotated) and values are stored in the cache before the layer's attention, so a query
+reads its own key through the cache; attention with scale `scale`, causal, optionally
+limited to a window; output projection. Sizes and constants are parameters of the spec:
+num_heads, num_kv_heads, head_dim, scale, window (0 = all keys), head_norm_eps (None =
+no head norm).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..config.schema import ConfigError, PartSpec
+from ..weights.loader import WeightSpec
+from .base import Mixer, PagedCacheSpec, PositionEncoding, register_part
+from .linear import linear
+
+
+class Attention(Mixer):
+    def __init__(self, spec: PartSpec, hidden_size: int, position: Optional[PositionEncoding]):
+        super().__init__(spec, hidden_size, position)
+        self.nq = int(spec["num_heads"])
+        self.nkv = int(spec["num_kv_heads"])
+        self.d = int(spec["head_dim"])
+        self.scale = float(spec["scale"])
+        self.window = int(spec.get("window", 0) or 0)
+        eps = spec.get("head_norm_eps")
+        self.head_norm_eps = None if eps is None else float(eps)
+        if self.nq <= 0 or self.nkv <= 0 or self.nq % self.nkv:
+            raise ConfigError(f"attention: num_heads {self.nq} must be a positive multiple of "
+                              f"num_kv_heads {self.nkv}")
+        if self.d <= 0 or self.d % 16 or self.d > 256:
+            raise ConfigError(f"attention: head_dim {self.d} must be a multiple of 16, at most 256")
+        if self.window < 0:
+            raise ConfigError("attention: window must be >= 0")
+        self.w_qkv = self.w_q = self.w_o = self.q_norm = self.k_norm = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        h, nq, nkv, d = self.hidden_size, self.nq, self.nkv, self.d
+        specs = {
+            "q_proj.weight": WeightSpec((nq * d, h)), "k_proj.weight": WeightSpec((nkv * d, h)),
+            "v_proj.weight": WeightSpec((nkv * d, h)), "o_proj.weight": WeightSpec((h, nq * d)),
+        }
+        if self.head_norm_eps is not None:
+            specs["q_norm.weight"] = WeightSpec((d,), init="norm", std=0.1)
+            specs["k_norm.weight"] = WeightSpec((d,), init="norm", std=0.1)
+        return specs
+
+    def load(self, tensors, dtype):
+        parts = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+        # one [ (nq + 2 nkv) d, hidden ] matrix: the projection is a single product
+        self.w_qkv = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
+        self.w_q = self.w_qkv[: self.nq * self.d]
+        self.w_o = tensors["o_proj.weight"]
+        if self.head_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors["q_norm.weight"], tensors["k_norm.weight"]
+            if self.q_norm.dtype != self.k_norm.dtype:
+                self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+
+    def setup(self, device, dtype):
+        if self.position is not None:
+            self.position.setup(device, dtype)
+
+    def cache_spec(self) -> PagedCacheSpec:
+        return PagedCacheSpec(entries=2, heads=self.nkv, width=self.d, window=self.window)
+
+    def forward(self, ctx, x, cache, writes_cache: bool = True):
+        group = ctx.group(cache.group)
+        tables = self.position.rotation_tables() if self.position is not None else None
+        cos, sin = tables if tables is not None else (None, None)
+        eps = self.head_norm_eps if self.head_norm_eps is not None else 1.0
+        common = dict(nq=self.nq, head_dim=self.d, q_norm_w=self.q_norm, eps=eps, cos=cos, sin=sin,
+                      positions=ctx.positions, status=ctx.status)
+        if writes_cache:
+            qkv = linear(ctx, x, self.w_qkv)
+            q = ops.qkv_post(qkv, cache.k, cache.v, nkv=self.nkv, k_norm_w=self.k_norm,
+                             slot_mapping=group.slot_mapping, **common)
+        else:
+            q = ops.qkv_post(linear(ctx, x, self.w_q), None, None, nkv=0, k_norm_w=None,
+                             slot_mapping=None, **common)
+        attn = ops.attention(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, head_dim=self.d,
+                             scale=self.scale, window=self.window)
+        return linear(ctx, attn, self.w_o)
+
+
+register_part("mixer", "attention", Attention, replace=True)

@@ -1,0 +1,151 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part is built from a `PartSpec` (its kind and constants) and the model's
+hidden width; it declares the tensors it needs by name (`weight_specs`), takes
+them in `load`, and computes in `forward`. No part knows which model it is in.
+
+* Norm:            forward(x) / forward_add(x, residual)
+* PositionEncoding: tables the mixer applies (cos/sin for a rotation), or nothing
+* Mixer:           forward(ctx, x, cache, writes_cache) -> y. It declares what it keeps per
+                   token in pages (`cache_spec`) and what it keeps per request in a slot
+                   of fixed size (`state_spec`).
+* FeedForward:     forward(ctx, x) -> y
+* Arrangement:     how a block wires mixer, feed-forward and norms around the residual.
+
+The reference has the same roles as closed Rust records
+(src/boundary/dense_swiglu_decoder.rs:18-24, 96-106).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, Optional, Tuple
+
+import torch
+
+from ..config.schema import ConfigError, PartSpec
+from ..weights.loader import WeightSpec
+
+
+@dataclass(frozen=True)
+class PagedCacheSpec:
+    """Per-token cache of a mixer: `entries` tensors (keys and values: 2), each
+    [tokens, heads, width] per token; `window` > 0 means only the last `window`
+    tokens are ever read again, so older pages may be given back."""
+
+    entries: int
+    heads: int
+    width: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size: one tensor of `shape` per request slot,
+    zeroed when a request takes the slot."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    def __init__(self, spec: PartSpec, hidden_size: int):
+        self.spec = spec
+        self.hidden_size = hidden_size
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
+        """Take the tensors named in `weight_specs` (relative names)."""
+
+    def setup(self, device: torch.device, dtype: torch.dtype) -> None:
+        """Build device tables that do not come from the checkpoint."""
+
+
+class Norm(Part):
+    def forward(self, ctx, x):
+        raise NotImplementedError
+
+    def forward_add(self, ctx, x, residual):
+        """Return (norm(x + residual), x + residual)."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def __init__(self, spec: PartSpec, hidden_size: int, head_dim: int):
+        super().__init__(spec, hidden_size)
+        self.head_dim = head_dim
+
+    def rotation_tables(self) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        """float32 cos and sin [max_positions, head_dim/2] for a half-split rotation of q
+        and k, or None if this encoding is not a rotation."""
+        return None
+
+
+class Mixer(Part):
+    def __init__(self, spec: PartSpec, hidden_size: int, position: Optional[PositionEncoding]):
+        super().__init__(spec, hidden_size)
+        self.position = position
+
+    def cache_spec(self) -> Optional[PagedCacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, ctx, x, cache, writes_cache: bool = True):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x):
+        raise NotImplementedError
+
+
+_REGISTRIES: Dict[str, Dict[str, Callable]] = {
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {},
+}
+
+
+def register_part(role: str, kind: str, factory: Callable, *, replace: bool = False) -> None:
+    """Register `factory` for parts of `role` ('norm', 'position', 'mixer', 'feed_forward',
+    'arrangement') with the given kind."""
+    if role not in _REGISTRIES:
+        raise ConfigError(f"unknown part role '{role}'; roles: {sorted(_REGISTRIES)}")
+    if kind in _REGISTRIES[role] and not replace:
+        raise ConfigError(f"{role} kind '{kind}' is already registered")
+    _REGISTRIES[role][kind] = factory
+
+
+def unregister_part(role: str, kind: str) -> None:
+    _REGISTRIES[role].pop(kind, None)
+
+
+def part_factory(role: str, kind: str) -> Callable:
+    table = _REGISTRIES[role]
+    if kind not in table:
+        raise ConfigError(f"unknown {role} kind '{kind}'; known: {sorted(table)}")
+    return table[kind]
+
+
+def build_norm(spec: PartSpec, width: int) -> Norm:
+    return part_factory("norm", spec.kind)(spec, width)
+
+
+def build_position(spec: Optional[PartSpec], hidden_size: int, head_dim: int) -> Optional[PositionEncoding]:
+    if spec is None:
+        return None
+    return part_factory("position", spec.kind)(spec, hidden_size, head_dim)
+
+
+def build_mixer(spec: PartSpec, hidden_size: int, position_spec: Optional[PartSpec]) -> Mixer:
+    factory = part_factory("mixer", spec.kind)
+    head_dim = spec.get("head_dim", 0)
+    position = build_position(position_spec, hidden_size, head_dim) if head_dim else None
+    return factory(spec, hidden_size, position)
+
+
+def build_feed_forward(spec: Optional[PartSpec], hidden_size: int) -> Optional[FeedForward]:
+    if spec is None:
+        return None
+    return part_factory("feed_forward", spec.kind)(spec, hidden_size)

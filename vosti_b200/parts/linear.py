@@ -1,0 +1,21 @@
+"""Matrix product y = x @ w.T for the parts, choosing the kernel by operand types.
+
+bfloat16 x bfloat16 goes to the tensor-core kernel when it takes the sizes; every
+other combination (the float32 path, a 32-bit weight under bfloat16 serving, sizes
+the tensor-core kernel refuses) goes to the CUDA-core kernel with float32 arithmetic.
+The choice depends on types and on (N, K) only, never on the number of rows.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+
+
+def linear(ctx, x: torch.Tensor, w: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
+           row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.gemm_tc_supported(w.shape[0], w.shape[1])):
+        return ops.gemm_tc(x, w, ctx.status, out_dtype=out_dtype, row_index=row_index)
+    return ops.gemm_simt(x, w, ctx.status, out_dtype=out_dtype, row_index=row_index)
