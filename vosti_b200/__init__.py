@@ -2,3 +2,10 @@
 from . import config  # registers the built-in architecture
 
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    if name == "Engine":
+        from .engine.engine import Engine
+        return Engine
+    raise AttributeError(name)

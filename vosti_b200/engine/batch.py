@@ -58,6 +58,7 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     all_decode: bool = False
+    extras: dict = field(default_factory=dict)   # further per-step device arrays by name
 
     def group(self, index: int) -> GroupView:
         return self.groups[index]
@@ -99,7 +100,8 @@ def _round_up(value: int, multiple: int) -> int:
 
 def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: Sequence[int],
                   slots_per_group: Sequence[Sequence[Sequence[int]]], block_rows: Sequence[Sequence[Sequence[int]]],
-                  state_slots: Sequence[int], page_size: int, status: torch.Tensor, dtype: torch.dtype) -> StepContext:
+                  state_slots: Sequence[int], page_size: int, status: torch.Tensor, dtype: torch.dtype,
+                  extras: Optional[dict] = None) -> StepContext:
     """Lay the batch out and copy it. `starts[i]` is the position of entry i's first token;
     `slots_per_group[g][i]` the cache slots of its tokens in group g; `block_rows[g][i]` its
     page ids in group g."""
@@ -115,6 +117,11 @@ def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: 
     for s in sizes:
         offsets.append(total)
         total += _round_up(max(s, 1), 4)
+    extra_at = {}
+    for name, array in (extras or {}).items():
+        words = np.ascontiguousarray(array).view(np.int32)
+        extra_at[name] = (total, words, array.dtype)
+        total += _round_up(max(words.size, 1), 4)
     staging.reserve(total)
     buf = staging.host_np
     o_tok, o_pos, o_req, o_cu, o_kv, o_slot, o_want = offsets[:7]
@@ -149,8 +156,14 @@ def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: 
             buf[base:base + len(row)] = row
             buf[base + len(row):base + max_pages[g]] = 0
         group_offsets.append((o_sm, o_bt))
+    for name, (at, words, _) in extra_at.items():
+        buf[at:at + words.size] = words
     staging.upload(total)
     dev = staging.dev
+    torch_types = {np.dtype(np.float32): torch.float32, np.dtype(np.int64): torch.int64,
+                   np.dtype(np.int32): torch.int32}
+    extra_views = {name: dev[at:at + words.size].view(torch_types[np.dtype(kind)])
+                   for name, (at, words, kind) in extra_at.items()}
     groups = [GroupView(block_table=dev[o_bt:o_bt + B * max_pages[g]].view(B, max_pages[g]),
                         slot_mapping=dev[o_sm:o_sm + T], page_size=page_size, max_pages=max_pages[g])
               for g, (o_sm, o_bt) in enumerate(group_offsets)]
@@ -160,4 +173,4 @@ def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: 
         state_slots=dev[o_slot:o_slot + B], want_rows=dev[o_want:o_want + W], groups=groups, status=status,
         dtype=dtype, device=staging.device, host_q_lens=q_lens, host_kv_lens=kv_lens,
         host_state_slots=list(state_slots), max_q_len=max(q_lens, default=0),
-        max_kv_len=max(kv_lens, default=0), all_decode=all(n == 1 for n in q_lens))
+        max_kv_len=max(kv_lens, default=0), all_decode=all(n == 1 for n in q_lens), extras=extra_views)

@@ -1,0 +1,162 @@
+"""The engine: scheduler above the step function, with sampling. This is the Python
+entry point.
+
+    engine = Engine(model_dir, dtype="bfloat16", num_blocks=4096)
+    engine.add_request(0, prompt_ids, max_tokens=8, eos_token_ids=[eos])
+    while engine.has_unfinished():
+        emitted = engine.step()            # {request id: token}
+    # or
+    outputs = engine.generate([prompt_ids, ...], max_tokens=8)
+
+The surface is the reference's Rust API as its example drives it: `Engine::init`,
+`try_add_request`, `step` -> emitted tokens (src/exec/engine.rs:2515, 2664, 2795;
+examples/support/engine_serving.rs:211-219). One step is plan -> forward -> sample ->
+publish completed pages -> commit (src/exec/engine.rs:2781-2782), with one device-to-host
+copy for the sampled tokens and the device fault word.
+"""
+from __future__ import annotations
+
+import json
+import time
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import torch
+
+from ..sampling import sample_rows, sampling_arrays
+from .batch import StepEntry
+from .request import AdmissionStatus, Request
+from .runner import DeviceFault, ModelRunner, _FAULTS
+from .scheduler import Scheduler, SchedulerConfig, StepPlan
+
+
+class Engine:
+    def __init__(self, model: Optional[str] = None, *, dtype="bfloat16", device: str = "cuda:0",
+                 num_blocks: int = 32, block_size: int = 16, max_num_seqs: int = 1,
+                 max_num_batched_tokens: int = 4096, prefill_chunk_size: int = 0,
+                 enable_prefix_caching: bool = True, step_trace: Optional[str] = None,
+                 spec=None, tensors=None):
+        """`num_blocks` pages of `block_size` tokens; `max_num_seqs` rows and
+        `max_num_batched_tokens` tokens per step at most (the reference's VOSTI_NUM_BLOCKS,
+        VOSTI_MAX_SEQS, VOSTI_MAX_BATCHED_TOKENS; its page size is fixed at 64)."""
+        self.runner = ModelRunner(model, dtype=dtype, device=device, num_pages=num_blocks, page_size=block_size,
+                                  max_requests=max_num_seqs, prefix_reuse=enable_prefix_caching, spec=spec,
+                                  tensors=tensors)
+        spec = self.runner.spec
+        self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
+            max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
+            prefill_chunk_size=prefill_chunk_size, vocab_size=spec.vocab_size, max_context=spec.max_positions))
+        self.step_trace = open(step_trace, "a") if step_trace else None
+        self.step_index = 0
+        self.last_plan: Optional[StepPlan] = None
+
+    # ------------------------------------------------------------ requests
+    def add_request(self, request_id, prompt_tokens: Sequence[int], max_tokens: int,
+                    eos_token_ids: Optional[Sequence[int]] = None, ignore_eos: bool = False,
+                    temperature: float = 0.0, seed: int = 0) -> AdmissionStatus:
+        """Queue a request; pages are taken when a step first schedules it."""
+        if eos_token_ids is None:
+            eos_token_ids, ignore_eos = (), True
+        request = Request(request_id, [int(t) for t in prompt_tokens], int(max_tokens),
+                          tuple(int(t) for t in eos_token_ids), bool(ignore_eos), float(temperature), int(seed))
+        return self.scheduler.add_request(request)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def request(self, request_id) -> Optional[Request]:
+        for r in self.scheduler.running + self.scheduler.waiting:
+            if r.request_id == request_id:
+                return r
+        return self.scheduler.finished.get(request_id)
+
+    # ------------------------------------------------------------ one step
+    def step(self) -> Dict[object, int]:
+        """Plan, run, sample and commit one step; returns the tokens emitted by it."""
+        plan = self.scheduler.plan()
+        self.last_plan = plan
+        self.step_index += 1
+        if not plan.rows:
+            self._trace(plan, {})
+            return {}
+        entries, temps, seeds, counters = [], [], [], []
+        for row in plan.rows:
+            request = row.request
+            tokens = request.tokens()[row.start:row.start + row.count]
+            entries.append(StepEntry(request.request_id, tokens, [row.count - 1] if row.sample else []))
+            if row.sample:
+                temps.append(request.temperature)
+                seeds.append(request.seed)
+                counters.append(len(request.generated))
+        runner = self.runner
+        arrays = sampling_arrays(temps, seeds, counters)
+        extras = None if arrays is None else {"temperature": arrays[0], "seeds": arrays[1], "counters": arrays[2]}
+        ctx = runner.prepare(entries, extras=extras)
+        logits = runner.run(ctx)
+        sampled: List[Optional[int]] = [None] * len(plan.rows)
+        count = len(temps)
+        if logits is not None:
+            ex = ctx.extras
+            sample_rows(logits, ex.get("temperature"), ex.get("seeds"), ex.get("counters"),
+                        out=runner.result[1:1 + count])
+        runner.result_host[:1 + count].copy_(runner.result[:1 + count], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host = runner.result_host[:1 + count].tolist()
+        if host[0]:
+            runner.status.zero_()
+            raise DeviceFault("device reported: " + "; ".join(t for b, t in _FAULTS.items() if host[0] & b))
+        it = iter(host[1:])
+        for i, row in enumerate(plan.rows):
+            if row.sample:
+                sampled[i] = next(it)
+        for e in entries:
+            runner.cache.trim(e.request_id)
+        emitted = self.scheduler.commit(plan, sampled)
+        self._trace(plan, emitted)
+        return emitted
+
+    def _trace(self, plan: StepPlan, emitted: Dict[object, int]) -> None:
+        """One JSON line per step, as the reference's VOSTI_ENGINE_STEP_TRACE
+        (examples/support/engine_benchmark.rs:273-317)."""
+        if self.step_trace is None:
+            return
+        self.step_trace.write(json.dumps({
+            "step": self.step_index,
+            "scheduled": [[str(r.request.request_id), r.start, r.count, r.sample] for r in plan.rows],
+            "emitted": {str(k): v for k, v in emitted.items()},
+            "preempted": [str(r) for r in plan.preempted], "dropped": [str(r) for r in plan.dropped],
+            "free_pages": self.runner.cache.available_pages(),
+        }) + "\n")
+        self.step_trace.flush()
+
+    # ------------------------------------------------------------ convenience
+    def generate(self, prompts: Iterable[Sequence[int]], max_tokens: int = 8,
+                 eos_token_ids: Optional[Sequence[int]] = None, ignore_eos: bool = False,
+                 temperature: float = 0.0, seeds: Optional[Sequence[int]] = None,
+                 arrival_steps: Optional[Sequence[int]] = None, first_id: Optional[int] = None) -> List[List[int]]:
+        """Generate for token-id prompts and return the new tokens of each, in order.
+        `arrival_steps[i]` delays prompt i until that many engine steps have passed."""
+        prompts = list(prompts)
+        base = first_id if first_id is not None else len(self.scheduler.accepted_ids)
+        ids = [base + i for i in range(len(prompts))]
+        pending = sorted(range(len(prompts)), key=lambda i: (arrival_steps[i] if arrival_steps else 0, i))
+        outputs: Dict[object, List[int]] = {rid: [] for rid in ids}
+        step = 0
+        while pending or self.has_unfinished():
+            while pending and (not arrival_steps or arrival_steps[pending[0]] <= step):
+                i = pending.pop(0)
+                status = self.add_request(ids[i], prompts[i], max_tokens, eos_token_ids, ignore_eos,
+                                          temperature, seeds[i] if seeds else 0)
+                if status is not AdmissionStatus.ACCEPTED:
+                    raise ValueError(f"prompt {i} was not accepted: {status.value}")
+            for rid, token in self.step().items():
+                if rid in outputs:
+                    outputs[rid].append(token)
+            step += 1
+        return [outputs[rid] for rid in ids]
+
+    def cache_stats(self) -> dict:
+        cache = self.runner.cache
+        return {"admitted_requests": self.scheduler.admitted_requests,
+                "requests_with_reuse": cache.requests_with_reuse,
+                "reused_prefix_blocks": cache.reused_prefix_pages,
+                "preemptions": self.scheduler.preemptions}

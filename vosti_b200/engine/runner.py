@@ -88,7 +88,7 @@ class ModelRunner:
         self.cache.finish(request_id)
 
     # ------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    def prepare(self, entries: Sequence[StepEntry], extras: Optional[dict] = None) -> StepContext:
         """Reserve cache entries for the step's tokens (all requests or none) and copy the
         batch to the device."""
         cache = self.cache
@@ -122,7 +122,7 @@ class ModelRunner:
         block_rows = [[cache.block_row(e.request_id, g) for e in entries] for g in range(G)]
         state_slots = [cache.slot(e.request_id) for e in entries]
         return build_context(self.staging, entries, starts, slots_per_group, block_rows, state_slots,
-                             cache.page_size, self.status, self.dtype)
+                             cache.page_size, self.status, self.dtype, extras=extras)
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """The model over the prepared batch; float32 logits [wanted, vocab] or None."""

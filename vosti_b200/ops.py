@@ -174,12 +174,16 @@ def attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
-           seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Tokens (int32[rows]) from float32 logits [rows, vocab]."""
+           seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tokens (int32[rows]) from float32 logits [rows, vocab], written to `out` if given."""
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 [rows, vocab] with unit inner stride")
     _contig(temperature, seeds, counters)
-    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    elif out.dtype != torch.int32 or out.numel() < logits.shape[0] or not out.is_contiguous():
+        raise KernelError("sample: out must be a contiguous int32 tensor with a slot per row")
     _check(library().vosti_sample(_p(logits), logits.shape[0], logits.shape[1],
                                   ctypes.c_int64(logits.stride(0)), _p(temperature), _p(seeds),
                                   _p(counters), _p(out), _stream()), "sample")

@@ -46,7 +46,7 @@ class SafetensorsFile:
                 header = json.loads(handle.read(length))
             except (json.JSONDecodeError, UnicodeDecodeError) as error:
                 raise SafetensorsError(f"{self.path}: header is not JSON: {error}") from error
-            self._map = mmap.mmap(handle.fileno(), 0, access=mmap.ACCESS_READ)
+            self._map = mmap.mmap(handle.fileno(), 0, access=mmap.ACCESS_COPY)
         self._base = 8 + length
         self.metadata = header.pop("__metadata__", {})
         self.entries: Dict[str, Tuple[str, Tuple[int, ...], int, int]] = {}
