@@ -1,0 +1,273 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 reference of the same
+operation, at sizes other than the engine's tiny models (widths and vocabularies that are
+no power of two, head sizes in steps of 16, any number of heads and groups)."""
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from vosti_b200 import ops
+    device = torch.device("cuda:0")
+    ops.require_device(device)
+    return device
+
+
+@pytest.fixture()
+def status(dev):
+    return torch.zeros(1, dtype=torch.int32, device=dev)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(80, 331), (7, 19), (4096, 1000)])
+def test_embedding(dev, status, dtype, hidden, vocab):
+    from vosti_b200 import ops
+    table = torch.randn(vocab, hidden, device=dev).to(dtype)
+    ids = torch.randint(0, vocab, (37,), device=dev, dtype=torch.int32)
+    out = ops.embedding(ids, table, status)
+    assert torch.equal(out, table[ids.long()]) and status.item() == 0
+    bad = ids.clone()
+    bad[3] = vocab
+    out = ops.embedding(bad, table, status)
+    assert status.item() == 1 and out[3].abs().max() == 0        # reported, not read
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [80, 96, 1000, 4096 + 24])
+@pytest.mark.parametrize("weight_f32", [False, True])
+def test_rmsnorm(dev, dtype, width, weight_f32):
+    from vosti_b200 import ops
+    x = (torch.randn(11, width, device=dev) * 3).to(dtype)
+    r = torch.randn(11, width, device=dev).to(dtype)
+    w = (1 + 0.1 * torch.randn(width, device=dev)).to(torch.float32 if weight_f32 else dtype)
+    eps = 3e-5
+    out, _ = ops.rmsnorm(x, w, eps)
+    want = plain.rms_norm(x.float().cpu(), w.float().cpu(), eps)
+    assert torch.allclose(out.float().cpu(), want, **tol(dtype))
+    res = r.clone()
+    out, new_res = ops.rmsnorm(x, w, eps, residual=res, residual_out=res)
+    want_n, want_r = plain.add_rms_norm(x.float().cpu(), r.float().cpu(), w.float().cpu(), eps)
+    assert new_res is res
+    assert torch.allclose(res.float().cpu(), want_r, **tol(dtype))
+    assert torch.allclose(out.float().cpu(), want_n, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dev, dtype):
+    from vosti_b200 import ops
+    gu = (torch.randn(13, 2 * 200, device=dev) * 4).to(dtype)
+    out = ops.silu_mul(gu)
+    g, u = gu.float()[:, :200], gu.float()[:, 200:]
+    assert torch.allclose(out.float(), (g * torch.sigmoid(g) * u).to(dtype).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("xdt,wdt,ydt", [(torch.float32, torch.float32, torch.float32),
+                                         (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                         (torch.bfloat16, torch.bfloat16, torch.float32),
+                                         (torch.bfloat16, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("rows,n,k", [(1, 331, 80), (37, 200, 96), (130, 67, 1000), (5, 1, 3)])
+def test_gemm_simt(dev, status, xdt, wdt, ydt, rows, n, k):
+    from vosti_b200 import ops
+    x = torch.randn(rows, k, device=dev).to(xdt)
+    w = (torch.randn(n, k, device=dev) / math.sqrt(k)).to(wdt)
+    y = ops.gemm_simt(x, w, status, out_dtype=ydt)
+    want = x.double() @ w.double().T
+    assert y.dtype == ydt and torch.allclose(y.double(), want, **tol(ydt))
+    index = torch.randint(0, rows, (9,), device=dev, dtype=torch.int32)
+    y = ops.gemm_simt(x, w, status, out_dtype=ydt, row_index=index)
+    assert torch.allclose(y.double(), want[index.long()], **tol(ydt)) and status.item() == 0
+
+
+def test_gemm_simt_is_true_float32_and_row_independent(dev, status):
+    """No reduced-precision matrix mode: values that TF32 would round survive; and a row's
+    result does not depend on the other rows of the launch."""
+    from vosti_b200 import ops
+    k = 64
+    x = torch.zeros(3, k, device=dev)
+    x[:, 0] = 1.0 + 2.0 ** -20                                   # needs more than 10 mantissa bits
+    w = torch.zeros(2, k, device=dev)
+    w[:, 0] = 1.0
+    y = ops.gemm_simt(x, w, status)
+    assert y[0, 0].item() == 1.0 + 2.0 ** -20
+    a = torch.randn(70, 300, device=dev)
+    b = torch.randn(130, 300, device=dev)
+    full = ops.gemm_simt(a, b, status)
+    for r in (0, 33, 69):
+        assert torch.equal(ops.gemm_simt(a[r:r + 1].contiguous(), b, status)[0], full[r])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,use_norm,use_rope", [(6, 3, 48, True, True), (4, 4, 16, False, True),
+                                                         (5, 1, 128, True, False), (8, 2, 256, True, True)])
+def test_qkv_post(dev, status, dtype, nq, nkv, d, use_norm, use_rope):
+    from vosti_b200 import ops
+    T, slots_total, eps, theta = 19, 64, 2e-6, 50000.0
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev).to(dtype)
+    qw = (1 + 0.1 * torch.randn(d, device=dev)).to(dtype) if use_norm else None
+    kw = (1 + 0.1 * torch.randn(d, device=dev)).to(dtype) if use_norm else None
+    positions = torch.randint(0, 500, (T,), device=dev, dtype=torch.int32)
+    cos = sin = None
+    if use_rope:
+        c, s = plain.rope_tables(torch.arange(500), d, theta)
+        cos, sin = c.to(dev).contiguous(), s.to(dev).contiguous()
+    slots = torch.randperm(slots_total, device=dev)[:T].to(torch.int32)
+    slots[4] = -1                                               # a skipped row
+    k_cache = torch.full((slots_total, nkv, d), float("nan"), device=dev).to(dtype)
+    v_cache = torch.full((slots_total, nkv, d), float("nan"), device=dev).to(dtype)
+    q = ops.qkv_post(qkv, k_cache, v_cache, nq=nq, nkv=nkv, head_dim=d, q_norm_w=qw, k_norm_w=kw, eps=eps,
+                     cos=cos, sin=sin, positions=positions, slot_mapping=slots, status=status)
+    f = qkv.float().cpu()
+    qr = f[:, :nq * d].view(T, nq, d)
+    kr = f[:, nq * d:(nq + nkv) * d].view(T, nkv, d)
+    vr = f[:, (nq + nkv) * d:].view(T, nkv, d)
+    if use_norm:
+        qr, kr = plain.head_rms_norm(qr, qw.float().cpu(), eps), plain.head_rms_norm(kr, kw.float().cpu(), eps)
+    if use_rope:
+        c, s = plain.rope_tables(positions.cpu(), d, theta)
+        qr, kr = plain.apply_rope(qr, c, s), plain.apply_rope(kr, c, s)
+    assert torch.allclose(q.float().cpu().view(T, nq, d), qr, **tol(dtype))
+    keep = [t for t in range(T) if t != 4]
+    sl = slots.long().cpu()[keep]
+    assert torch.allclose(k_cache.float().cpu()[sl], kr[keep], **tol(dtype))
+    assert torch.equal(v_cache.float().cpu()[sl], vr[keep].to(dtype).float())
+    untouched = torch.ones(slots_total, dtype=torch.bool)
+    untouched[sl] = False
+    assert torch.isnan(k_cache.float().cpu()[untouched]).all()  # nothing else was written
+    assert status.item() == 0
+    slots[0] = slots_total
+    ops.qkv_post(qkv, k_cache, v_cache, nq=nq, nkv=nkv, head_dim=d, q_norm_w=qw, k_norm_w=kw, eps=eps,
+                 cos=cos, sin=sin, positions=positions, slot_mapping=slots, status=status)
+    assert status.item() & 2
+
+
+def paged_case(dev, dtype, lens_q, lens_k, nq, nkv, d, page, poison=True, seed=0):
+    """Random requests with their keys scattered over shuffled pages; unused cache is NaN."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens_q)
+    pages_of = [(k + page - 1) // page for k in lens_k]
+    num_pages = sum(pages_of) + 3
+    order = torch.randperm(num_pages, generator=g).tolist()
+    fill = float("nan") if poison else 0.0
+    k_cache = torch.full((num_pages * page, nkv, d), fill)
+    v_cache = torch.full((num_pages * page, nkv, d), fill)
+    max_pages = max(pages_of)
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    ks, vs, qs, positions, request_of = [], [], [], [], []
+    for b in range(B):
+        mine = [order.pop() for _ in range(pages_of[b])]
+        table[b, :len(mine)] = torch.tensor(mine, dtype=torch.int32)
+        k = torch.randn(lens_k[b], nkv, d, generator=g).to(dtype).float()
+        v = torch.randn(lens_k[b], nkv, d, generator=g).to(dtype).float()
+        for j in range(lens_k[b]):
+            slot = mine[j // page] * page + j % page
+            k_cache[slot], v_cache[slot] = k[j], v[j]
+        ks.append(k), vs.append(v)
+        qs.append(torch.randn(lens_q[b], nq, d, generator=g).to(dtype).float())
+        positions += list(range(lens_k[b] - lens_q[b], lens_k[b]))
+        request_of += [b] * lens_q[b]
+    return dict(q=torch.cat(qs), ks=ks, vs=vs, qs=qs, k_cache=k_cache, v_cache=v_cache, table=table,
+                positions=torch.tensor(positions, dtype=torch.int32),
+                request_of=torch.tensor(request_of, dtype=torch.int32), page=page)
+
+
+def reference_attention(case, scale, window):
+    outs = []
+    for q, k, v in zip(case["qs"], case["ks"], case["vs"]):
+        L, n = k.shape[0], q.shape[0]
+        full_q = torch.zeros(L, q.shape[1], q.shape[2])
+        full_q[L - n:] = q
+        outs.append(plain.causal_attention(full_q, k, v, scale, window=window)[L - n:])
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(6, 3, 48, 16, 0), (4, 1, 16, 8, 0), (8, 8, 128, 16, 0),
+                                                   (6, 2, 80, 4, 13), (2, 1, 256, 64, 0), (4, 2, 32, 8, 40)])
+def test_attention_simt(dev, status, dtype, nq, nkv, d, page, window):
+    from vosti_b200 import ops
+    lens_k = [1, 33, 64, 130, 17, 95]
+    lens_q = [1, 33, 1, 7, 2, 1]
+    case = paged_case(dev, dtype, lens_q, lens_k, nq, nkv, d, page)
+    scale = 0.37 * d ** -0.5
+    out = ops.attention_simt(case["q"].to(dev, dtype), case["k_cache"].to(dev, dtype), case["v_cache"].to(dev, dtype),
+                             positions=case["positions"].to(dev), request_of=case["request_of"].to(dev),
+                             block_table=case["table"].to(dev), page_size=page, nq=nq, nkv=nkv, head_dim=d,
+                             scale=scale, window=window, status=status)
+    want = reference_attention(case, scale, window)
+    assert torch.isfinite(out).all(), "a masked or unused (NaN) cache entry was read"
+    assert torch.allclose(out.float().cpu(), want, **tol(dtype)) and status.item() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dev, status, dtype):
+    """One key among hundreds is made to stand out (query and key scaled); the output must be
+    that key's value. Placed at a page's first and last slot and at the window's edge."""
+    from vosti_b200 import ops
+    nq, nkv, d, page = 2, 1, 32, 16
+    for L, far, window in [(400, 0, 0), (400, 15, 0), (400, 16, 0), (400, 383, 0), (400, 399, 0),
+                           (400, 300, 100), (400, 299, 100)]:
+        case = paged_case(dev, dtype, [1], [L], nq, nkv, d, page, seed=L + far)
+        direction = torch.nn.functional.normalize(torch.randn(d), dim=0)
+        case["q"][0, :, :] = 40.0 * direction
+        slot = int(case["table"][0, far // page]) * page + far % page
+        case["k_cache"][slot, 0] = (40.0 * direction).to(dtype).float()
+        marker = torch.full((d,), 3.0)
+        case["v_cache"][slot, 0] = marker
+        out = ops.attention_simt(case["q"].to(dev, dtype), case["k_cache"].to(dev, dtype),
+                                 case["v_cache"].to(dev, dtype), positions=case["positions"].to(dev),
+                                 request_of=case["request_of"].to(dev), block_table=case["table"].to(dev),
+                                 page_size=page, nq=nq, nkv=nkv, head_dim=d, scale=1.0, window=window, status=status)
+        visible = window == 0 or far > L - 1 - window
+        if visible:
+            assert torch.allclose(out.float().cpu()[0], marker.expand(nq, d), atol=2e-2), (L, far, window)
+        else:
+            assert (out.float().cpu()[0] - 3.0).abs().min() > 0.5, (L, far, window)
+
+
+def test_attention_refuses_sizes_it_cannot_do(dev, status):
+    from vosti_b200 import ops
+    q = torch.zeros(1, 2 * 24, device=dev)
+    cache = torch.zeros(16, 1, 24, device=dev)
+    with pytest.raises(ops.KernelError, match="multiple of 16"):
+        ops.attention_simt(q, cache, cache, positions=torch.zeros(1, dtype=torch.int32, device=dev),
+                           request_of=torch.zeros(1, dtype=torch.int32, device=dev),
+                           block_table=torch.zeros(1, 1, dtype=torch.int32, device=dev), page_size=16, nq=2,
+                           nkv=1, head_dim=24, scale=1.0, window=0, status=status)
+
+
+def test_sampling(dev):
+    from vosti_b200 import ops
+    vocab = 1531
+    logits = torch.randn(6, vocab, device=dev) * 2
+    logits[1, 700] = logits[1, 20] = 50.0                        # a tie: the lowest index wins
+    assert ops.sample(logits).tolist() == [int(torch.argmax(r)) if i != 1 else 20 for i, r in enumerate(logits.cpu())]
+    temps = torch.tensor([0.0, 0.0, 0.7, 1.0, 1.3, 0.7], device=dev)
+    hits = 0
+    for index in range(40):
+        seeds = torch.tensor([3, 3, 5, 2 ** 40 + 7, 11, 6], dtype=torch.int64, device=dev)
+        counters = torch.full((6,), index, dtype=torch.int64, device=dev)
+        got = ops.sample(logits, temps, seeds, counters).tolist()
+        assert got[0] == int(torch.argmax(logits[0])) and got[1] == 20
+        for row in range(2, 6):
+            t = float(temps[row])
+            w = torch.exp((logits[row].double().cpu() - logits[row].double().cpu().max()) / t)
+            cdf = torch.cumsum(w, 0)
+            u = plain.uniform(int(seeds[row]), index) * float(cdf[-1])
+            low = float(cdf[got[row] - 1]) if got[row] > 0 else 0.0
+            slack = 1e-5 * float(cdf[-1])
+            assert low - slack <= u <= float(cdf[got[row]]) + slack, (row, index)
+            hits += got[row] == plain.sample(logits[row].cpu(), t, int(seeds[row]), index)
+    assert hits >= 155                                           # equal to the plain sampler but for rounding at an edge
+    assert ops.sample(logits, temps, seeds, counters).tolist() == got      # same state, same token
