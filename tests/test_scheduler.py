@@ -220,3 +220,16 @@ def test_random_workloads_finish_with_every_token(seed):
     for rid, n in want.items():
         assert sched.finished[rid].generated == list(range(n))
     assert cache.available_pages() == total_pages and not cache.live
+
+
+def test_abort_gives_everything_back():
+    cache, sched = make(num_pages=16)
+    sched.add_request(Request(0, [1] * 9, 5, ignore_eos=True))
+    sched.add_request(Request(1, [2] * 9, 5, ignore_eos=True))
+    run_step(cache, sched)
+    assert sched.abort(0) and not sched.abort(0) and not sched.abort(77)
+    assert [r.request_id for r in sched.running] == [1] and sched.finished[0].finish_reason == "aborted"
+    cache.check()
+    while sched.has_unfinished():
+        run_step(cache, sched)
+    assert cache.available_pages() == 16

@@ -70,6 +70,7 @@ class StagingBuffer:
     def __init__(self, device: torch.device, capacity: int = 1 << 16):
         self.device = device
         self.copied = None          # event after the last host-to-device copy
+        self.last_upload_bytes = 0
         self._alloc(capacity)
 
     def _alloc(self, capacity: int) -> None:
@@ -89,6 +90,7 @@ class StagingBuffer:
 
     def upload(self, count: int) -> None:
         self.dev[:count].copy_(self.host[:count], non_blocking=True)
+        self.last_upload_bytes = 4 * count
         if self.copied is None:
             self.copied = torch.cuda.Event()
         self.copied.record()

@@ -60,6 +60,10 @@ class Engine:
                           tuple(int(t) for t in eos_token_ids), bool(ignore_eos), float(temperature), int(seed))
         return self.scheduler.add_request(request)
 
+    def abort(self, request_id) -> bool:
+        """End a queued or running request between steps; its pages and slot come back."""
+        return self.scheduler.abort(request_id)
+
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
 

@@ -100,6 +100,19 @@ class Scheduler:
         self.waiting.append(request)
         return AdmissionStatus.ACCEPTED
 
+    def abort(self, request_id) -> bool:
+        """End a request now: it leaves its queue and gives back what it holds."""
+        for queue in (self.waiting, self.running):
+            for request in queue:
+                if request.request_id == request_id:
+                    queue.remove(request)
+                    if request_id in self.cache.live:
+                        self.cache.finish(request_id)
+                    request.finished, request.finish_reason = True, "aborted"
+                    self.finished[request_id] = request
+                    return True
+        return False
+
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
 

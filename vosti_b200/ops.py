@@ -47,7 +47,12 @@ def require_device(device: torch.device) -> None:
     _CHECKED_DEVICES.add(index)
 
 
-def _check(code: int, what: str) -> None:
+LAUNCHES = 0   # kernels of this library launched so far (counted per launcher call)
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += kernels
     if code != 0:
         raise KernelError(f"{what}: {library().vosti_last_error().decode()} (code {code})")
 
