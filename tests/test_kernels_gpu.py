@@ -271,3 +271,59 @@ def test_sampling(dev):
             hits += got[row] == plain.sample(logits[row].cpu(), t, int(seeds[row]), index)
     assert hits >= 155                                           # equal to the plain sampler but for rounding at an edge
     assert ops.sample(logits, temps, seeds, counters).tolist() == got      # same state, same token
+
+
+# ---------------------------------------------------------------- tensor-core product
+@pytest.mark.parametrize("tokens", [1, 7, 33, 64, 100, 129, 300, 1100])
+@pytest.mark.parametrize("features,k", [(64, 64), (200, 80), (331, 96), (4096, 1000), (1536, 4096), (152, 12288)])
+def test_gemm_tc(dev, status, tokens, features, k):
+    from vosti_b200 import ops
+    assert ops.gemm_tc_supported(features, k)
+    x = torch.randn(tokens, k, device=dev).bfloat16()
+    w = (torch.randn(features, k, device=dev) / math.sqrt(k)).bfloat16()
+    want = x.double() @ w.double().T
+    y32 = ops.gemm_tc(x, w, status, out_dtype=torch.float32)
+    assert torch.allclose(y32.double(), want, atol=2e-4, rtol=2e-4), (y32.double() - want).abs().max()
+    y16 = ops.gemm_tc(x, w, status)
+    assert y16.dtype == torch.bfloat16 and torch.allclose(y16.double(), want, atol=2e-2, rtol=2e-2)
+    assert torch.equal(y16, y32.bfloat16())                       # one rounding, at the store
+    assert status.item() == 0
+
+
+def test_gemm_tc_refuses_what_it_cannot_do(dev, status):
+    from vosti_b200 import ops
+    assert not ops.gemm_tc_supported(64, 48) and not ops.gemm_tc_supported(64, 100)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tc(torch.zeros(4, 100, device=dev).bfloat16(), torch.zeros(8, 100, device=dev).bfloat16(), status)
+
+
+@pytest.mark.parametrize("tokens", [3, 70, 400])
+@pytest.mark.parametrize("inter,k", [(128, 64), (208, 96), (12288 // 8, 4096)])
+def test_gemm_tc_fused_silu_mul(dev, status, tokens, inter, k):
+    """SiLU(gate)*up in the epilogue, with the weight rows in blocks of 16 gate and 16 up
+    rows, against the unfused order of operations."""
+    from vosti_b200 import ops
+    x = torch.randn(tokens, k, device=dev).bfloat16()
+    gate = (torch.randn(inter, k, device=dev) / math.sqrt(k)).bfloat16()
+    up = (torch.randn(inter, k, device=dev) / math.sqrt(k)).bfloat16()
+    blocks = torch.stack([gate.view(-1, 16, k), up.view(-1, 16, k)], dim=1).reshape(2 * inter, k).contiguous()
+    y = ops.gemm_tc(x, blocks, status, swiglu=True)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = g * torch.sigmoid(g) * u
+    assert y.shape == (tokens, inter) and torch.allclose(y.double(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_gemm_tc_rows_do_not_depend_on_their_companions(dev, status):
+    """Within one tile size and split count a row's bits do not depend on the other rows."""
+    from vosti_b200 import ops
+    k, features = 4096, 1024
+    x = torch.randn(24, k, device=dev).bfloat16()
+    w = (torch.randn(features, k, device=dev) / 64).bfloat16()
+    full = ops.gemm_tc(x, w, status, out_dtype=torch.float32)
+    for r in (0, 11, 23):
+        alone = ops.gemm_tc(x[r:r + 1].contiguous(), w, status, out_dtype=torch.float32)
+        assert torch.equal(alone[0], full[r])
+    big = torch.randn(700, k, device=dev).bfloat16()
+    full = ops.gemm_tc(big, w, status, out_dtype=torch.float32)
+    part = ops.gemm_tc(big[300:600].contiguous(), w, status, out_dtype=torch.float32)
+    assert torch.equal(part, full[300:600])

@@ -1,0 +1,426 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), operands staged
+// in shared memory by TMA, accumulator in tensor memory:
+//   Y[t, f] = sum_k X[t, k] * W[f, k]          X: [T, K], W: [F, K] (both K-major), no bias
+// Output features fill the MMA's M = 128 (one accumulator lane per feature), tokens are
+// the N side (32..256 per tile), so a decode step of a few tokens still uses whole
+// instructions and the operand roles are the same for prefill and decode.
+//
+// One CTA computes one 128 x BN tile (one K split of it): warp 0 issues the TMA loads,
+// warp 1 allocates tensor memory and issues the MMAs, warps 2..5 read the accumulator
+// back (tcgen05.ld) and store. Every wait on an mbarrier is bounded: after about a second
+// it sets the fault bit VOSTI_FAULT_WAIT_TIMEOUT, the CTA stops issuing work, frees its
+// tensor memory and returns.
+//
+// The reference's matmul is a Triton kernel with float32 accumulation and no split-K
+// (kernels/triton_kernels/matmul.py:95-147); its SiLU(gate)*up is a second kernel
+// (silu_mul.py:66-87), fused here into the epilogue.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;           // features per tile (MMA M)
+constexpr int BK = 64;            // k elements per stage: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int THREADS = 192;
+
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~2e9 cycles or when another role of the CTA gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned* status) {
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - start > 2000000000LL) {
+      *abort_flag = 1;
+      raise_fault(status, VOSTI_FAULT_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols));
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
+// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                           // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                           // descriptor version
+  d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
+
+// ------------------------------------------------------------------ the kernel
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               void* __restrict__ out, int tokens, int features, int k_blocks, int ld_out, int epilogue,
+               unsigned* status) {
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the 128-byte swizzle pattern
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int splits = gridDim.z, split = blockIdx.z;
+  const int kb_begin = (int)((long long)k_blocks * split / splits);
+  const int kb_end = (int)((long long)k_blocks * (split + 1) / splits);
+  const int my_blocks = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_holder), BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < my_blocks; ++i) {
+        const int s = i % STAGES;
+        const uint32_t round = i / STAGES;
+        if (i >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, &abort_flag, status)) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
+        const int k0 = (kb_begin + i) * BK;          // multiple of 64 elements: 16-byte aligned
+        tma_load_2d(a_dst, &map_w, k0, m0, bar);
+        tma_load_2d(a_dst + A_BYTES, &map_x, k0, n0, bar);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      bool ok = true;
+      for (int i = 0; i < my_blocks && ok; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1, &abort_flag, status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // 16 elements further along K: 32 bytes, 2 in the descriptor's 16-byte units
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(smem_u32(&accum_bar));  // the accumulator is complete
+    }
+  } else {
+    // epilogue: this warp may read the 32 accumulator lanes of its quarter only
+    const int quarter = warp & 3;
+    bool ok = my_blocks > 0 ? mbar_wait(smem_u32(&accum_bar), 0, &abort_flag, status) : true;
+    tc_fence_after();
+    const int feature = m0 + quarter * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= tokens) break;                 // uniform across the warp
+        uint32_t r[32];
+        if (my_blocks > 0) {
+          tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (epilogue == EPI_SWIGLU) {
+          // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows
+          bf16* y = reinterpret_cast<bf16*>(out);
+          const int out_feature = (m0 + quarter * 32) / 2 + (lane & 15);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float mine = __uint_as_float(r[j]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+            const int t = n0 + c0 + j;
+            if (lane < 16 && t < tokens && out_feature < ld_out)
+              y[(int64_t)t * ld_out + out_feature] = __float2bfloat16_rn(silu(mine) * other);
+          }
+        } else if (feature < features) {
+          if (epilogue == EPI_BF16) {
+            bf16* y = reinterpret_cast<bf16*>(out);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int t = n0 + c0 + j;
+              if (t < tokens) y[(int64_t)t * ld_out + feature] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          } else {  // EPI_F32, or EPI_PARTIAL into this split's slice
+            float* y = reinterpret_cast<float*>(out) + (epilogue == EPI_PARTIAL ? (int64_t)split * tokens * ld_out : 0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int t = n0 + c0 + j;
+              if (t < tokens) y[(int64_t)t * ld_out + feature] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    // leave time for copies that are still in flight to land before the CTA's memory goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, BN);
+  }
+}
+
+// Sum the K splits in split order and apply the epilogue.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int splits,
+                                     int tokens, int features, int ld_out, int epilogue) {
+  const int64_t plane = (int64_t)tokens * features;
+  if (epilogue == EPI_SWIGLU) {
+    const int64_t n = (int64_t)tokens * (features / 2);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t t = i / (features / 2);
+      const int f = (int)(i % (features / 2));
+      const int row_g = (f / 16) * 32 + (f % 16), row_u = row_g + 16;
+      float g = 0.f, u = 0.f;
+      for (int s = 0; s < splits; ++s) {
+        g += partial[s * plane + t * features + row_g];
+        u += partial[s * plane + t * features + row_u];
+      }
+      reinterpret_cast<bf16*>(out)[t * ld_out + f] = __float2bfloat16_rn(silu(g) * u);
+    }
+    return;
+  }
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (int64_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[s * plane + i];
+    const int64_t t = i / features;
+    const int f = (int)(i % features);
+    if (epilogue == EPI_F32)
+      reinterpret_cast<float*>(out)[t * ld_out + f] = acc;
+    else
+      reinterpret_cast<bf16*>(out)[t * ld_out + f] = __float2bfloat16_rn(acc);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Map of a row-major [rows, k] bfloat16 matrix, box [box_rows, 64], 128-byte swizzle; what
+// lies outside the matrix reads as zero.
+bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct WeightKey {
+  const void* p;
+  int rows, k;
+  bool operator==(const WeightKey& o) const { return p == o.p && rows == o.rows && k == o.k; }
+};
+struct WeightKeyHash {
+  size_t operator()(const WeightKey& key) const {
+    return std::hash<const void*>()(key.p) ^ ((size_t)key.rows * 1000003u) ^ ((size_t)key.k << 20);
+  }
+};
+
+bool weight_map(const void* w, int rows, int k, CUtensorMap* out) {
+  static std::unordered_map<WeightKey, CUtensorMap, WeightKeyHash> cache;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  WeightKey key{w, rows, k};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  if (cache.size() > 4096) cache.clear();
+  if (!make_map(out, w, rows, k, BM)) return false;
+  cache.emplace(key, *out);
+  return true;
+}
+
+int token_tile(int tokens) { return tokens <= 32 ? 32 : tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256; }
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int k_blocks, int ld_out,
+           int epilogue, int splits, unsigned* status, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      vosti_set_error("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = true;
+  }
+  dim3 grid((features + BM - 1) / BM, (tokens + BN - 1) / BN, splits);
+  gemm_tc_kernel<BN, STAGES><<<grid, THREADS, smem, stream>>>(mw, mx, out, tokens, features, k_blocks, ld_out, epilogue, status);
+  return 0;
+}
+
+}  // namespace
+
+// Whether the tensor-core product takes a [features, k] bfloat16 weight at all.
+VOSTI_API int vosti_gemm_tc_supported(int features, int k) { return features >= 1 && k >= BK && k % 8 == 0; }
+
+// How many K splits a product of these sizes uses (a function of the sizes only; the
+// sum over splits is taken in split order). More than one split needs a float32 workspace
+// of splits * tokens * features elements.
+VOSTI_API int vosti_gemm_tc_splits(int tokens, int features, int k) {
+  const int k_blocks = (k + BK - 1) / BK;
+  const int tiles = ((features + BM - 1) / BM) * ((tokens + token_tile(tokens) - 1) / token_tile(tokens));
+  if (tokens > 128 || tiles >= 96) return 1;
+  int splits = (148 + tiles - 1) / tiles;
+  if (splits > k_blocks / 8) splits = k_blocks / 8;   // at least 8 k-blocks (512 elements) per split
+  if (splits > 16) splits = 16;
+  return splits < 1 ? 1 : splits;
+}
+
+// x: [tokens, k] bf16; w: [features, k] bf16; epilogue 0: y bf16 [tokens, features];
+// 1: y float32 [tokens, features]; 2: y bf16 [tokens, features / 2] = silu(gate) * up with
+// the weight rows interleaved in blocks of 16 gate rows and their 16 up rows.
+VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, int features, int k, int epilogue,
+                            float* workspace, int64_t workspace_elems, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(tokens >= 0 && vosti_gemm_tc_supported(features, k), "gemm_tc: unsupported sizes F=%d K=%d", features, k);
+  VOSTI_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "gemm_tc: unknown epilogue %d", epilogue);
+  VOSTI_REQUIRE(epilogue != EPI_SWIGLU || features % 32 == 0, "gemm_tc: fused SiLU*up needs features %% 32 == 0");
+  VOSTI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+  if (tokens == 0) return VOSTI_OK;
+  const int ld_out = epilogue == EPI_SWIGLU ? features / 2 : features;
+  const int k_blocks = (k + BK - 1) / BK;
+  const int splits = vosti_gemm_tc_splits(tokens, features, k);
+  VOSTI_REQUIRE(splits == 1 || (workspace != nullptr && workspace_elems >= (int64_t)splits * tokens * features),
+                "gemm_tc: workspace too small for %d splits", splits);
+  CUtensorMap mw_storage, mx;
+  const CUtensorMap* mw = &mw_storage;
+  const int bn = token_tile(tokens);
+  VOSTI_REQUIRE(weight_map(w, features, k, &mw_storage) && make_map(&mx, x, tokens, k, bn),
+                "gemm_tc: cuTensorMapEncodeTiled failed");
+  void* dst = splits > 1 ? (void*)workspace : y;
+  const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
+  const int ld = splits > 1 ? features : ld_out;
+  int rc;
+  switch (bn) {
+    case 32: rc = launch<32, 5>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
+    case 64: rc = launch<64, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
+    case 128: rc = launch<128, 6>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
+    default: rc = launch<256, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
+  }
+  if (rc != 0) return rc;
+  if (splits > 1) {
+    const int64_t n = (int64_t)tokens * features;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(workspace, y, splits, tokens, features, ld_out, epilogue);
+  }
+  VOSTI_LAUNCH_CHECK();
+}

@@ -126,11 +126,11 @@ class ModelRunner:
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """The model over the prepared batch; float32 logits [wanted, vocab] or None."""
-        final = self.model.forward(ctx, self.cache.layer_caches)
+        hidden, residual = self.model.forward(ctx, self.cache.layer_caches)
         self.steps += 1
         if ctx.want_rows.shape[0] == 0:
             return None
-        return self.model.logits(ctx, final, ctx.want_rows)
+        return self.model.logits(ctx, hidden, residual, ctx.want_rows)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         ctx = self.prepare(entries)

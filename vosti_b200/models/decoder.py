@@ -87,19 +87,23 @@ class DecoderModel:
         return total
 
     # ------------------------------------------------------------ forward
-    def forward(self, ctx, layer_caches: List) -> torch.Tensor:
-        """Run every entry of the run order over the batch in `ctx`; returns the normed
-        final hidden rows [T, hidden]."""
+    def forward(self, ctx, layer_caches: List):
+        """Run every entry of the run order over the batch in `ctx`; returns the last
+        block's (hidden, residual), both [T, hidden] (residual None without blocks)."""
         hidden = ops.embedding(ctx.tokens, self.embed, ctx.status)
         residual: Optional[torch.Tensor] = None
         for entry in self.spec.run_order:
             owner = entry.layer if entry.cache_from is None else entry.cache_from
             hidden, residual = self.blocks[entry.layer].forward(
                 ctx, hidden, residual, layer_caches[owner], writes_cache=entry.cache_from is None)
-        if residual is None:
-            return self.final_norm.forward(ctx, hidden)
-        return self.final_norm.forward_add(ctx, hidden, residual)[0]
+        return hidden, residual
 
-    def logits(self, ctx, final: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-        """float32 logits [len(rows), vocab] of the rows (flat token indices) asked for."""
-        return linear(ctx, final, self.head, out_dtype=torch.float32, row_index=rows)
+    def logits(self, ctx, hidden: torch.Tensor, residual: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+        """float32 logits [len(rows), vocab] of the rows (flat token indices) asked for:
+        only those rows are gathered, added, normed and multiplied with the head."""
+        hidden = ops.gather_rows(hidden, rows, ctx.status)
+        if residual is None:
+            final = self.final_norm.forward(ctx, hidden)
+        else:
+            final = self.final_norm.forward_add(ctx, hidden, ops.gather_rows(residual, rows, ctx.status))[0]
+        return linear(ctx, final, self.head, out_dtype=torch.float32)

@@ -197,11 +197,59 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
 
 def gemm_tc_supported(n: int, k: int) -> bool:
     """Whether the tensor-core product takes a [n, k] bfloat16 weight."""
-    return False
+    return bool(library().vosti_gemm_tc_supported(int(n), int(k)))
 
 
-def gemm_tc(x, w, status, *, out_dtype=None, row_index=None):
-    raise KernelError("tensor-core product is not available")
+_WORKSPACES = {}
+
+
+def _workspace(device: torch.device, elems: int) -> torch.Tensor:
+    """float32 scratch of the split-K product, one per device, grown on demand. Kernels on
+    one stream use it one after the other."""
+    key = (device.type, device.index)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < elems:
+        buf = torch.empty(max(elems, 1 << 20), dtype=torch.float32, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
+            swiglu: bool = False) -> torch.Tensor:
+    """y = x @ w.T on the tensor cores (bfloat16 operands, float32 accumulation). With
+    `swiglu` the rows of w are blocks of 16 gate rows followed by their 16 up rows and
+    y = silu(gate) * up has half as many columns."""
+    _contig(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc takes bfloat16 operands")
+    tokens, k = x.shape
+    features = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"gemm: inner sizes differ ({k} vs {w.shape[1]})")
+    out_dtype = out_dtype or torch.bfloat16
+    if swiglu:
+        epilogue, width = EPI_SWIGLU, features // 2
+        if out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc: the fused SiLU*up epilogue writes bfloat16")
+    else:
+        epilogue, width = (EPI_F32 if out_dtype == torch.float32 else EPI_BF16), features
+    out = torch.empty((tokens, width), dtype=out_dtype, device=x.device)
+    lib = library()
+    splits = lib.vosti_gemm_tc_splits(tokens, features, k)
+    elems = splits * tokens * features if splits > 1 else 0
+    ws = _workspace(x.device, elems) if elems else None
+    _check(lib.vosti_gemm_tc(_p(x), _p(w), _p(out), tokens, features, k, epilogue, _p(ws),
+                             ctypes.c_int64(ws.numel() if ws is not None else 0), _p(status), _stream()),
+           "gemm_tc", kernels=2 if splits > 1 else 1)
+    return out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """x[rows] for int32 row indices (the embedding kernel over an activation matrix)."""
+    return embedding(rows, x, status)
 
 
 def attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,

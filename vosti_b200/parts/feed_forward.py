@@ -15,7 +15,7 @@ from .. import ops
 from ..config.schema import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
 from .base import FeedForward, register_part
-from .linear import linear
+from .linear import linear, uses_tensor_cores
 
 
 class SwiGLU(FeedForward):
@@ -25,6 +25,7 @@ class SwiGLU(FeedForward):
         if self.inter <= 0:
             raise ConfigError("swiglu: intermediate_size must be positive")
         self.w_gate_up = self.w_down = None
+        self.fused = False
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, i = self.hidden_size, self.inter
@@ -34,12 +35,25 @@ class SwiGLU(FeedForward):
     def load(self, tensors, dtype):
         gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         common = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
-        self.w_gate_up = torch.cat([gate.to(common), up.to(common)], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
+        stacked = torch.cat([gate.to(common), up.to(common)], dim=0)
+        # On the tensor-core path SiLU(gate)*up is the product's epilogue: rows are laid out
+        # as blocks of 16 gate rows followed by their 16 up rows, so that both halves of an
+        # output land in one warp's slice of the accumulator.
+        self.fused = (dtype == torch.bfloat16 and self.inter % 16 == 0 and uses_tensor_cores(dtype, stacked))
+        if self.fused:
+            h = stacked.shape[1]
+            blocks = torch.stack([stacked[:self.inter].view(-1, 16, h), stacked[self.inter:].view(-1, 16, h)], dim=1)
+            self.w_gate_up = blocks.reshape(2 * self.inter, h).contiguous()
+        else:
+            self.w_gate_up = stacked.contiguous()
 
     def forward(self, ctx, x):
-        gate_up = linear(ctx, x, self.w_gate_up)
-        return linear(ctx, ops.silu_mul(gate_up), self.w_down)
+        if self.fused:
+            mlp = ops.gemm_tc(x, self.w_gate_up, ctx.status, swiglu=True)
+        else:
+            mlp = ops.silu_mul(linear(ctx, x, self.w_gate_up))
+        return linear(ctx, mlp, self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -14,8 +14,15 @@ import torch
 from .. import ops
 
 
+def uses_tensor_cores(x_dtype: torch.dtype, w: torch.Tensor) -> bool:
+    return (x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_cuda
+            and ops.gemm_tc_supported(w.shape[0], w.shape[1]))
+
+
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
            row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
-    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.gemm_tc_supported(w.shape[0], w.shape[1])):
-        return ops.gemm_tc(x, w, ctx.status, out_dtype=out_dtype, row_index=row_index)
+    if uses_tensor_cores(x.dtype, w):
+        if row_index is not None:
+            x = ops.gather_rows(x, row_index, ctx.status)
+        return ops.gemm_tc(x, w, ctx.status, out_dtype=out_dtype)
     return ops.gemm_simt(x, w, ctx.status, out_dtype=out_dtype, row_index=row_index)
