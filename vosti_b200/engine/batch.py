@@ -59,6 +59,13 @@ class StepContext:
     max_kv_len: int = 0
     all_decode: bool = False
     extras: dict = field(default_factory=dict)   # further per-step device arrays by name
+    # attention work lists: tokens of requests that bring at most SHORT_ROW tokens (served
+    # one query at a time) and the requests that bring more (served as portions)
+    short_tokens: Optional[torch.Tensor] = None   # int32 token indices, None: every token
+    num_short_tokens: int = 0
+    long_rows: Optional[torch.Tensor] = None      # int32 request rows, None: every request
+    num_long_rows: int = 0
+    max_long_q_len: int = 0
 
     def group(self, index: int) -> GroupView:
         return self.groups[index]
@@ -67,7 +74,7 @@ class StepContext:
 class StagingBuffer:
     """Pinned host memory and its device twin, grown on demand."""
 
-    def __init__(self, device: torch.device, capacity: int = 1 << 16):
+    def __init__(self, device: torch.device, capacity: int = 1 << 18):
         self.device = device
         self.copied = None          # event after the last host-to-device copy
         self.last_upload_bytes = 0
@@ -96,6 +103,9 @@ class StagingBuffer:
         self.copied.record()
 
 
+SHORT_ROW = 4
+
+
 def _round_up(value: int, multiple: int) -> int:
     return (value + multiple - 1) // multiple * multiple
 
@@ -103,7 +113,7 @@ def _round_up(value: int, multiple: int) -> int:
 def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: Sequence[int],
                   slots_per_group: Sequence[Sequence[Sequence[int]]], block_rows: Sequence[Sequence[Sequence[int]]],
                   state_slots: Sequence[int], page_size: int, status: torch.Tensor, dtype: torch.dtype,
-                  extras: Optional[dict] = None) -> StepContext:
+                  extras: Optional[dict] = None, min_pages: int = 0, kv_bucket: int = 0) -> StepContext:
     """Lay the batch out and copy it. `starts[i]` is the position of entry i's first token;
     `slots_per_group[g][i]` the cache slots of its tokens in group g; `block_rows[g][i]` its
     page ids in group g."""
@@ -112,15 +122,28 @@ def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: 
     T = sum(q_lens)
     W = sum(len(e.want) for e in entries)
     G = len(slots_per_group)
-    max_pages = [_round_up(max((len(r) for r in block_rows[g]), default=1) or 1, 4) for g in range(G)]
+    max_pages = [max(min_pages, _round_up(max((len(r) for r in block_rows[g]), default=1) or 1, 4))
+                 for g in range(G)]
     # sections are padded to 4 ints so that every section starts 16-byte aligned
     sizes = [T, T, T, B + 1, B, B, W] + [x for g in range(G) for x in (T, B * max_pages[g])]
     offsets, total = [], 0
     for s in sizes:
         offsets.append(total)
         total += _round_up(max(s, 1), 4)
+    extras = dict(extras or {})
+    short_tokens, long_rows, cursor = [], [], 0
+    for i, n in enumerate(q_lens):
+        if n <= SHORT_ROW:
+            short_tokens.extend(range(cursor, cursor + n))
+        else:
+            long_rows.append(i)
+        cursor += n
+    mixed = bool(short_tokens) and bool(long_rows)
+    if mixed:
+        extras["_short_tokens"] = np.asarray(short_tokens, dtype=np.int32)
+        extras["_long_rows"] = np.asarray(long_rows, dtype=np.int32)
     extra_at = {}
-    for name, array in (extras or {}).items():
+    for name, array in extras.items():
         words = np.ascontiguousarray(array).view(np.int32)
         extra_at[name] = (total, words, array.dtype)
         total += _round_up(max(words.size, 1), 4)
@@ -175,4 +198,7 @@ def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: 
         state_slots=dev[o_slot:o_slot + B], want_rows=dev[o_want:o_want + W], groups=groups, status=status,
         dtype=dtype, device=staging.device, host_q_lens=q_lens, host_kv_lens=kv_lens,
         host_state_slots=list(state_slots), max_q_len=max(q_lens, default=0),
-        max_kv_len=max(kv_lens, default=0), all_decode=all(n == 1 for n in q_lens), extras=extra_views)
+        max_kv_len=max(kv_bucket, max(kv_lens, default=0)), all_decode=all(n == 1 for n in q_lens), extras=extra_views,
+        short_tokens=extra_views.pop("_short_tokens", None), num_short_tokens=len(short_tokens),
+        long_rows=extra_views.pop("_long_rows", None), num_long_rows=len(long_rows),
+        max_long_q_len=max((q_lens[i] for i in long_rows), default=0))

@@ -17,6 +17,7 @@ meaning here, and every one also has a flag (the flag wins):
   VOSTI_BENCH_INPUT         --bench-input      prepared requests: MAX_TOKENS<TAB>IDS[<TAB>ARRIVAL_STEP]
   VOSTI_BENCH_WARMUP_INPUT  --bench-warmup-input   a disjoint prepared workload run first
   VOSTI_ENGINE_STEP_TRACE   --step-trace       one JSON line per step
+  VOSTI_CUDA_GRAPH          --cuda-graph       0/1: replay decode steps as CUDA graphs (default 1 here)
 
 Added here: --dtype {bfloat16,float32} (VOSTI_DTYPE), --block-size (VOSTI_BLOCK_SIZE, the
 reference's page size is the constant 64), --temperature, --seed, --chunk-size, and
@@ -142,6 +143,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     parser.add_argument("--bench-warmup-input", default=_env("VOSTI_BENCH_WARMUP_INPUT"))
     parser.add_argument("--step-trace", default=_env("VOSTI_ENGINE_STEP_TRACE"))
     parser.add_argument("--no-prefix-caching", action="store_true")
+    parser.add_argument("--cuda-graph", type=int, choices=[0, 1], default=int(_env("VOSTI_CUDA_GRAPH", 1)))
     parser.add_argument("--random-config", help="config.json to draw a random-weights model from")
     parser.add_argument("--random-seed", type=int, default=0)
     args = parser.parse_args(argv)
@@ -165,7 +167,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     engine = Engine(args.model, dtype=args.dtype, device=args.device, num_blocks=args.num_blocks,
                     block_size=args.block_size, max_num_seqs=max_seqs,
                     max_num_batched_tokens=args.max_batched_tokens, prefill_chunk_size=args.chunk_size,
-                    enable_prefix_caching=not args.no_prefix_caching, step_trace=args.step_trace)
+                    enable_prefix_caching=not args.no_prefix_caching, step_trace=args.step_trace,
+                    cuda_graphs=bool(args.cuda_graph))
     print(f"MODEL_RUNTIME architecture={engine.runner.spec.architecture} dtype={args.dtype} "
           f"device={args.device}", flush=True)
 

@@ -34,7 +34,7 @@ class Engine:
                  num_blocks: int = 32, block_size: int = 16, max_num_seqs: int = 1,
                  max_num_batched_tokens: int = 4096, prefill_chunk_size: int = 0,
                  enable_prefix_caching: bool = True, step_trace: Optional[str] = None,
-                 spec=None, tensors=None):
+                 cuda_graphs: bool = True, spec=None, tensors=None):
         """`num_blocks` pages of `block_size` tokens; `max_num_seqs` rows and
         `max_num_batched_tokens` tokens per step at most (the reference's VOSTI_NUM_BLOCKS,
         VOSTI_MAX_SEQS, VOSTI_MAX_BATCHED_TOKENS; its page size is fixed at 64)."""
@@ -45,6 +45,8 @@ class Engine:
         self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
             max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
             prefill_chunk_size=prefill_chunk_size, vocab_size=spec.vocab_size, max_context=spec.max_positions))
+        from .graphs import DecodeGraphs
+        self.graphs = DecodeGraphs(self.runner) if cuda_graphs else None
         self.step_trace = open(step_trace, "a") if step_trace else None
         self.step_index = 0
         self.last_plan: Optional[StepPlan] = None
@@ -94,14 +96,17 @@ class Engine:
         runner = self.runner
         arrays = sampling_arrays(temps, seeds, counters)
         extras = None if arrays is None else {"temperature": arrays[0], "seeds": arrays[1], "counters": arrays[2]}
-        ctx = runner.prepare(entries, extras=extras)
-        logits = runner.run(ctx)
         sampled: List[Optional[int]] = [None] * len(plan.rows)
         count = len(temps)
-        if logits is not None:
-            ex = ctx.extras
-            sample_rows(logits, ex.get("temperature"), ex.get("seeds"), ex.get("counters"),
-                        out=runner.result[1:1 + count])
+        if self.graphs is not None and all(row.count == 1 and row.sample for row in plan.rows):
+            self.graphs.step(entries, extras)
+        else:
+            ctx = runner.prepare(entries, extras=extras)
+            logits = runner.run(ctx)
+            if logits is not None:
+                ex = ctx.extras
+                sample_rows(logits, ex.get("temperature"), ex.get("seeds"), ex.get("counters"),
+                            out=runner.result[1:1 + count])
         runner.result_host[:1 + count].copy_(runner.result[:1 + count], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         host = runner.result_host[:1 + count].tolist()

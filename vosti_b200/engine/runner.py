@@ -88,7 +88,8 @@ class ModelRunner:
         self.cache.finish(request_id)
 
     # ------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry], extras: Optional[dict] = None) -> StepContext:
+    def prepare(self, entries: Sequence[StepEntry], extras: Optional[dict] = None, min_pages: int = 0,
+                kv_bucket: int = 0) -> StepContext:
         """Reserve cache entries for the step's tokens (all requests or none) and copy the
         batch to the device."""
         cache = self.cache
@@ -122,7 +123,8 @@ class ModelRunner:
         block_rows = [[cache.block_row(e.request_id, g) for e in entries] for g in range(G)]
         state_slots = [cache.slot(e.request_id) for e in entries]
         return build_context(self.staging, entries, starts, slots_per_group, block_rows, state_slots,
-                             cache.page_size, self.status, self.dtype, extras=extras)
+                             cache.page_size, self.status, self.dtype, extras=extras, min_pages=min_pages,
+                             kv_bucket=kv_bucket)
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """The model over the prepared batch; float32 logits [wanted, vocab] or None."""

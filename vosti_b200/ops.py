@@ -201,6 +201,7 @@ def gemm_tc_supported(n: int, k: int) -> bool:
 
 
 _WORKSPACES = {}
+WORKSPACE_GENERATION = 0   # bumped whenever a scratch buffer moves (captured graphs hold its address)
 
 
 def _workspace(device: torch.device, elems: int) -> torch.Tensor:
@@ -209,7 +210,9 @@ def _workspace(device: torch.device, elems: int) -> torch.Tensor:
     key = (device.type, device.index)
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < elems:
-        buf = torch.empty(max(elems, 1 << 20), dtype=torch.float32, device=device)
+        global WORKSPACE_GENERATION
+        WORKSPACE_GENERATION += 1
+        buf = torch.empty(max(elems, 1 << 22), dtype=torch.float32, device=device)
         _WORKSPACES[key] = buf
     return buf
 
@@ -252,9 +255,49 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, status: torch.Tensor) -> to
     return embedding(rows, x, status)
 
 
+def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, request_of, block_table,
+                     page_size, nq, nkv, head_dim, max_kv_len, scale, window, status) -> None:
+    """Single-query attention with split keys for `count` tokens (bfloat16)."""
+    lib = library()
+    tokens_total = q.shape[0]
+    lib.vosti_attention_decode_scratch.restype = ctypes.c_int64
+    elems = lib.vosti_attention_decode_scratch(count, nq, head_dim, max_kv_len)
+    scratch = _workspace(q.device, elems)
+    num_pages = k_cache.numel() // (page_size * nkv * head_dim)
+    _check(lib.vosti_attention_decode(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), ctypes.c_int64(scratch.numel()), _p(token_list),
+        count, tokens_total, _p(positions), _p(request_of), _p(block_table), block_table.shape[1], page_size,
+        num_pages, nq, nkv, head_dim, max_kv_len, ctypes.c_float(scale), window, _p(status), _stream()),
+        "attention_decode", kernels=2)
+
+
+def attention_prefill(q, k_cache, v_cache, out, *, row_list, count, cu_q, kv_len, block_table, page_size, nq, nkv,
+                      head_dim, max_q_len, scale, window, status) -> None:
+    """Attention of whole portions for `count` requests (bfloat16)."""
+    num_pages = k_cache.numel() // (page_size * nkv * head_dim)
+    _check(library().vosti_attention_prefill(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(row_list), count, _p(cu_q), _p(kv_len), _p(block_table),
+        block_table.shape[1], page_size, num_pages, nq, nkv, head_dim, max_q_len, ctypes.c_float(scale), window,
+        _p(status), _stream()), "attention_prefill")
+
+
 def attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,
               head_dim: int, scale: float, window: int) -> torch.Tensor:
-    """Attention of every query row of the batch over its request's cached keys."""
-    return attention_simt(q, k_cache, v_cache, positions=ctx.positions, request_of=ctx.request_of,
-                          block_table=group.block_table, page_size=group.page_size, nq=nq, nkv=nkv,
-                          head_dim=head_dim, scale=scale, window=window, status=ctx.status)
+    """Attention of every query row of the batch over its request's cached keys. float32
+    runs on the CUDA cores; bfloat16 on the tensor cores, requests that bring a few tokens
+    one query at a time with split keys, longer portions tile by tile."""
+    if q.dtype != torch.bfloat16 or nq // nkv > 16:
+        return attention_simt(q, k_cache, v_cache, positions=ctx.positions, request_of=ctx.request_of,
+                              block_table=group.block_table, page_size=group.page_size, nq=nq, nkv=nkv,
+                              head_dim=head_dim, scale=scale, window=window, status=ctx.status)
+    _contig(q, k_cache, v_cache)
+    out = torch.empty_like(q)
+    common = dict(block_table=group.block_table, page_size=group.page_size, nq=nq, nkv=nkv, head_dim=head_dim,
+                  scale=scale, window=window, status=ctx.status)
+    if ctx.num_short_tokens:
+        attention_decode(q, k_cache, v_cache, out, token_list=ctx.short_tokens, count=ctx.num_short_tokens,
+                         positions=ctx.positions, request_of=ctx.request_of, max_kv_len=ctx.max_kv_len, **common)
+    if ctx.num_long_rows:
+        attention_prefill(q, k_cache, v_cache, out, row_list=ctx.long_rows, count=ctx.num_long_rows, cu_q=ctx.cu_q,
+                          kv_len=ctx.kv_len, max_q_len=ctx.max_long_q_len, **common)
+    return out
