@@ -176,6 +176,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (both are reported)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    parser.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
+    parser.add_argument("--no-cuda-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -210,13 +212,13 @@ def main() -> int:
     num_blocks = max_batch * ((tokens_per_request + PAGE - 1) // PAGE) + 8
     engine = Engine(spec=spec, tensors=tensors, dtype="bfloat16", device="cuda:0", num_blocks=num_blocks,
                     block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=2 * CONTEXT,
-                    enable_prefix_caching=False)
+                    enable_prefix_caching=False, cuda_graphs=not args.no_cuda_graphs)
     del tensors
     torch.cuda.empty_cache()
     weight_bytes = engine.runner.model.weight_bytes() - spec.vocab_size * spec.hidden_size * 2  # embedding rows: not read whole
     kv_bytes_per_token = engine.runner.cache.bytes_per_token()
 
-    prefill_ms = prefill_run(engine, 3, seed=11)
+    prefill_ms = float("nan") if args.no_prefill else prefill_run(engine, 3, seed=11)
     main_run = decode_run(engine, args.batch, args.steps, args.warmup, seed=21, sample_clocks=True)
     points = {}
     if not args.no_points:

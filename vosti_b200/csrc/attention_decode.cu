@@ -4,8 +4,9 @@
 //   grid = (segments, kv heads, tokens). One CTA takes one token, one kv head with the
 //   whole group of query heads that share it (they fill the MMA's 16 rows), and one
 //   segment of SEGMENT keys counted from key 0 of the request. Its four warps each take a
-//   quarter of the segment, run the online softmax (base 2, float32) over tiles of 16 keys
-//   with mma.sync m16n8k16 for Q.K^T and P.V, and are merged in warp order. The CTA writes
+//   quarter of the segment (two tiles of 16 keys, both requested from memory before any
+//   arithmetic), run the online softmax (base 2, float32) with mma.sync m16n8k16 for
+//   Q.K^T and P.V, and are merged in warp order. The CTA writes
 //   an unnormalised partial (max, sum, accumulator) per query head; a second kernel merges
 //   the segments in segment order and normalises.
 //
@@ -14,7 +15,7 @@
 // kv head = query head * nkv / nq, scale * log2(e), causal up to the token's own position,
 // optional window, P rounded to bfloat16 before P.V (:246), out = acc / l (0 if l = 0).
 // K and V tiles are staged in shared memory with cp.async (16-byte chunks straight from the
-// pages), double-buffered per warp; masked keys are never read from the cache.
+// pages); masked keys are never read from the cache.
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -22,22 +23,26 @@ namespace {
 
 constexpr int WARPS = 4;
 constexpr int TILE = 16;              // keys per MMA step
-constexpr int SEGMENT = 256;          // keys per CTA
+constexpr int SEGMENT = 128;          // keys per CTA
 constexpr int WARP_KEYS = SEGMENT / WARPS;
+constexpr int WARP_TILES = WARP_KEYS / TILE;   // tiles a warp holds in shared memory at once
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Partial record of one (token, query head, segment): [0] max (base-2 scores), [1] sum,
 // [2 .. 2+d) accumulator.
 __host__ __device__ inline int record_floats(int d) { return d + 2; }
 
-template <int DMAX>
+// DMAX bounds the head size; with EXACT the head size is DMAX itself, which turns the index
+// arithmetic of the staging loops into shifts.
+template <int DMAX, bool EXACT>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         float* __restrict__ partial, const int* __restrict__ token_list,
                         const int* __restrict__ positions, const int* __restrict__ request_of,
                         const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
-                        int nq, int nkv, int d, int max_segments, float scale_log2, int window, unsigned* status) {
+                        int nq, int nkv, int d_runtime, int max_segments, float scale_log2, int window, unsigned* status) {
   extern __shared__ __align__(16) uint8_t smem[];
+  const int d = EXACT ? DMAX : d_runtime;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = token_list ? token_list[blockIdx.z] : blockIdx.z;
   const int g = blockIdx.y, seg = blockIdx.x;
@@ -50,7 +55,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 
   const int pitch = d * 2 + 16;                     // bytes per staged row: conflict-free ldmatrix
   uint8_t* q_s = smem;                              // [16][pitch]
-  uint8_t* stage_base = smem + 16 * pitch + warp * (4 * TILE * pitch);   // per warp: 2 buffers x (K, V)
+  uint8_t* stage_base = smem + 16 * pitch + warp * (2 * WARP_TILES * TILE * pitch);   // per warp: tiles x (K, V)
   const int chunks = d / 8;                         // 16-byte chunks per row
 
   // ---- Q rows of the group (rows >= group are zero)
@@ -67,26 +72,25 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
   const int first_tile = max(my_begin, (kstart / TILE) * TILE);       // tiles stay aligned to the key index
   const int tiles = my_end > first_tile ? (my_end - first_tile + TILE - 1) / TILE : 0;
 
-  auto issue = [&](int tile, int buffer) {
+  // One cache slot per key of a tile: lane r (< 16) looks up key r, the others get it by shuffle.
+  auto issue = [&](int tile) {
     const int key0 = first_tile + tile * TILE;
-    uint8_t* kdst = stage_base + buffer * (2 * TILE * pitch);
+    uint8_t* kdst = stage_base + tile * (2 * TILE * pitch);
     uint8_t* vdst = kdst + TILE * pitch;
-    for (int i = lane; i < TILE * chunks; i += 32) {
-      const int row = i / chunks, c = i % chunks;
-      const int key = key0 + row;
-      bool valid = key >= kstart && key <= pos;
-      int64_t slot = 0;
-      if (valid) {
+    int64_t my_slot = -1;
+    {
+      const int key = key0 + (lane & 15);
+      if (key >= kstart && key <= pos) {
         const int index = key / page_size;
         const int page = index < max_pages ? table[index] : -1;
-        if (page < 0 || page >= num_pages) {
-          raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
-          valid = false;
-        } else {
-          slot = (int64_t)page * page_size + key % page_size;
-        }
+        if (page < 0 || page >= num_pages) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
+        else my_slot = (int64_t)page * page_size + key % page_size;
       }
-      if (valid) {
+    }
+    for (int i = lane; i < TILE * chunks; i += 32) {
+      const int row = i / chunks, c = i % chunks;
+      const int64_t slot = __shfl_sync(0xffffffffu, my_slot, row);
+      if (slot >= 0) {
         const int64_t offset = (slot * nkv + g) * d + c * 8;
         cp_async16(smem_addr(kdst + row * pitch + c * 16), k_cache + offset);
         cp_async16(smem_addr(vdst + row * pitch + c * 16), v_cache + offset);
@@ -103,17 +107,13 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 #pragma unroll
   for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  if (tiles > 0) issue(0, 0);
+  static_assert(WARP_TILES == 2, "the wait below counts two outstanding groups");
+  for (int tile = 0; tile < tiles; ++tile) issue(tile);           // everything is requested up front
   for (int tile = 0; tile < tiles; ++tile) {
-    const int buffer = tile & 1;
-    if (tile + 1 < tiles) {
-      issue(tile + 1, buffer ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    if (tile + 1 < tiles) cp_async_wait<1>();
+    else cp_async_wait<0>();
     __syncwarp();
-    const uint8_t* ks = stage_base + buffer * (2 * TILE * pitch);
+    const uint8_t* ks = stage_base + tile * (2 * TILE * pitch);
     const uint8_t* vs = ks + TILE * pitch;
     const int key0 = first_tile + tile * TILE;
 
@@ -175,7 +175,6 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         mma_bf16(o[2 * nt + 1], p, b[2], b[3]);
       }
     }
-    __syncwarp();
   }
   // ---- merge the four warps in warp order (through the staging memory)
 #pragma unroll
@@ -223,7 +222,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
   }
 }
 
-// One warp per (token, query head): combine the segments in segment order.
+// One warp per (token, query head): combine the segments. Lane s holds segment s's max and
+// weight; the sums run over segments in segment order.
 __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
                                        const int* __restrict__ token_list, const int* __restrict__ positions,
                                        int count, int nq, int d, int max_segments, int window) {
@@ -238,21 +238,38 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
   const int first = kstart / SEGMENT, last = pos / SEGMENT;
   const int rec = d + 2;
   const float* base = partial + ((int64_t)item * nq + h) * max_segments * rec;
+  // pass 1: the overall maximum
   float m = -INFINITY;
-  for (int s = first; s <= last; ++s) m = fmaxf(m, base[(int64_t)s * rec]);
+  for (int s0 = first; s0 <= last; s0 += 32) {
+    const int s = s0 + lane;
+    m = fmaxf(m, s <= last ? base[(int64_t)s * rec] : -INFINITY);
+  }
+  m = warp_max(m);
+  // pass 2: weights, sum and accumulator
   float l = 0.f;
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int s = first; s <= last; ++s) {
-    const float ms = base[(int64_t)s * rec];
-    if (ms == -INFINITY) continue;
-    const float w = exp2f(ms - m);
-    l += base[(int64_t)s * rec + 1] * w;
+  for (int s0 = first; s0 <= last; s0 += 32) {
+    const int mine = s0 + lane;
+    float w_mine = 0.f, l_mine = 0.f;
+    if (mine <= last) {
+      const float ms = base[(int64_t)mine * rec];
+      if (ms != -INFINITY) {
+        w_mine = exp2f(ms - m);
+        l_mine = base[(int64_t)mine * rec + 1] * w_mine;
+      }
+    }
+    const int n = min(32, last - s0 + 1);
+    for (int j = 0; j < n; ++j) {
+      const float w = __shfl_sync(0xffffffffu, w_mine, j);
+      l += __shfl_sync(0xffffffffu, l_mine, j);
+      const float* row = base + (int64_t)(s0 + j) * rec + 2;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = lane + 32 * i;
-      if (c < d) acc[i] += base[(int64_t)s * rec + 2 + c] * w;
+      for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d) acc[i] = fmaf(row[c], w, acc[i]);
+      }
     }
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -266,7 +283,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
 
 size_t decode_smem_bytes(int d) {
   const size_t pitch = (size_t)d * 2 + 16;
-  const size_t stage = 16 * pitch + (size_t)WARPS * 4 * TILE * pitch;
+  const size_t stage = 16 * pitch + (size_t)WARPS * 2 * WARP_TILES * TILE * pitch;
   const size_t merge = 16 * pitch + (size_t)WARPS * 16 * (d + 2) * sizeof(float);
   return stage > merge ? stage : merge;
 }
@@ -302,21 +319,24 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   const size_t smem = decode_smem_bytes(d);
   dim3 grid(segments, nkv, count);
   VOSTI_REQUIRE(count <= 65535, "attention_decode: too many tokens (%d) for one launch", count);
-#define LAUNCH_DECODE(DMAX)                                                                                         \
+#define LAUNCH_DECODE(DMAX, EXACT)                                                                                  \
   do {                                                                                                              \
     static bool configured = false;                                                                                 \
     if (!configured) {                                                                                              \
-      cudaFuncSetAttribute(attention_decode_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+      cudaFuncSetAttribute(attention_decode_kernel<DMAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                            (int)decode_smem_bytes(DMAX));                                                           \
       configured = true;                                                                                            \
     }                                                                                                               \
-    attention_decode_kernel<DMAX><<<grid, WARPS * 32, smem, stream>>>(                                              \
+    attention_decode_kernel<DMAX, EXACT><<<grid, WARPS * 32, smem, stream>>>(                                       \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, scratch, token_list, positions, request_of,      \
         block_table, max_pages, page_size, num_pages, nq, nkv, d, segments, scale * LOG2E, window, status);          \
   } while (0)
-  if (d <= 64) LAUNCH_DECODE(64);
-  else if (d <= 128) LAUNCH_DECODE(128);
-  else LAUNCH_DECODE(256);
+  if (d == 64) LAUNCH_DECODE(64, true);
+  else if (d == 128) LAUNCH_DECODE(128, true);
+  else if (d == 256) LAUNCH_DECODE(256, true);
+  else if (d < 64) LAUNCH_DECODE(64, false);
+  else if (d < 128) LAUNCH_DECODE(128, false);
+  else LAUNCH_DECODE(256, false);
 #undef LAUNCH_DECODE
   const int64_t warps = (int64_t)count * nq;
   attention_merge_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(scratch, (bf16*)out, token_list, positions,

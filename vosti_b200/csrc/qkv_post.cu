@@ -40,7 +40,7 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
     }
   }
 
-  for (int h = warp; h < heads; h += nwarps) {
+  for (int h = blockIdx.y * nwarps + warp; h < heads; h += gridDim.y * nwarps) {
     const T* src = qkv + in_base + (int64_t)h * d;
     const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
     T* dst;
@@ -108,12 +108,14 @@ VOSTI_API int vosti_qkv_post(const void* qkv, void* q_out, void* k_cache, void* 
   VOSTI_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "qkv_post: cos and sin go together");
   VOSTI_REQUIRE(cos_table == nullptr || positions != nullptr, "qkv_post: rotation needs positions");
   if (tokens == 0) return VOSTI_OK;
+  const int heads = nq + 2 * nkv;
+  const dim3 grid(tokens, tokens >= 2048 ? 1 : (heads + 3) / 4);   // few tokens: a warp per (token, head)
   if (is_f32)
-    qkv_post_kernel<float><<<tokens, 128, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_cache,
+    qkv_post_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_cache,
         (float*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
         slot_mapping, num_slots, nq, nkv, d, status);
   else
-    qkv_post_kernel<bf16><<<tokens, 128, 0, stream>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+    qkv_post_kernel<bf16><<<grid, 128, 0, stream>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
         (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
         slot_mapping, num_slots, nq, nkv, d, status);
   VOSTI_LAUNCH_CHECK();
