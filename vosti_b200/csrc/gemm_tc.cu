@@ -1,9 +1,10 @@
 // bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), operands staged
 // in shared memory by TMA, accumulator in tensor memory:
 //   Y[t, f] = sum_k X[t, k] * W[f, k]          X: [T, K], W: [F, K] (both K-major), no bias
-// Output features fill the MMA's M = 128 (one accumulator lane per feature), tokens are
-// the N side (32..256 per tile), so a decode step of a few tokens still uses whole
-// instructions and the operand roles are the same for prefill and decode.
+// Up to 128 tokens, output features fill the MMA's M = 128 (one accumulator lane per
+// feature) and tokens are the N side (32..128 per tile), so a decode step of a few tokens
+// still uses whole instructions; K is split for enough CTAs, by a rule of the sizes only,
+// and the splits are summed in split order. For more tokens see gemm_tc_wide_kernel.
 //
 // One CTA computes one 128 x BN tile (one K split of it): warp 0 issues the TMA loads,
 // warp 1 allocates tensor memory and issues the MMAs, warps 2..5 read the accumulator
@@ -258,6 +259,190 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
+
+// ------------------------------------------------------------------ the kernel for many tokens
+// For more than 128 tokens the roles are swapped: 128 tokens fill the MMA's M (one
+// accumulator lane per token) and 256 features are the N side, so that a thread of the
+// epilogue holds consecutive features of one token and stores them as 16-byte vectors, and
+// the gate and up halves of a fused SiLU*up block sit in one thread. The kernel is
+// persistent (one CTA per SM walks over tiles) with two accumulators in tensor memory, so
+// the epilogue of a tile runs while the next tile's MMAs are issued.
+constexpr int WIDE_BN = 256;
+constexpr int WIDE_STAGES = 4;
+constexpr int WIDE_B_BYTES = WIDE_BN * BK * 2;
+constexpr int WIDE_STAGE_BYTES = A_BYTES + WIDE_B_BYTES;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    void* __restrict__ out, int tokens, int features, int k_blocks, int ld_out, int epilogue,
+                    unsigned* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[WIDE_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[WIDE_STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (tokens + BM - 1) / BM, n_tiles = (features + WIDE_BN - 1) / WIDE_BN;
+  const int total_tiles = m_tiles * n_tiles;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < WIDE_STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 4);       // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_holder), 2 * WIDE_BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * WIDE_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % WIDE_STAGES;
+          const uint32_t round = it / WIDE_STAGES;
+          if (it >= WIDE_STAGES && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, &abort_flag, status)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          mbar_expect_tx(bar, WIDE_STAGE_BYTES);
+          const uint32_t a_dst = smem_u32(smem + s * WIDE_STAGE_BYTES);
+          tma_load_2d(a_dst, &map_x, kb * BK, m0, bar);
+          tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(WIDE_BN);
+      uint32_t it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t as = local & 1, acc_round = local >> 1;
+        if (local >= 2) ok = mbar_wait(smem_u32(&acc_empty[as]), (acc_round - 1) & 1, &abort_flag, status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * WIDE_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % WIDE_STAGES;
+          ok = mbar_wait(smem_u32(&full_bar[s]), (it / WIDE_STAGES) & 1, &abort_flag, status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * WIDE_STAGE_BYTES);
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(smem_u32(&empty_bar[s]));
+        }
+        if (ok) umma_commit(smem_u32(&acc_full[as]));
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * WIDE_BN;
+      const uint32_t as = local & 1;
+      ok = mbar_wait(smem_u32(&acc_full[as]), (local >> 1) & 1, &abort_flag, status);
+      if (!ok) break;
+      tc_fence_after();
+      const int token = m0 + quarter * 32 + lane;
+      const bool row_ok = token < tokens;
+#pragma unroll 1
+      for (int c0 = 0; c0 < WIDE_BN; c0 += 32) {
+        const int f0 = n0 + c0;
+        if (f0 >= features) break;
+        uint32_t r[32];
+        tmem_load32(tmem_base + as * WIDE_BN + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        if (!row_ok) continue;
+        if (epilogue == EPI_SWIGLU) {
+          // columns f0..f0+15 are gate rows, f0+16..f0+31 their up rows (features % 32 == 0)
+          bf16* y = reinterpret_cast<bf16*>(out) + (int64_t)token * ld_out + f0 / 2;
+          uint32_t packed[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float a = silu(__uint_as_float(r[2 * j])) * __uint_as_float(r[16 + 2 * j]);
+            const float b = silu(__uint_as_float(r[2 * j + 1])) * __uint_as_float(r[17 + 2 * j]);
+            __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+            packed[j] = *reinterpret_cast<uint32_t*>(&v);
+          }
+          if ((ld_out & 7) == 0) {
+            reinterpret_cast<uint4*>(y)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(y)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) reinterpret_cast<uint32_t*>(y)[j] = packed[j];   // ld_out is even
+          }
+        } else if (epilogue == EPI_BF16) {
+          bf16* y = reinterpret_cast<bf16*>(out) + (int64_t)token * ld_out + f0;
+          if (f0 + 32 <= features && (ld_out & 7) == 0) {
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint32_t p[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * v4 + 2 * j]), __uint_as_float(r[8 * v4 + 2 * j + 1]));
+                p[j] = *reinterpret_cast<uint32_t*>(&v);
+              }
+              reinterpret_cast<uint4*>(y)[v4] = make_uint4(p[0], p[1], p[2], p[3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (f0 + j < features) y[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
+        } else {  // EPI_F32
+          float* y = reinterpret_cast<float*>(out) + (int64_t)token * ld_out + f0;
+          if (f0 + 32 <= features && (ld_out & 3) == 0) {
+#pragma unroll
+            for (int v4 = 0; v4 < 8; ++v4)
+              reinterpret_cast<uint4*>(y)[v4] = make_uint4(r[4 * v4], r[4 * v4 + 1], r[4 * v4 + 2], r[4 * v4 + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (f0 + j < features) y[j] = __uint_as_float(r[j]);
+          }
+        }
+      }
+      // this warp is done reading the accumulator: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[as]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * WIDE_BN);
+  }
+}
+
 // Sum the K splits in split order and apply the epilogue.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int splits,
                                      int tokens, int features, int ld_out, int epilogue) {
@@ -323,27 +508,27 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows)
 
 struct WeightKey {
   const void* p;
-  int rows, k;
-  bool operator==(const WeightKey& o) const { return p == o.p && rows == o.rows && k == o.k; }
+  int rows, k, box;
+  bool operator==(const WeightKey& o) const { return p == o.p && rows == o.rows && k == o.k && box == o.box; }
 };
 struct WeightKeyHash {
   size_t operator()(const WeightKey& key) const {
-    return std::hash<const void*>()(key.p) ^ ((size_t)key.rows * 1000003u) ^ ((size_t)key.k << 20);
+    return std::hash<const void*>()(key.p) ^ ((size_t)key.rows * 1000003u) ^ ((size_t)key.k << 20) ^ (size_t)key.box;
   }
 };
 
-bool weight_map(const void* w, int rows, int k, CUtensorMap* out) {
+bool weight_map(const void* w, int rows, int k, int box_rows, CUtensorMap* out) {
   static std::unordered_map<WeightKey, CUtensorMap, WeightKeyHash> cache;
   static std::mutex mutex;
   std::lock_guard<std::mutex> lock(mutex);
-  WeightKey key{w, rows, k};
+  WeightKey key{w, rows, k, box_rows};
   auto it = cache.find(key);
   if (it != cache.end()) {
     *out = it->second;
     return true;
   }
   if (cache.size() > 4096) cache.clear();
-  if (!make_map(out, w, rows, k, BM)) return false;
+  if (!make_map(out, w, rows, k, box_rows)) return false;
   cache.emplace(key, *out);
   return true;
 }
@@ -403,8 +588,30 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
                 "gemm_tc: workspace too small for %d splits", splits);
   CUtensorMap mw_storage, mx;
   const CUtensorMap* mw = &mw_storage;
+  if (tokens > 128) {
+    // many tokens: persistent kernel with tokens on the M side
+    VOSTI_REQUIRE(weight_map(w, features, k, WIDE_BN, &mw_storage) && make_map(&mx, x, tokens, k, BM),
+                  "gemm_tc: cuTensorMapEncodeTiled failed");
+    constexpr size_t smem = (size_t)WIDE_STAGES * WIDE_STAGE_BYTES + 1024;
+    static int sms = 0;
+    if (sms == 0) {
+      int device = 0;
+      cudaGetDevice(&device);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess || sms <= 0) {
+        sms = 0;
+        vosti_set_error("gemm_tc: cannot configure the persistent kernel: %s", cudaGetErrorString(e));
+        return e != cudaSuccess ? (int)e : VOSTI_UNSUPPORTED;
+      }
+    }
+    const int tiles = ((tokens + BM - 1) / BM) * ((features + WIDE_BN - 1) / WIDE_BN);
+    gemm_tc_wide_kernel<<<tiles < sms ? tiles : sms, THREADS, smem, stream>>>(mx, *mw, y, tokens, features, k_blocks,
+                                                                             ld_out, epilogue, status);
+    VOSTI_LAUNCH_CHECK();
+  }
   const int bn = token_tile(tokens);
-  VOSTI_REQUIRE(weight_map(w, features, k, &mw_storage) && make_map(&mx, x, tokens, k, bn),
+  VOSTI_REQUIRE(weight_map(w, features, k, BM, &mw_storage) && make_map(&mx, x, tokens, k, bn),
                 "gemm_tc: cuTensorMapEncodeTiled failed");
   void* dst = splits > 1 ? (void*)workspace : y;
   const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
