@@ -1,9 +1,9 @@
 // Paged causal attention for prompts and portions of prompts, bfloat16, on the tensor
 // cores (mma.sync m16n8k16), in the manner of flash attention:
 //
-//   grid = (query tiles, kv heads, requests). A CTA takes 64 rows of one request and one
+//   grid = (query tiles, kv heads, requests). A CTA takes 128 rows of one request and one
 //   kv head, where a row is a (query token, query head of the group) pair, so the query
-//   heads that share a kv head share its K and V tiles in shared memory. Each of the four
+//   heads that share a kv head share its K and V tiles in shared memory. Each of the eight
 //   warps owns 16 rows; K/V tiles of 64 keys, aligned to the absolute key index, are staged
 //   with cp.async (double-buffered) straight from the pages. Online softmax in base 2 and
 //   float32; P is rounded to bfloat16 before P.V; out = acc / l.
@@ -17,19 +17,22 @@
 
 namespace {
 
-constexpr int WARPS = 4;
-constexpr int ROWS = 64;              // packed (token, head) rows per CTA
+constexpr int WARPS = 8;
+constexpr int ROWS = 128;              // packed (token, head) rows per CTA
 constexpr int KT = 64;                // keys per tile
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int DMAX>
+// DMAX bounds the head size; with EXACT the head size is DMAX itself (index arithmetic
+// becomes shifts). page_shift >= 0: the page size is 1 << page_shift.
+template <int DMAX, bool EXACT>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                          bf16* __restrict__ out, const int* __restrict__ row_list, const int* __restrict__ cu_q,
                          const int* __restrict__ kv_len, const int* __restrict__ block_table, int max_pages,
-                         int page_size, int num_pages, int nq, int nkv, int d, float scale_log2, int window,
-                         unsigned* status) {
+                         int page_size, int page_shift, int num_pages, int nq, int nkv, int d_runtime,
+                         float scale_log2, int window, unsigned* status) {
   extern __shared__ __align__(16) uint8_t smem[];
+  const int d = EXACT ? DMAX : d_runtime;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = row_list ? row_list[blockIdx.z] : blockIdx.z;
   const int g = blockIdx.y;
@@ -63,6 +66,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     pos_row[r] = token < q_len ? shift + token : -1;     // -1: no key is visible, nothing is written
     kstart_row[r] = (window > 0 && pos_row[r] - window + 1 > 0) ? pos_row[r] - window + 1 : 0;
   }
+  // what the whole warp sees (its rows 0..15): used to skip tiles and masks
+  const int warp_token_lo = (row0 + warp * 16) / group, warp_token_hi = (row0 + warp * 16 + 15) / group;
+  const int warp_pos_max = warp_token_lo < q_len ? shift + min(warp_token_hi, q_len - 1) : -1;
+  const int warp_pos_min = warp_token_hi < q_len ? shift + warp_token_lo : -1;       // -1: some row is padding
+  const int warp_kstart_max = (window > 0 && warp_pos_max - window + 1 > 0) ? warp_pos_max - window + 1 : 0;
   const int token_lo = row0 / group, token_hi = min(q_len - 1, (row0 + ROWS - 1) / group);
   const int key_end = shift + token_hi + 1;              // exclusive
   const int first_key = (window > 0 && shift + token_lo - window + 1 > 0) ? shift + token_lo - window + 1 : 0;
@@ -79,13 +87,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       bool valid = key >= first_key && key < key_end;
       int64_t slot = 0;
       if (valid) {
-        const int index = key / page_size;
+        const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
         const int page = index < max_pages ? table[index] : -1;
         if (page < 0 || page >= num_pages) {
           raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
           valid = false;
         } else {
-          slot = (int64_t)page * page_size + key % page_size;
+          slot = (int64_t)page * page_size + (key - index * page_size);
         }
       }
       if (valid) {
@@ -119,6 +127,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     const uint8_t* ks = kv_s + buffer * (2 * KT * pitch);
     const uint8_t* vs = ks + KT * pitch;
     const int key0 = tile_begin + tile * KT;
+    // rows of this warp that see nothing of the tile skip its arithmetic
+    if (key0 > warp_pos_max) {
+      __syncthreads();
+      continue;
+    }
+    const bool need_mask = key0 + KT - 1 > warp_pos_min || key0 < warp_kstart_max;
 
     // ---- S = Q K^T: 16 rows x 64 keys per warp
     float s[KT / 8][4];
@@ -146,7 +160,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
         const int r = e >> 1;
-        const bool visible = key <= pos_row[r] && key >= kstart_row[r];
+        const bool visible = !need_mask || (key <= pos_row[r] && key >= kstart_row[r]);
         s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
         tile_max[r] = fmaxf(tile_max[r], s[nt][e]);
       }
@@ -231,21 +245,27 @@ VOSTI_API int vosti_attention_prefill(const void* q, const void* k_cache, const 
   const int64_t tiles = ((int64_t)max_q_len * group + ROWS - 1) / ROWS;
   dim3 grid((unsigned)tiles, nkv, count);
   const size_t smem = prefill_smem_bytes(d);
-#define LAUNCH_PREFILL(DMAX)                                                                                         \
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
+#define LAUNCH_PREFILL(DMAX, EXACT)                                                                                   \
   do {                                                                                                               \
     static bool configured = false;                                                                                  \
     if (!configured) {                                                                                               \
-      cudaFuncSetAttribute(attention_prefill_kernel<DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+      cudaFuncSetAttribute(attention_prefill_kernel<DMAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
                            (int)prefill_smem_bytes(DMAX));                                                           \
       configured = true;                                                                                             \
     }                                                                                                                \
-    attention_prefill_kernel<DMAX><<<grid, WARPS * 32, smem, stream>>>(                                              \
+    attention_prefill_kernel<DMAX, EXACT><<<grid, WARPS * 32, smem, stream>>>(                                        \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, row_list, cu_q, kv_len, block_table,  \
-        max_pages, page_size, num_pages, nq, nkv, d, scale * LOG2E, window, status);                                  \
+        max_pages, page_size, page_shift, num_pages, nq, nkv, d, scale * LOG2E, window, status);                      \
   } while (0)
-  if (d <= 64) LAUNCH_PREFILL(64);
-  else if (d <= 128) LAUNCH_PREFILL(128);
-  else LAUNCH_PREFILL(256);
+  if (d == 64) LAUNCH_PREFILL(64, true);
+  else if (d == 128) LAUNCH_PREFILL(128, true);
+  else if (d == 256) LAUNCH_PREFILL(256, true);
+  else if (d < 64) LAUNCH_PREFILL(64, false);
+  else if (d < 128) LAUNCH_PREFILL(128, false);
+  else LAUNCH_PREFILL(256, false);
 #undef LAUNCH_PREFILL
   VOSTI_LAUNCH_CHECK();
 }
