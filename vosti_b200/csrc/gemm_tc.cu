@@ -631,3 +631,73 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
   }
   VOSTI_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+// See no_alloc.h. The scratch of the K splits is this array instead of a caller's buffer.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_static_scratch[VOSTI_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_address[MAX_DEVICES] = {};   // device address of the array, per device
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel
+// can use; the device address comes from cudaGetSymbolAddress, per device.
+int static_scratch(float** out) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+    vosti_set_error("gemm_tc_split_static: no usable current device (%s)", cudaGetErrorString(e));
+    return e != cudaSuccess ? (int)e : VOSTI_UNSUPPORTED;
+  }
+  if (g_static_scratch_address[device] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      vosti_set_error("gemm_tc_split_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : VOSTI_UNSUPPORTED;
+    }
+    g_static_scratch_address[device] = p;
+  }
+  *out = g_static_scratch_address[device];
+  return VOSTI_OK;
+}
+}  // namespace
+
+VOSTI_API int vosti_gemm_tc_split_static(const void* x, const void* w, void* y, int tokens, int features, int k,
+                                         int y_is_f32, unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(x != nullptr && w != nullptr && y != nullptr, "gemm_tc_split_static: null operand");
+  VOSTI_REQUIRE(tokens >= 1 && tokens <= 128, "gemm_tc_split_static: tokens must be 1..128, got %d", tokens);
+  VOSTI_REQUIRE(vosti_gemm_tc_supported(features, k), "gemm_tc_split_static: unsupported sizes F=%d K=%d", features, k);
+  VOSTI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc_split_static: operands must be 16-byte aligned");
+  const int splits = vosti_gemm_tc_splits(tokens, features, k);
+  const int64_t need = splits > 1 ? (int64_t)splits * tokens * features : 0;
+  VOSTI_REQUIRE(need <= (int64_t)VOSTI_STATIC_SCRATCH_FLOATS,
+                "gemm_tc_split_static: %d splits x %d tokens x %d features need %lld scratch floats, the static array "
+                "holds %d", splits, tokens, features, (long long)need, VOSTI_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  const int rc_scratch = static_scratch(&scratch);
+  if (rc_scratch != VOSTI_OK) return rc_scratch;
+  const int epilogue = y_is_f32 ? EPI_F32 : EPI_BF16;
+  const int k_blocks = (k + BK - 1) / BK;
+  const int bn = token_tile(tokens);
+  CUtensorMap mw, mx;                       // encoded on the stack: no cache, nothing allocated
+  VOSTI_REQUIRE(make_map(&mw, w, features, k, BM) && make_map(&mx, x, tokens, k, bn),
+                "gemm_tc_split_static: cuTensorMapEncodeTiled failed");
+  void* dst = splits > 1 ? (void*)scratch : y;
+  const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
+  int rc;
+  switch (bn) {
+    case 32: rc = launch<32, 5>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, status, stream); break;
+    case 64: rc = launch<64, 4>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, status, stream); break;
+    default: rc = launch<128, 6>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, status, stream); break;
+  }
+  if (rc != 0) return rc;
+  if (splits > 1) {
+    const int64_t n = (int64_t)tokens * features;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(scratch, y, splits, tokens, features, features, epilogue);
+  }
+  VOSTI_LAUNCH_CHECK();
+}
