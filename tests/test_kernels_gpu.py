@@ -400,3 +400,46 @@ def test_attention_decode_is_independent_of_the_batch(dev, status):
                          request_of=case["request_of"].to(dev), block_table=case["table"].to(dev), page_size=page,
                          nq=nq, nkv=nkv, head_dim=d, max_kv_len=1000, scale=d ** -0.5, window=0, status=status)
     assert torch.equal(out[3], full[3]) and torch.equal(out[1], full[1]) and out[0].abs().max() == 0
+
+
+def test_deferred_split_sums_feed_the_norm_and_the_head_kernel(dev, status):
+    """A split-K product may hand its unsummed splits to the fused add + RMSNorm or to the
+    head-norm / rotation kernel; the results equal the unfused order of operations."""
+    from vosti_b200 import ops
+    tokens, k, width = 8, 4096, 1024
+    x = torch.randn(tokens, k, device=dev).bfloat16()
+    w = (torch.randn(width, k, device=dev) / 64).bfloat16()
+    res = torch.randn(tokens, width, device=dev).bfloat16()
+    nw = (1 + 0.1 * torch.randn(width, device=dev)).bfloat16()
+    deferred = ops.gemm_tc(x, w, status, allow_partial=True)
+    assert isinstance(deferred, ops.PartialSum) and deferred.splits > 1
+    assert torch.equal(deferred.materialize(), ops.gemm_tc(x, w, status))
+    deferred = ops.gemm_tc(x, w, status, allow_partial=True)
+    r1 = res.clone()
+    normed, _ = ops.rmsnorm(deferred, nw, 1e-6, residual=r1, residual_out=r1)
+    y = x.double() @ w.double().T
+    h = y + res.double()
+    want = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + 1e-6) * nw.double()
+    assert torch.allclose(r1.double(), h, atol=2e-2, rtol=2e-2) and torch.allclose(normed.double(), want, atol=3e-2, rtol=3e-2)
+    plain_norm, _ = ops.rmsnorm(ops.gemm_tc(x, w, status, allow_partial=True), nw, 1e-6)
+    want = y * torch.rsqrt((y * y).mean(-1, keepdim=True) + 1e-6) * nw.double()
+    assert torch.allclose(plain_norm.double(), want, atol=3e-2, rtol=3e-2)
+    # a stale deferred result is refused
+    stale = ops.gemm_tc(x, w, status, allow_partial=True)
+    ops.gemm_tc(x, w, status)
+    with pytest.raises(ops.KernelError, match="overwrote"):
+        stale.materialize()
+    # the head kernel: same q and cache as from the summed projection
+    nq, nkv, d = 4, 2, 128
+    w2 = (torch.randn((nq + 2 * nkv) * d, k, device=dev) / 64).bfloat16()
+    kc1, vc1 = torch.zeros(32, nkv, d, device=dev).bfloat16(), torch.zeros(32, nkv, d, device=dev).bfloat16()
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    qw = torch.ones(d, device=dev).bfloat16()
+    c, s_ = plain.rope_tables(torch.arange(64), d, 1e4)
+    args = dict(nq=nq, nkv=nkv, head_dim=d, q_norm_w=qw, k_norm_w=qw, eps=1e-6, cos=c.to(dev), sin=s_.to(dev),
+                positions=torch.arange(tokens, dtype=torch.int32, device=dev),
+                slot_mapping=torch.arange(tokens, dtype=torch.int32, device=dev), status=status)
+    q1 = ops.qkv_post(ops.gemm_tc(x, w2, status), kc1, vc1, **args)
+    q2 = ops.qkv_post(ops.gemm_tc(x, w2, status, allow_partial=True), kc2, vc2, **args)
+    assert torch.allclose(q1.float(), q2.float(), atol=2e-2, rtol=2e-2)
+    assert torch.allclose(kc1.float(), kc2.float(), atol=2e-2, rtol=2e-2) and torch.allclose(vc1.float(), vc2.float(), atol=2e-2)

@@ -574,8 +574,11 @@ VOSTI_API int vosti_gemm_tc_splits(int tokens, int features, int k) {
 // x: [tokens, k] bf16; w: [features, k] bf16; epilogue 0: y bf16 [tokens, features];
 // 1: y float32 [tokens, features]; 2: y bf16 [tokens, features / 2] = silu(gate) * up with
 // the weight rows interleaved in blocks of 16 gate rows and their 16 up rows.
+// With `defer_reduce` and more than one split the partial sums stay in the workspace
+// ([splits, tokens, features] float32) for a consumer that sums them itself; y is not written.
 VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, int features, int k, int epilogue,
-                            float* workspace, int64_t workspace_elems, unsigned* status, cudaStream_t stream) {
+                            float* workspace, int64_t workspace_elems, int defer_reduce, unsigned* status,
+                            cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && vosti_gemm_tc_supported(features, k), "gemm_tc: unsupported sizes F=%d K=%d", features, k);
   VOSTI_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "gemm_tc: unknown epilogue %d", epilogue);
   VOSTI_REQUIRE(epilogue != EPI_SWIGLU || features % 32 == 0, "gemm_tc: fused SiLU*up needs features %% 32 == 0");
@@ -624,11 +627,24 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
     default: rc = launch<256, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
   }
   if (rc != 0) return rc;
-  if (splits > 1) {
+  if (splits > 1 && !defer_reduce) {
     const int64_t n = (int64_t)tokens * features;
     const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
     splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(workspace, y, splits, tokens, features, ld_out, epilogue);
   }
+  VOSTI_LAUNCH_CHECK();
+}
+
+// Sum deferred partial sums ([splits, tokens, features] float32) in split order into y
+// (bf16 or float32 [tokens, features]).
+VOSTI_API int vosti_splitk_reduce(const float* partial, void* y, int splits, int tokens, int features, int y_is_f32,
+                                  cudaStream_t stream) {
+  VOSTI_REQUIRE(splits >= 1 && tokens >= 0 && features >= 1, "splitk_reduce: bad sizes");
+  if (tokens == 0) return VOSTI_OK;
+  const int64_t n = (int64_t)tokens * features;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, y, splits, tokens, features, features,
+                                                   y_is_f32 ? EPI_F32 : EPI_BF16);
   VOSTI_LAUNCH_CHECK();
 }
 

@@ -14,7 +14,8 @@ constexpr int MAX_PAIRS_PER_LANE = 8;  // head_dim <= 512
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache,
+qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, int splits, int64_t plane,
+                T* __restrict__ q_out, T* __restrict__ k_cache,
                 T* __restrict__ v_cache, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
                 int norm_w_is_f32, float eps, const float* __restrict__ cos_table,
                 const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
@@ -42,6 +43,14 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
 
   for (int h = blockIdx.y * nwarps + warp; h < heads; h += gridDim.y * nwarps) {
     const T* src = qkv + in_base + (int64_t)h * d;
+    const float* psrc = partial ? partial + in_base + (int64_t)h * d : nullptr;
+    // element i of this head: the stored projection, or the sum of its K-split partial sums
+    auto load = [&](int i) -> float {
+      if (partial == nullptr) return to_f32(src[i]);
+      float v = 0.f;
+      for (int s = 0; s < splits; ++s) v += psrc[s * plane + i];
+      return v;
+    };
     const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
     T* dst;
     if (is_q) {
@@ -52,22 +61,35 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
       dst = (is_k ? k_cache : v_cache) + (slot * nkv + g) * d;
     }
     if (!is_q && !is_k) {  // value head: plain copy
-      for (int i = lane; i < d; i += 32) dst[i] = src[i];
+      for (int i = lane; i < d; i += 32) dst[i] = partial == nullptr ? src[i] : from_f32<T>(load(i));
       continue;
     }
     float x1[MAX_PAIRS_PER_LANE], x2[MAX_PAIRS_PER_LANE];
     float ss = 0.f;
+    if (partial == nullptr) {
 #pragma unroll
-    for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
-      const int i = lane + 32 * j;
-      if (i < half) {
-        x1[j] = to_f32(src[i]);
-        x2[j] = to_f32(src[i + half]);
-        ss += x1[j] * x1[j] + x2[j] * x2[j];
-      } else {
-        x1[j] = x2[j] = 0.f;
+      for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
+        const int i = lane + 32 * j;
+        x1[j] = i < half ? to_f32(src[i]) : 0.f;
+        x2[j] = i < half ? to_f32(src[i + half]) : 0.f;
+      }
+    } else {
+      // splits outermost so that the loads of one split are independent of each other
+#pragma unroll
+      for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) x1[j] = x2[j] = 0.f;
+      for (int s = 0; s < splits; ++s) {
+#pragma unroll
+        for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
+          const int i = lane + 32 * j;
+          if (i < half) {
+            x1[j] += psrc[s * plane + i];
+            x2[j] += psrc[s * plane + i + half];
+          }
+        }
       }
     }
+#pragma unroll
+    for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) ss += x1[j] * x1[j] + x2[j] * x2[j];
     const void* w = is_q ? q_norm_w : k_norm_w;
     float rrms = 1.f;
     if (w) rrms = rsqrtf(warp_sum(ss) / (float)d + eps);
@@ -93,16 +115,21 @@ qkv_post_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict_
 }
 }  // namespace
 
-// qkv: [tokens, (nq + 2*nkv) * d]; q_out: [tokens, nq * d]; caches: [num_slots, nkv, d].
+// qkv: [tokens, (nq + 2*nkv) * d], or null with `partial`: float32 [splits, tokens, (nq + 2*nkv) * d],
+// the K-split partial sums of the projection, summed here in split order.
+// q_out: [tokens, nq * d]; caches: [num_slots, nkv, d].
 // nkv == 0: the input holds query heads only and nothing is stored.
 // q_norm_w / k_norm_w null: no head norm. cos/sin null: no rotation; else float32
 // tables [max_positions, d/2].
-VOSTI_API int vosti_qkv_post(const void* qkv, void* q_out, void* k_cache, void* v_cache, const void* q_norm_w,
+VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, void* q_out, void* k_cache, void* v_cache, const void* q_norm_w,
                              const void* k_norm_w, int norm_w_is_f32, float eps, const float* cos_table,
                              const float* sin_table, int max_positions, const int* positions,
                              const int* slot_mapping, int64_t num_slots, int tokens, int nq, int nkv, int d,
                              int is_f32, unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && d > 0, "qkv_post: bad sizes");
+  VOSTI_REQUIRE((qkv != nullptr) != (partial != nullptr), "qkv_post: give the projection or its partial sums");
+  VOSTI_REQUIRE(partial == nullptr || splits >= 1, "qkv_post: bad split count");
+  const int64_t plane = (int64_t)tokens * (nq + 2 * nkv) * d;
   VOSTI_REQUIRE(d % 2 == 0 && d / 2 <= 32 * MAX_PAIRS_PER_LANE, "qkv_post: head_dim %d must be even and <= %d", d,
                 64 * MAX_PAIRS_PER_LANE);
   VOSTI_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "qkv_post: cos and sin go together");
@@ -111,11 +138,11 @@ VOSTI_API int vosti_qkv_post(const void* qkv, void* q_out, void* k_cache, void* 
   const int heads = nq + 2 * nkv;
   const dim3 grid(tokens, tokens >= 2048 ? 1 : (heads + 3) / 4);   // few tokens: a warp per (token, head)
   if (is_f32)
-    qkv_post_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_cache,
+    qkv_post_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, partial, splits, plane, (float*)q_out, (float*)k_cache,
         (float*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
         slot_mapping, num_slots, nq, nkv, d, status);
   else
-    qkv_post_kernel<bf16><<<grid, 128, 0, stream>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+    qkv_post_kernel<bf16><<<grid, 128, 0, stream>>>((const bf16*)qkv, partial, splits, plane, (bf16*)q_out, (bf16*)k_cache,
         (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
         slot_mapping, num_slots, nq, nkv, d, status);
   VOSTI_LAUNCH_CHECK();

@@ -84,6 +84,79 @@ VOSTI_API int vosti_rmsnorm(const void* x, const void* residual, const void* wei
   VOSTI_LAUNCH_CHECK();
 }
 
+// The same norm fed by the float32 partial sums of a split-K product: x[t, i] is the sum of
+// `splits` planes of [rows, width] taken in split order; it is not rounded before the add.
+template <typename T, int BLOCK>
+__global__ void __launch_bounds__(BLOCK)
+rmsnorm_partial_kernel(const float* __restrict__ partial, int splits, int64_t plane, const T* __restrict__ residual,
+                       const void* __restrict__ weight, int weight_is_f32, T* __restrict__ out,
+                       T* __restrict__ residual_out, int width, float eps) {
+  __shared__ float scratch[32];
+  extern __shared__ float row_sum[];                       // the summed row, kept for the second pass
+  const int64_t base = (int64_t)blockIdx.x * width;
+  constexpr int GROUP = 4;                                 // elements a thread sums at once: independent loads
+  float ss = 0.f;
+  for (int i0 = threadIdx.x; i0 < width; i0 += BLOCK * GROUP) {
+    float h[GROUP];
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) h[j] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+#pragma unroll
+      for (int j = 0; j < GROUP; ++j) {
+        const int i = i0 + j * BLOCK;
+        if (i < width) h[j] += partial[s * plane + base + i];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) {
+      const int i = i0 + j * BLOCK;
+      if (i < width) {
+        if (residual) h[j] += to_f32(residual[base + i]);
+        row_sum[i] = h[j];
+        ss += h[j] * h[j];
+      }
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float rrms = rsqrtf(total / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += BLOCK) {
+    const float h = row_sum[i];
+    if (residual_out) residual_out[base + i] = from_f32<T>(h);
+    out[base + i] = from_f32<T>(h * rrms * load_flex(weight, weight_is_f32, i));
+  }
+}
+
+// partial: float32 [splits, rows, width]; residual may be null; residual_out may be residual.
+VOSTI_API int vosti_rmsnorm_partial(const float* partial, int splits, const void* residual, const void* weight,
+                                    int weight_is_f32, void* out, void* residual_out, int rows, int width, float eps,
+                                    int is_f32, cudaStream_t stream) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0 && splits >= 1, "rmsnorm_partial: bad sizes rows=%d width=%d splits=%d", rows, width, splits);
+  VOSTI_REQUIRE(eps > 0.f, "rmsnorm_partial: eps must be positive");
+  VOSTI_REQUIRE(width <= 24576, "rmsnorm_partial: width %d does not fit the row buffer", width);
+  if (rows == 0) return VOSTI_OK;
+  VOSTI_REQUIRE(out != residual && out != residual_out, "rmsnorm_partial: out must not alias another operand");
+  const int64_t plane = (int64_t)rows * width;
+  const size_t smem = (size_t)width * sizeof(float);
+  if (is_f32) {
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(rmsnorm_partial_kernel<float, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 24576 * 4);
+      configured = true;
+    }
+    rmsnorm_partial_kernel<float, 1024><<<rows, 1024, smem, stream>>>(partial, splits, plane, (const float*)residual, weight,
+        weight_is_f32, (float*)out, (float*)residual_out, width, eps);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(rmsnorm_partial_kernel<bf16, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 24576 * 4);
+      configured = true;
+    }
+    rmsnorm_partial_kernel<bf16, 1024><<<rows, 1024, smem, stream>>>(partial, splits, plane, (const bf16*)residual, weight,
+        weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
+  }
+  VOSTI_LAUNCH_CHECK();
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 // in: [rows, 2*inter] with the gate half first; out: [rows, inter].
 template <typename T>

@@ -101,7 +101,7 @@ class DecoderModel:
     def logits(self, ctx, hidden: torch.Tensor, residual: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] of the rows (flat token indices) asked for:
         only those rows are gathered, added, normed and multiplied with the head."""
-        hidden = ops.gather_rows(hidden, rows, ctx.status)
+        hidden = ops.gather_rows(ops.materialize(hidden), rows, ctx.status)
         if residual is None:
             final = self.final_norm.forward(ctx, hidden)
         else:

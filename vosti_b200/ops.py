@@ -99,6 +99,18 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
             residual: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None):
     """out = rmsnorm(x [+ residual]) * weight; with `residual` the sum is written to
     `residual_out` (which may be `residual` itself). Returns (out, residual_out)."""
+    if isinstance(x, PartialSum):
+        x.check()
+        _contig(weight, residual, residual_out)
+        like = residual if residual is not None else None
+        out = torch.empty((x.rows, x.width), dtype=x.dtype, device=x.partial.device)
+        flag = _is_f32(out)
+        if like is not None and _is_f32(like) != flag:
+            raise KernelError("activation tensors of one call must share a dtype")
+        _check(library().vosti_rmsnorm_partial(_p(x.partial), x.splits, _p(residual), _p(weight), _is_f32(weight),
+                                               _p(out), _p(residual_out), x.rows, x.width, ctypes.c_float(eps), flag,
+                                               _stream()), "rmsnorm_partial")
+        return out, residual_out
     _contig(x, weight, residual, residual_out)
     flag = _same_dtype(x, residual, residual_out)
     out = torch.empty_like(x)
@@ -138,13 +150,23 @@ def qkv_post(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Option
              k_norm_w: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
              sin: Optional[torch.Tensor], positions: Optional[torch.Tensor],
              slot_mapping: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:
-    """Head norm, rotation and cache store after the QKV projection; returns q [T, nq*d]."""
+    """Head norm, rotation and cache store after the QKV projection; returns q [T, nq*d].
+    `qkv` may be the projection or the unsummed partial sums of its split-K product."""
+    partial, splits = None, 0
+    if isinstance(qkv, PartialSum):
+        qkv.check()
+        partial, splits = qkv.partial, qkv.splits
+        proxy = torch.empty((0,), dtype=qkv.dtype, device=partial.device)
+        tokens, width, dtype, device = qkv.rows, qkv.width, qkv.dtype, partial.device
+        qkv = None
+    else:
+        proxy = qkv
+        tokens, width, dtype, device = qkv.shape[0], qkv.shape[1], qkv.dtype, qkv.device
     _contig(qkv, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, positions, slot_mapping)
-    tokens = qkv.shape[0]
-    if qkv.shape[1] != (nq + 2 * nkv) * head_dim:
+    if width != (nq + 2 * nkv) * head_dim:
         raise KernelError("qkv_post: input width does not match the head counts")
-    flag = _same_dtype(qkv, k_cache, v_cache)
-    q_out = torch.empty((tokens, nq * head_dim), dtype=qkv.dtype, device=qkv.device)
+    flag = _same_dtype(proxy, k_cache, v_cache)
+    q_out = torch.empty((tokens, nq * head_dim), dtype=dtype, device=device)
     num_slots = 0 if k_cache is None else k_cache.numel() // (nkv * head_dim)
     norm_flag = 0
     if q_norm_w is not None:
@@ -157,7 +179,7 @@ def qkv_post(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Option
     if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != head_dim // 2):
         raise KernelError("qkv_post: rotation tables must be float32 [positions, head_dim/2]")
     _check(library().vosti_qkv_post(
-        _p(qkv), _p(q_out), _p(k_cache), _p(v_cache), _p(q_norm_w), _p(k_norm_w), norm_flag,
+        _p(qkv), _p(partial), splits, _p(q_out), _p(k_cache), _p(v_cache), _p(q_norm_w), _p(k_norm_w), norm_flag,
         ctypes.c_float(eps), _p(cos), _p(sin), max_positions, _p(positions), _p(slot_mapping),
         ctypes.c_int64(num_slots), tokens, nq, nkv, head_dim, flag, _p(status), _stream()), "qkv_post")
     return q_out
@@ -204,10 +226,10 @@ _WORKSPACES = {}
 WORKSPACE_GENERATION = 0   # bumped whenever a scratch buffer moves (captured graphs hold its address)
 
 
-def _workspace(device: torch.device, elems: int) -> torch.Tensor:
-    """float32 scratch of the split-K product, one per device, grown on demand. Kernels on
-    one stream use it one after the other."""
-    key = (device.type, device.index)
+def _workspace(device: torch.device, elems: int, purpose: str = "attention") -> torch.Tensor:
+    """float32 scratch, one per device and purpose, grown on demand. Kernels on one stream
+    use it one after the other."""
+    key = (device.type, device.index, purpose)
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < elems:
         global WORKSPACE_GENERATION
@@ -218,10 +240,43 @@ def _workspace(device: torch.device, elems: int) -> torch.Tensor:
 
 
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+_SPLIT_GENERATION = 0   # counts split-K products: a PartialSum is valid until the next one runs
+
+
+class PartialSum:
+    """The result of a split-K product whose splits have not been summed yet: float32
+    [splits, rows, width] in the split-K scratch. A consumer that can add the splits itself
+    (the fused add + RMSNorm, the head norm / rotation kernel) takes it as it is; anything else
+    calls `materialize`. It must be consumed before the next split-K product runs."""
+
+    def __init__(self, partial: torch.Tensor, splits: int, rows: int, width: int, dtype: torch.dtype,
+                 status: torch.Tensor):
+        self.partial, self.splits, self.rows, self.width, self.dtype = partial, splits, rows, width, dtype
+        self.status = status
+        self.generation = _SPLIT_GENERATION
+
+    @property
+    def shape(self):
+        return (self.rows, self.width)
+
+    def check(self) -> None:
+        if self.generation != _SPLIT_GENERATION:
+            raise KernelError("a deferred split-K result was used after a later split-K product overwrote it")
+
+    def materialize(self) -> torch.Tensor:
+        self.check()
+        out = torch.empty((self.rows, self.width), dtype=self.dtype, device=self.partial.device)
+        _check(library().vosti_splitk_reduce(_p(self.partial), _p(out), self.splits, self.rows, self.width,
+                                             _is_f32(out), _stream()), "splitk_reduce")
+        return out
+
+
+def materialize(x):
+    return x.materialize() if isinstance(x, PartialSum) else x
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
-            swiglu: bool = False) -> torch.Tensor:
+            swiglu: bool = False, allow_partial: bool = False):
     """y = x @ w.T on the tensor cores (bfloat16 operands, float32 accumulation). With
     `swiglu` the rows of w are blocks of 16 gate rows followed by their 16 up rows and
     y = silu(gate) * up has half as many columns."""
@@ -239,14 +294,20 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, *, out_dtype
             raise KernelError("gemm_tc: the fused SiLU*up epilogue writes bfloat16")
     else:
         epilogue, width = (EPI_F32 if out_dtype == torch.float32 else EPI_BF16), features
-    out = torch.empty((tokens, width), dtype=out_dtype, device=x.device)
+    global _SPLIT_GENERATION
     lib = library()
     splits = lib.vosti_gemm_tc_splits(tokens, features, k)
     elems = splits * tokens * features if splits > 1 else 0
-    ws = _workspace(x.device, elems) if elems else None
+    ws = _workspace(x.device, elems, "split_k") if elems else None
+    defer = bool(allow_partial and splits > 1 and epilogue == EPI_BF16)
+    out = None if defer else torch.empty((tokens, width), dtype=out_dtype, device=x.device)
+    if splits > 1:
+        _SPLIT_GENERATION += 1
     _check(lib.vosti_gemm_tc(_p(x), _p(w), _p(out), tokens, features, k, epilogue, _p(ws),
-                             ctypes.c_int64(ws.numel() if ws is not None else 0), _p(status), _stream()),
-           "gemm_tc", kernels=2 if splits > 1 else 1)
+                             ctypes.c_int64(ws.numel() if ws is not None else 0), int(defer), _p(status), _stream()),
+           "gemm_tc", kernels=2 if splits > 1 and not defer else 1)
+    if defer:
+        return PartialSum(ws, splits, tokens, features, out_dtype, status)
     return out
 
 

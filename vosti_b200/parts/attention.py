@@ -79,7 +79,7 @@ class Attention(Mixer):
         common = dict(nq=self.nq, head_dim=self.d, q_norm_w=self.q_norm, eps=eps, cos=cos, sin=sin,
                       positions=ctx.positions, status=ctx.status)
         if writes_cache:
-            qkv = linear(ctx, x, self.w_qkv)
+            qkv = linear(ctx, x, self.w_qkv, allow_partial=True)   # summed inside qkv_post
             q = ops.qkv_post(qkv, cache.k, cache.v, nkv=self.nkv, k_norm_w=self.k_norm,
                              slot_mapping=group.slot_mapping, **common)
         else:
@@ -87,7 +87,7 @@ class Attention(Mixer):
                              slot_mapping=None, **common)
         attn = ops.attention(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, head_dim=self.d,
                              scale=self.scale, window=self.window)
-        return linear(ctx, attn, self.w_o)
+        return linear(ctx, attn, self.w_o, allow_partial=True)       # summed by the norm that follows
 
 
 register_part("mixer", "attention", Attention, replace=True)

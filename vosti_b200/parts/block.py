@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from typing import Dict
 
+from .. import ops
 from ..config.schema import ConfigError, LayerSpec
 from ..weights.loader import WeightSpec
 from .base import build_feed_forward, build_mixer, build_norm, part_factory, register_part
@@ -46,11 +47,13 @@ class PreNormBlock:
 
     def forward(self, ctx, hidden, residual, cache, writes_cache=True):
         if residual is None:
-            residual = hidden
+            residual = hidden = ops.materialize(hidden)
             normed = self.input_norm.forward(ctx, hidden)
         else:
             normed, residual = self.input_norm.forward_add(ctx, hidden, residual)
         out = self.mixer.forward(ctx, normed, cache, writes_cache)
+        # (a mixer or feed-forward may return its last product as unsummed K splits; the
+        # norm that follows adds them, see ops.PartialSum)
         if self.feed_forward is not None:
             normed, residual = self.post_norm.forward_add(ctx, out, residual)
             out = self.feed_forward.forward(ctx, normed)

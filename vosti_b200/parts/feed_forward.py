@@ -50,10 +50,10 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, x):
         if self.fused:
-            mlp = ops.gemm_tc(x, self.w_gate_up, ctx.status, swiglu=True)
+            mlp = ops.gemm_tc(ops.materialize(x), self.w_gate_up, ctx.status, swiglu=True)
         else:
             mlp = ops.silu_mul(linear(ctx, x, self.w_gate_up))
-        return linear(ctx, mlp, self.w_down)
+        return linear(ctx, mlp, self.w_down, allow_partial=True)     # summed by the norm that follows
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -20,9 +20,13 @@ def uses_tensor_cores(x_dtype: torch.dtype, w: torch.Tensor) -> bool:
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
-           row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+           row_index: Optional[torch.Tensor] = None, allow_partial: bool = False):
+    """y = x @ w.T. With `allow_partial` the result may come back as an `ops.PartialSum` (the
+    K splits not yet summed) for a consumer that adds them itself; the caller must hand it to
+    such a consumer, or to `ops.materialize`, before any other product runs."""
+    x = ops.materialize(x)
     if uses_tensor_cores(x.dtype, w):
         if row_index is not None:
             x = ops.gather_rows(x, row_index, ctx.status)
-        return ops.gemm_tc(x, w, ctx.status, out_dtype=out_dtype)
+        return ops.gemm_tc(x, w, ctx.status, out_dtype=out_dtype, allow_partial=allow_partial)
     return ops.gemm_simt(x, w, ctx.status, out_dtype=out_dtype, row_index=row_index)
