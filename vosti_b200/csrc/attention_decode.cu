@@ -58,15 +58,6 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
   uint8_t* stage_base = smem + 16 * pitch + warp * (2 * WARP_TILES * TILE * pitch);   // per warp: tiles x (K, V)
   const int chunks = d / 8;                         // 16-byte chunks per row
 
-  // ---- Q rows of the group (rows >= group are zero)
-  for (int i = threadIdx.x; i < 16 * chunks; i += WARPS * 32) {
-    const int row = i / chunks, c = i % chunks;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < group) v = *reinterpret_cast<const uint4*>(q + ((int64_t)t * nq + g * group + row) * d + c * 8);
-    *reinterpret_cast<uint4*>(q_s + row * pitch + c * 16) = v;
-  }
-  __syncthreads();
-
   const int my_begin = seg_begin + warp * WARP_KEYS;
   const int my_end = min(my_begin + WARP_KEYS, seg_end);
   const int first_tile = max(my_begin, (kstart / TILE) * TILE);       // tiles stay aligned to the key index
@@ -109,6 +100,15 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 
   static_assert(WARP_TILES == 2, "the wait below counts two outstanding groups");
   for (int tile = 0; tile < tiles; ++tile) issue(tile);           // everything is requested up front
+  // ---- Q rows of the group (rows >= group are zero)
+  for (int i = threadIdx.x; i < 16 * chunks; i += WARPS * 32) {
+    const int row = i / chunks, c = i % chunks;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < group) v = *reinterpret_cast<const uint4*>(q + ((int64_t)t * nq + g * group + row) * d + c * 8);
+    *reinterpret_cast<uint4*>(q_s + row * pitch + c * 16) = v;
+  }
+  __syncthreads();                                                  // (the K/V requests above are in flight meanwhile)
+
   for (int tile = 0; tile < tiles; ++tile) {
     if (tile + 1 < tiles) cp_async_wait<1>();
     else cp_async_wait<0>();
@@ -261,14 +261,25 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
       }
     }
     const int n = min(32, last - s0 + 1);
-    for (int j = 0; j < n; ++j) {
-      const float w = __shfl_sync(0xffffffffu, w_mine, j);
-      l += __shfl_sync(0xffffffffu, l_mine, j);
-      const float* row = base + (int64_t)(s0 + j) * rec + 2;
+    // segments in batches of 4: their loads are issued together, then summed in segment order
+    for (int j0 = 0; j0 < n; j0 += 4) {
+      float v[4][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = lane + 32 * i;
-        if (c < d) acc[i] = fmaf(row[c], w, acc[i]);
+      for (int b = 0; b < 4; ++b) {
+        const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = lane + 32 * i;
+          v[b][i] = (c < d) ? row[c] : 0.f;
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const bool live = j0 + b < n;
+        const float w = live ? __shfl_sync(0xffffffffu, w_mine, (j0 + b) & 31) : 0.f;
+        l += live ? __shfl_sync(0xffffffffu, l_mine, (j0 + b) & 31) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[b][i], w, acc[i]);
       }
     }
   }
