@@ -42,6 +42,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
                         int nq, int nkv, int d_runtime, int max_segments, float scale_log2, int window, unsigned* status) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   const int d = EXACT ? DMAX : d_runtime;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = token_list ? token_list[blockIdx.z] : blockIdx.z;
@@ -227,6 +229,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
                                        const int* __restrict__ token_list, const int* __restrict__ positions,
                                        int count, int nq, int d, int max_segments, int window) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= (int64_t)count * nq) return;
@@ -338,7 +342,7 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
                            (int)decode_smem_bytes(DMAX));                                                           \
       configured = true;                                                                                            \
     }                                                                                                               \
-    attention_decode_kernel<DMAX, EXACT><<<grid, WARPS * 32, smem, stream>>>(                                       \
+    vosti_launch(attention_decode_kernel<DMAX, EXACT>, grid, dim3(WARPS * 32), smem, stream,                        \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, scratch, token_list, positions, request_of,      \
         block_table, max_pages, page_size, num_pages, nq, nkv, d, segments, scale * LOG2E, window, status);          \
   } while (0)
@@ -350,7 +354,7 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   else LAUNCH_DECODE(256, false);
 #undef LAUNCH_DECODE
   const int64_t warps = (int64_t)count * nq;
-  attention_merge_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(scratch, (bf16*)out, token_list, positions,
-                                                                         count, nq, d, segments, window);
+  vosti_launch(attention_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)scratch,
+               (bf16*)out, token_list, positions, count, nq, d, segments, window);
   VOSTI_LAUNCH_CHECK();
 }

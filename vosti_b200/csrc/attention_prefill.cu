@@ -33,6 +33,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          int page_size, int page_shift, int num_pages, int nq, int nkv, int d_runtime,
                          float scale_log2, int window, unsigned* status) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int WARP_ROWS = 16 * MT, ROWS = WARPS * WARP_ROWS;
   const int d = EXACT ? DMAX : d_runtime;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -301,7 +303,7 @@ VOSTI_API int vosti_attention_prefill(const void* q, const void* k_cache, const 
                            (int)prefill_smem_bytes(DMAX));                                                           \
       configured = true;                                                                                             \
     }                                                                                                                \
-    attention_prefill_kernel<DMAX, EXACT, MT><<<grid, WARPS * 32, smem, stream>>>(                                        \
+    vosti_launch(attention_prefill_kernel<DMAX, EXACT, MT>, grid, dim3(WARPS * 32), smem, stream,                     \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, row_list, cu_q, kv_len, block_table,  \
         max_pages, page_size, page_shift, num_pages, nq, nkv, d, scale * LOG2E, window, status);                      \
   } while (0)

@@ -104,3 +104,33 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ void raise_fault(unsigned* status, unsigned bit) {
   if (status) atomicOr(status, bit);
 }
+
+// ---------------------------------------------------------------- dependent launches
+// Kernels of the serving path are launched with programmatic stream serialization: a
+// kernel may be scheduled while its predecessor in the stream is still running, runs
+// whatever does not depend on the predecessor (set-up, and for the products the first
+// weight tiles), and calls pdl_wait() before it touches anything the predecessor wrote or
+// still reads. pdl_wait() returns once the predecessor grid has completed and its memory
+// operations are visible; without the launch attribute it returns at once. Every kernel
+// launched through vosti_launch must call pdl_wait() on every path before its first access
+// to global memory that another kernel writes.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+int vosti_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t vosti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = vosti_pdl_enabled() ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}

@@ -1,6 +1,7 @@
 // Last-error text of the launchers (thread-local), and the library's version probe.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -24,3 +25,17 @@ VOSTI_API int vosti_device_sm(int device) {
   if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return -1;
   return prop.major * 10 + prop.minor;
 }
+
+// Dependent launches (see common.cuh) are on unless VOSTI_PDL=0 is set or they are switched
+// off through vosti_set_pdl.
+static int g_pdl = -1;
+
+int vosti_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* env = getenv("VOSTI_PDL");
+    g_pdl = (env != nullptr && env[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+
+VOSTI_API void vosti_set_pdl(int enabled) { g_pdl = enabled ? 1 : 0; }

@@ -163,12 +163,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_holder;
 
+  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < my_blocks; ++i) {
+      // The weight tiles of the first stages do not depend on the kernel before this one:
+      // they are requested at once, the token tiles after that kernel has completed.
+      const int ahead = my_blocks < STAGES ? my_blocks : STAGES;
+      for (int i = 0; i < ahead; ++i) {
+        const uint32_t bar = smem_u32(&full_bar[i]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb_begin + i) * BK, m0, bar);
+      }
+      pdl_wait();
+      for (int i = 0; i < ahead; ++i)
+        tma_load_2d(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, &map_x, (kb_begin + i) * BK, n0, smem_u32(&full_bar[i]));
+      for (int i = ahead; i < my_blocks; ++i) {
         const int s = i % STAGES;
         const uint32_t round = i / STAGES;
-        if (i >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, &abort_flag, status)) break;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, &abort_flag, status)) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
         mbar_expect_tx(bar, STAGE_BYTES);
         const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
@@ -200,6 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // epilogue: this warp may read the 32 accumulator lanes of its quarter only
     const int quarter = warp & 3;
+    pdl_wait();                                       // the output may still be read by the kernel before
     bool ok = my_blocks > 0 ? mbar_wait(smem_u32(&accum_bar), 0, &abort_flag, status) : true;
     tc_fence_after();
     const int feature = m0 + quarter * 32 + lane;
@@ -311,10 +324,12 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_holder;
 
+  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      pdl_wait();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * WIDE_BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -361,6 +376,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int quarter = warp & 3;
     uint32_t local = 0;
     bool ok = true;
+    pdl_wait();
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * WIDE_BN;
       const uint32_t as = local & 1;
@@ -446,6 +462,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // Sum the K splits in split order and apply the epilogue.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int splits,
                                      int tokens, int features, int ld_out, int epilogue) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t plane = (int64_t)tokens * features;
   if (epilogue == EPI_SWIGLU) {
     const int64_t n = (int64_t)tokens * (features / 2);
@@ -549,7 +567,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
     configured = true;
   }
   dim3 grid((features + BM - 1) / BM, (tokens + BN - 1) / BN, splits);
-  gemm_tc_kernel<BN, STAGES><<<grid, THREADS, smem, stream>>>(mw, mx, out, tokens, features, k_blocks, ld_out, epilogue, status);
+  vosti_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, mw, mx, out, tokens, features, k_blocks, ld_out,
+               epilogue, status);
   return 0;
 }
 
@@ -609,8 +628,8 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
       }
     }
     const int tiles = ((tokens + BM - 1) / BM) * ((features + WIDE_BN - 1) / WIDE_BN);
-    gemm_tc_wide_kernel<<<tiles < sms ? tiles : sms, THREADS, smem, stream>>>(mx, *mw, y, tokens, features, k_blocks,
-                                                                             ld_out, epilogue, status);
+    vosti_launch(gemm_tc_wide_kernel, dim3(tiles < sms ? tiles : sms), dim3(THREADS), smem, stream, mx, *mw, y, tokens,
+                 features, k_blocks, ld_out, epilogue, status);
     VOSTI_LAUNCH_CHECK();
   }
   const int bn = token_tile(tokens);
@@ -630,7 +649,8 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
   if (splits > 1 && !defer_reduce) {
     const int64_t n = (int64_t)tokens * features;
     const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(workspace, y, splits, tokens, features, ld_out, epilogue);
+    vosti_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)workspace, y, splits, tokens,
+                 features, ld_out, epilogue);
   }
   VOSTI_LAUNCH_CHECK();
 }
@@ -643,8 +663,8 @@ VOSTI_API int vosti_splitk_reduce(const float* partial, void* y, int splits, int
   if (tokens == 0) return VOSTI_OK;
   const int64_t n = (int64_t)tokens * features;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, y, splits, tokens, features, features,
-                                                   y_is_f32 ? EPI_F32 : EPI_BF16);
+  vosti_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partial, y, splits, tokens, features, features,
+               (int)(y_is_f32 ? EPI_F32 : EPI_BF16));
   VOSTI_LAUNCH_CHECK();
 }
 
@@ -713,7 +733,8 @@ VOSTI_API int vosti_gemm_tc_split_static(const void* x, const void* w, void* y, 
   if (splits > 1) {
     const int64_t n = (int64_t)tokens * features;
     const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(scratch, y, splits, tokens, features, features, epilogue);
+    vosti_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)scratch, y, splits, tokens,
+                 features, features, epilogue);
   }
   VOSTI_LAUNCH_CHECK();
 }

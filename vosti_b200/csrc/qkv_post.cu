@@ -21,6 +21,8 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
                 const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
                 const int* __restrict__ slot_mapping, int64_t num_slots, int nq, int nkv, int d,
                 unsigned* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int half = d >> 1;
@@ -138,11 +140,11 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
   const int heads = nq + 2 * nkv;
   const dim3 grid(tokens, tokens >= 2048 ? 1 : (heads + 3) / 4);   // few tokens: a warp per (token, head)
   if (is_f32)
-    qkv_post_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, partial, splits, plane, (float*)q_out, (float*)k_cache,
+    vosti_launch(qkv_post_kernel<float>, grid, dim3(128), 0, stream, (const float*)qkv, partial, splits, plane, (float*)q_out, (float*)k_cache,
         (float*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
         slot_mapping, num_slots, nq, nkv, d, status);
   else
-    qkv_post_kernel<bf16><<<grid, 128, 0, stream>>>((const bf16*)qkv, partial, splits, plane, (bf16*)q_out, (bf16*)k_cache,
+    vosti_launch(qkv_post_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)qkv, partial, splits, plane, (bf16*)q_out, (bf16*)k_cache,
         (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
         slot_mapping, num_slots, nq, nkv, d, status);
   VOSTI_LAUNCH_CHECK();

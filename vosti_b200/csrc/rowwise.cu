@@ -8,6 +8,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  T* __restrict__ out, int hidden, int vocab, unsigned* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   int id = ids[t];
   const bool bad = id < 0 || id >= vocab;
@@ -33,9 +35,9 @@ VOSTI_API int vosti_embedding(const int* ids, const void* table, void* out, int 
                 tokens, hidden, vocab);
   if (tokens == 0) return VOSTI_OK;
   if (is_f32)
-    embedding_kernel<float><<<tokens, 128, 0, stream>>>(ids, (const float*)table, (float*)out, hidden, vocab, status);
+    vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, (const float*)table, (float*)out, hidden, vocab, status);
   else
-    embedding_kernel<bf16><<<tokens, 128, 0, stream>>>(ids, (const bf16*)table, (bf16*)out, hidden, vocab, status);
+    vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, (const bf16*)table, (bf16*)out, hidden, vocab, status);
   VOSTI_LAUNCH_CHECK();
 }
 
@@ -48,6 +50,8 @@ __global__ void __launch_bounds__(BLOCK)
 rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, const void* __restrict__ weight,
                int weight_is_f32, T* __restrict__ out, T* __restrict__ residual_out, int width, float eps) {
   __shared__ float scratch[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t base = (int64_t)blockIdx.x * width;
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += BLOCK) {
@@ -76,11 +80,11 @@ VOSTI_API int vosti_rmsnorm(const void* x, const void* residual, const void* wei
   if (rows == 0) return VOSTI_OK;
   VOSTI_REQUIRE(out != x && out != residual && out != residual_out, "rmsnorm: out must not alias another operand");
   if (is_f32)
-    rmsnorm_kernel<float, 256><<<rows, 256, 0, stream>>>((const float*)x, (const float*)residual, weight,
-                                                        weight_is_f32, (float*)out, (float*)residual_out, width, eps);
+    vosti_launch(rmsnorm_kernel<float, 256>, dim3(rows), dim3(256), 0, stream, (const float*)x, (const float*)residual,
+                 weight, weight_is_f32, (float*)out, (float*)residual_out, width, eps);
   else
-    rmsnorm_kernel<bf16, 256><<<rows, 256, 0, stream>>>((const bf16*)x, (const bf16*)residual, weight,
-                                                       weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
+    vosti_launch(rmsnorm_kernel<bf16, 256>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (const bf16*)residual,
+                 weight, weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
   VOSTI_LAUNCH_CHECK();
 }
 
@@ -93,6 +97,8 @@ rmsnorm_partial_kernel(const float* __restrict__ partial, int splits, int64_t pl
                        T* __restrict__ residual_out, int width, float eps) {
   __shared__ float scratch[32];
   extern __shared__ float row_sum[];                       // the summed row, kept for the second pass
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t base = (int64_t)blockIdx.x * width;
   constexpr int GROUP = 4;                                 // elements a thread sums at once: independent loads
   float ss = 0.f;
@@ -143,16 +149,16 @@ VOSTI_API int vosti_rmsnorm_partial(const float* partial, int splits, const void
       cudaFuncSetAttribute(rmsnorm_partial_kernel<float, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 24576 * 4);
       configured = true;
     }
-    rmsnorm_partial_kernel<float, 1024><<<rows, 1024, smem, stream>>>(partial, splits, plane, (const float*)residual, weight,
-        weight_is_f32, (float*)out, (float*)residual_out, width, eps);
+    vosti_launch(rmsnorm_partial_kernel<float, 1024>, dim3(rows), dim3(1024), smem, stream, partial, splits, plane,
+                 (const float*)residual, weight, weight_is_f32, (float*)out, (float*)residual_out, width, eps);
   } else {
     static bool configured = false;
     if (!configured) {
       cudaFuncSetAttribute(rmsnorm_partial_kernel<bf16, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 24576 * 4);
       configured = true;
     }
-    rmsnorm_partial_kernel<bf16, 1024><<<rows, 1024, smem, stream>>>(partial, splits, plane, (const bf16*)residual, weight,
-        weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
+    vosti_launch(rmsnorm_partial_kernel<bf16, 1024>, dim3(rows), dim3(1024), smem, stream, partial, splits, plane,
+                 (const bf16*)residual, weight, weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
   }
   VOSTI_LAUNCH_CHECK();
 }

@@ -28,6 +28,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, c
   __shared__ int s_idx[32];
   __shared__ float s_scan[THREADS + 1];
   __shared__ int s_token;
+  pdl_wait();
+  pdl_launch_dependents();
   const float* row = logits + (int64_t)blockIdx.x * row_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -116,6 +118,7 @@ VOSTI_API int vosti_sample(const float* logits, int rows, int vocab, int64_t row
   VOSTI_REQUIRE(temperature == nullptr || (seeds != nullptr && counters != nullptr),
                 "sample: temperature sampling needs seeds and counters");
   if (rows == 0) return VOSTI_OK;
-  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, row_stride, temperature, seeds, counters, out);
+  vosti_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, row_stride, temperature, seeds,
+               counters, out);
   VOSTI_LAUNCH_CHECK();
 }
