@@ -14,8 +14,8 @@
 // on its batch companions. Formulas as in kernels/triton_kernels/fattn_paged.py:176-252:
 // kv head = query head * nkv / nq, scale * log2(e), causal up to the token's own position,
 // optional window, P rounded to bfloat16 before P.V (:246), out = acc / l (0 if l = 0).
-// K and V tiles are staged in shared memory with cp.async (16-byte chunks straight from the
-// pages); masked keys are never read from the cache.
+// K and V rows are staged in shared memory by bulk copies (one per cache row, completing
+// on an mbarrier per tile) straight from the pages; masked keys are never read from the cache.
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -39,9 +39,15 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         float* __restrict__ partial, const int* __restrict__ token_list,
                         const int* __restrict__ positions, const int* __restrict__ request_of,
-                        const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
-                        int nq, int nkv, int d_runtime, int max_segments, float scale_log2, int window, unsigned* status) {
+                        const int* __restrict__ block_table, int max_pages, int page_size, int page_shift,
+                        int num_pages, int nq, int nkv, int d_runtime, int max_segments, float scale_log2, int window, unsigned* status) {
   extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ __align__(8) uint64_t tile_bar[WARPS][WARP_TILES];
+  if ((threadIdx.x & 31) == 0) {
+    for (int i = 0; i < WARP_TILES; ++i) mb_init(smem_addr(&tile_bar[threadIdx.x >> 5][i]), 1);
+    mb_fence_init();
+  }
+  __syncwarp();
   pdl_wait();
   pdl_launch_dependents();
   const int d = EXACT ? DMAX : d_runtime;
@@ -65,34 +71,33 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
   const int first_tile = max(my_begin, (kstart / TILE) * TILE);       // tiles stay aligned to the key index
   const int tiles = my_end > first_tile ? (my_end - first_tile + TILE - 1) / TILE : 0;
 
-  // One cache slot per key of a tile: lane r (< 16) looks up key r, the others get it by shuffle.
+  // A tile's 16 key rows and 16 value rows are fetched by one bulk copy each (lane r: key
+  // row r, lane 16 + r: value row r) that signals the tile's mbarrier; rows that are not
+  // visible are zero-filled and never read from the cache.
   auto issue = [&](int tile) {
     const int key0 = first_tile + tile * TILE;
     uint8_t* kdst = stage_base + tile * (2 * TILE * pitch);
     uint8_t* vdst = kdst + TILE * pitch;
-    int64_t my_slot = -1;
-    {
-      const int key = key0 + (lane & 15);
-      if (key >= kstart && key <= pos) {
-        const int index = key / page_size;
-        const int page = index < max_pages ? table[index] : -1;
-        if (page < 0 || page >= num_pages) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
-        else my_slot = (int64_t)page * page_size + key % page_size;
-      }
+    const int row = lane & 15;
+    const int key = key0 + row;
+    int64_t slot = -1;
+    if (key >= kstart && key <= pos) {
+      const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
+      const int page = index < max_pages ? table[index] : -1;
+      if (page < 0 || page >= num_pages) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
+      else slot = (int64_t)page * page_size + (key - index * page_size);
     }
-    for (int i = lane; i < TILE * chunks; i += 32) {
-      const int row = i / chunks, c = i % chunks;
-      const int64_t slot = __shfl_sync(0xffffffffu, my_slot, row);
-      if (slot >= 0) {
-        const int64_t offset = (slot * nkv + g) * d + c * 8;
-        cp_async16(smem_addr(kdst + row * pitch + c * 16), k_cache + offset);
-        cp_async16(smem_addr(vdst + row * pitch + c * 16), v_cache + offset);
-      } else {
-        *reinterpret_cast<uint4*>(kdst + row * pitch + c * 16) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(vdst + row * pitch + c * 16) = make_uint4(0, 0, 0, 0);
-      }
+    const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
+    const uint32_t bar = smem_addr(&tile_bar[warp][tile]);
+    if (lane == 0) mb_expect_tx(bar, (uint32_t)__popc(live) * (uint32_t)(d * 2));
+    __syncwarp();
+    uint8_t* dst = (lane < 16 ? kdst : vdst) + row * pitch;
+    if (slot >= 0) {
+      const bf16* src = (lane < 16 ? k_cache : v_cache) + (slot * nkv + g) * d;
+      bulk_copy_g2s(smem_addr(dst), src, (uint32_t)(d * 2), bar);
+    } else {
+      for (int c = 0; c < chunks; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0, 0, 0, 0);
     }
-    cp_async_commit();
   };
 
   float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
@@ -100,7 +105,6 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 #pragma unroll
   for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  static_assert(WARP_TILES == 2, "the wait below counts two outstanding groups");
   for (int tile = 0; tile < tiles; ++tile) issue(tile);           // everything is requested up front
   // ---- Q rows of the group (rows >= group are zero)
   for (int i = threadIdx.x; i < 16 * chunks; i += WARPS * 32) {
@@ -110,10 +114,19 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     *reinterpret_cast<uint4*>(q_s + row * pitch + c * 16) = v;
   }
   __syncthreads();                                                  // (the K/V requests above are in flight meanwhile)
+  // up to head size 128 the Q fragments stay in registers for both tiles
+  constexpr bool Q_IN_REGISTERS = DMAX <= 128;
+  uint32_t qa[Q_IN_REGISTERS ? DMAX / 16 : 1][4];
+  if (Q_IN_REGISTERS) {
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk)
+      if (kk * 16 < d) ldmatrix_x4(qa[Q_IN_REGISTERS ? kk : 0], smem_addr(q_s + (lane & 15) * pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+  }
+  // rows 8..15 of the MMA tile hold query heads only if the group has more than 8
+  const bool upper_rows_live = group > 8;
 
   for (int tile = 0; tile < tiles; ++tile) {
-    if (tile + 1 < tiles) cp_async_wait<1>();
-    else cp_async_wait<0>();
+    mb_wait(smem_addr(&tile_bar[warp][tile]), 0, status);
     __syncwarp();
     const uint8_t* ks = stage_base + tile * (2 * TILE * pitch);
     const uint8_t* vs = ks + TILE * pitch;
@@ -126,7 +139,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
       if (kk * 16 < d) {
         uint32_t a[4], b[4];
         // A: rows lane%16 of Q, columns kk*16 + (lane/16)*8
-        ldmatrix_x4(a, smem_addr(q_s + (lane & 15) * pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+        if (Q_IN_REGISTERS) {
+          a[0] = qa[Q_IN_REGISTERS ? kk : 0][0]; a[1] = qa[Q_IN_REGISTERS ? kk : 0][1];
+          a[2] = qa[Q_IN_REGISTERS ? kk : 0][2]; a[3] = qa[Q_IN_REGISTERS ? kk : 0][3];
+        } else {
+          ldmatrix_x4(a, smem_addr(q_s + (lane & 15) * pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+        }
         // B: matrices (keys 0-7, k lo), (keys 0-7, k hi), (keys 8-15, k lo), (keys 8-15, k hi)
         ldmatrix_x4(b, smem_addr(ks + ((lane & 7) + (lane >> 4) * 8) * pitch + (kk * 16 + ((lane >> 3) & 1) * 8) * 2));
         mma_bf16(s[0], a, b[0], b[1]);
@@ -147,17 +165,22 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     float alpha[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
+      if (r == 1 && !upper_rows_live) {              // padding rows: no exponentials (warp-uniform)
+        alpha[r] = 1.f;
+        s[0][2] = s[0][3] = s[1][2] = s[1][3] = 0.f;
+        continue;
+      }
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
       const float m_new = fmaxf(m_row[r], tile_max[r]);
       const float safe = m_new == -INFINITY ? 0.f : m_new;
-      alpha[r] = exp2f(m_row[r] - safe);
+      alpha[r] = fast_exp2(m_row[r] - safe);
       m_row[r] = m_new;
       float sum = 0.f;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        s[nt][2 * r] = exp2f(s[nt][2 * r] - safe);
-        s[nt][2 * r + 1] = exp2f(s[nt][2 * r + 1] - safe);
+        s[nt][2 * r] = fast_exp2(s[nt][2 * r] - safe);
+        s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - safe);
         sum += s[nt][2 * r] + s[nt][2 * r + 1];
       }
       l_row[r] = l_row[r] * alpha[r] + sum;          // per-thread share; reduced over the quad at the end
@@ -206,21 +229,32 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < group * rec; i += WARPS * 32) {
-    const int row = i / rec, c = i % rec;
-    float m = -INFINITY;
-    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge[((int64_t)w * 16 + row) * rec]);
-    float value;
-    if (c == 0) {
-      value = m;
-    } else {
-      value = 0.f;
-      for (int w = 0; w < WARPS; ++w) {
-        const float mw = merge[((int64_t)w * 16 + row) * rec];
-        if (mw != -INFINITY) value += merge[((int64_t)w * 16 + row) * rec + c] * exp2f(mw - m);
-      }
+  // per (row, warp): the row's maximum over the warps and this warp's weight 2^(m_w - m)
+  __shared__ float row_max[16], row_weight[WARPS][16];
+  if (threadIdx.x < 16 * WARPS) {
+    const int row = threadIdx.x & 15, w = threadIdx.x >> 4;
+    if (row < group) {
+      float m = -INFINITY;
+      for (int v = 0; v < WARPS; ++v) m = fmaxf(m, merge[((int64_t)v * 16 + row) * rec]);
+      const float mw = merge[((int64_t)w * 16 + row) * rec];
+      row_weight[w][row] = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
+      if (w == 0) row_max[row] = m;
     }
-    partial[(((int64_t)blockIdx.z * nq + g * group + row) * max_segments + seg) * rec + c] = value;
+  }
+  __syncthreads();
+  for (int row = 0; row < group; ++row) {
+    float* dst = partial + (((int64_t)blockIdx.z * nq + g * group + row) * max_segments + seg) * rec;
+    for (int c = threadIdx.x; c < rec; c += WARPS * 32) {
+      float value;
+      if (c == 0) {
+        value = row_max[row];
+      } else {
+        value = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) value += merge[((int64_t)w * 16 + row) * rec + c] * row_weight[w][row];
+      }
+      dst[c] = value;
+    }
   }
 }
 
@@ -260,7 +294,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
     if (mine <= last) {
       const float ms = base[(int64_t)mine * rec];
       if (ms != -INFINITY) {
-        w_mine = exp2f(ms - m);
+        w_mine = fast_exp2(ms - m);
         l_mine = base[(int64_t)mine * rec + 1] * w_mine;
       }
     }
@@ -334,6 +368,9 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   const size_t smem = decode_smem_bytes(d);
   dim3 grid(segments, nkv, count);
   VOSTI_REQUIRE(count <= 65535, "attention_decode: too many tokens (%d) for one launch", count);
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
 #define LAUNCH_DECODE(DMAX, EXACT)                                                                                  \
   do {                                                                                                              \
     static bool configured = false;                                                                                 \
@@ -344,7 +381,8 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
     }                                                                                                               \
     vosti_launch(attention_decode_kernel<DMAX, EXACT>, grid, dim3(WARPS * 32), smem, stream,                        \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, scratch, token_list, positions, request_of,      \
-        block_table, max_pages, page_size, num_pages, nq, nkv, d, segments, scale * LOG2E, window, status);          \
+        block_table, max_pages, page_size, page_shift, num_pages, nq, nkv, d, segments, scale * LOG2E, window,      \
+        status);                                                                                                    \
   } while (0)
   if (d == 64) LAUNCH_DECODE(64, true);
   else if (d == 128) LAUNCH_DECODE(128, true);
