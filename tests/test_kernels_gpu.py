@@ -182,6 +182,12 @@ def paged_case(dev, dtype, lens_q, lens_k, nq, nkv, d, page, poison=True, seed=0
                 request_of=torch.tensor(request_of, dtype=torch.int32), page=page)
 
 
+def dev_cache(case, key, dev, dtype):
+    """The test builds caches as [slot, kv head, d]; the kernels keep [page, kv head, offset, d]."""
+    c, page = case[key], case["page"]
+    return c.view(-1, page, c.shape[1], c.shape[2]).permute(0, 2, 1, 3).contiguous().to(dev, dtype)
+
+
 def reference_attention(case, scale, window):
     outs = []
     for q, k, v in zip(case["qs"], case["ks"], case["vs"]):
@@ -201,7 +207,7 @@ def test_attention_simt(dev, status, dtype, nq, nkv, d, page, window):
     lens_q = [1, 33, 1, 7, 2, 1]
     case = paged_case(dev, dtype, lens_q, lens_k, nq, nkv, d, page)
     scale = 0.37 * d ** -0.5
-    out = ops.attention_simt(case["q"].to(dev, dtype), case["k_cache"].to(dev, dtype), case["v_cache"].to(dev, dtype),
+    out = ops.attention_simt(case["q"].to(dev, dtype), dev_cache(case, "k_cache", dev, dtype), dev_cache(case, "v_cache", dev, dtype),
                              positions=case["positions"].to(dev), request_of=case["request_of"].to(dev),
                              block_table=case["table"].to(dev), page_size=page, nq=nq, nkv=nkv, head_dim=d,
                              scale=scale, window=window, status=status)
@@ -225,8 +231,8 @@ def test_attention_finds_one_far_key(dev, status, dtype):
         case["k_cache"][slot, 0] = (40.0 * direction).to(dtype).float()
         marker = torch.full((d,), 3.0)
         case["v_cache"][slot, 0] = marker
-        out = ops.attention_simt(case["q"].to(dev, dtype), case["k_cache"].to(dev, dtype),
-                                 case["v_cache"].to(dev, dtype), positions=case["positions"].to(dev),
+        out = ops.attention_simt(case["q"].to(dev, dtype), dev_cache(case, "k_cache", dev, dtype),
+                                 dev_cache(case, "v_cache", dev, dtype), positions=case["positions"].to(dev),
                                  request_of=case["request_of"].to(dev), block_table=case["table"].to(dev),
                                  page_size=page, nq=nq, nkv=nkv, head_dim=d, scale=1.0, window=window, status=status)
         visible = window == 0 or far > L - 1 - window
@@ -334,7 +340,7 @@ def _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale
     """Drive the decode (one query at a time) or the portion kernel directly."""
     from vosti_b200 import ops
     q = case["q"].to(dev, torch.bfloat16)
-    kc, vc = case["k_cache"].to(dev, torch.bfloat16), case["v_cache"].to(dev, torch.bfloat16)
+    kc, vc = dev_cache(case, "k_cache", dev, torch.bfloat16), dev_cache(case, "v_cache", dev, torch.bfloat16)
     out = torch.full_like(q, float("nan"))
     table = case["table"].to(dev)
     common = dict(block_table=table, page_size=page, nq=nq, nkv=nkv, head_dim=d, scale=scale, window=window, status=status)
@@ -393,7 +399,7 @@ def test_attention_decode_is_independent_of_the_batch(dev, status):
     case = paged_case(dev, torch.bfloat16, [1, 1, 1, 1], lens_k, nq, nkv, d, page)
     full = _run_tc_attention(dev, status, case, [1] * 4, lens_k, nq, nkv, d, page, d ** -0.5, 0, "decode")
     q = case["q"].to(dev, torch.bfloat16)
-    kc, vc = case["k_cache"].to(dev, torch.bfloat16), case["v_cache"].to(dev, torch.bfloat16)
+    kc, vc = dev_cache(case, "k_cache", dev, torch.bfloat16), dev_cache(case, "v_cache", dev, torch.bfloat16)
     out = torch.zeros_like(q)
     listed = torch.tensor([3, 1], dtype=torch.int32, device=dev)
     ops.attention_decode(q, kc, vc, out, token_list=listed, count=2, positions=case["positions"].to(dev),

@@ -6,8 +6,9 @@ Layers whose mixers keep everything share one group (one id space, one block tab
 as the reference's layers do: python/vosti_kernels/physical.py:124-147, 329-339);
 layers that only ever read a window of the past form a group of their own, whose pages
 are given back as soon as the window has passed them. A slot is ``page * page_size +
-offset`` into a layer's flat ``[num_pages * page_size, heads, width]`` storage
-(kernels/triton_kernels/store_kv_cache.py:21-25).
+offset`` (kernels/triton_kernels/store_kv_cache.py:21-25); a layer's storage is
+``[num_pages, heads, page_size, width]``, so the tokens one head holds in a page are
+contiguous (the reference keeps ``[pages, page_size, heads, width]``).
 
 Pages come back when a request finishes, when a window has passed them, and (for
 published prefix pages nobody holds) when an allocation needs them.
@@ -89,7 +90,7 @@ class CacheManager:
                 self.groups[cache.group].layers.append(layer)
                 if device is not None:
                     cache.tensors = tuple(
-                        torch.empty((num_pages * page_size, spec.heads, spec.width), dtype=dtype, device=device)
+                        torch.empty((num_pages, spec.heads, page_size, spec.width), dtype=dtype, device=device)
                         for _ in range(spec.entries))
             self.layer_caches.append(cache)
         for layer, spec in enumerate(state_specs):
@@ -111,7 +112,7 @@ class CacheManager:
         total = 0
         for cache in self.layer_caches:
             for t in cache.tensors:
-                total += t.shape[1] * t.shape[2] * t.element_size()
+                total += t.shape[1] * t.shape[3] * t.element_size()      # heads * width
         return total
 
     def pages_for(self, tokens: int) -> int:

@@ -85,7 +85,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
       const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
       const int page = index < max_pages ? table[index] : -1;
       if (page < 0 || page >= num_pages) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
-      else slot = (int64_t)page * page_size + (key - index * page_size);
+      else slot = ((int64_t)page * nkv + g) * page_size + (key - index * page_size);   // row of (page, head, offset)
     }
     const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
     const uint32_t bar = smem_addr(&tile_bar[warp][tile]);
@@ -93,7 +93,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     __syncwarp();
     uint8_t* dst = (lane < 16 ? kdst : vdst) + row * pitch;
     if (slot >= 0) {
-      const bf16* src = (lane < 16 ? k_cache : v_cache) + (slot * nkv + g) * d;
+      const bf16* src = (lane < 16 ? k_cache : v_cache) + slot * d;
       bulk_copy_g2s(smem_addr(dst), src, (uint32_t)(d * 2), bar);
     } else {
       for (int c = 0; c < chunks; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0, 0, 0, 0);
@@ -348,6 +348,7 @@ VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int d, int m
   return (int64_t)count * nq * vosti_attention_decode_segments(max_kv_len) * record_floats(d);
 }
 
+// caches: bf16 [pages, kv heads, page_size, d] (a head's tokens of a page are contiguous).
 // q, out: bf16 [tokens_total, nq, d]; the kernel serves `count` tokens: those listed in
 // token_list (int32[count]) or tokens 0..count-1. scratch holds the partial records of the
 // launch (vosti_attention_decode_scratch elements) and may be reused by the next launch.

@@ -100,11 +100,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
           raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
           valid = false;
         } else {
-          slot = (int64_t)page * page_size + (key - index * page_size);
+          slot = ((int64_t)page * nkv + g) * page_size + (key - index * page_size);   // row of (page, head, offset)
         }
       }
       if (valid) {
-        const int64_t offset = (slot * nkv + g) * d + c * 8;
+        const int64_t offset = slot * d + c * 8;
         cp_async16(smem_addr(kdst + r * pitch + c * 16), k_cache + offset);
         cp_async16(smem_addr(vdst + r * pitch + c * 16), v_cache + offset);
       } else {
@@ -274,6 +274,7 @@ size_t prefill_smem_bytes(int d) { return (size_t)(rows_per_cta(d) + 4 * KT) * (
 
 }  // namespace
 
+// caches: bf16 [pages, kv heads, page_size, d].
 // q, out: bf16 [tokens, nq, d]; serves `count` requests: those in row_list (int32[count])
 // or requests 0..count-1; cu_q: int32[requests + 1]; kv_len: int32[requests];
 // max_q_len: the longest portion among the served requests.

@@ -88,8 +88,8 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
         raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
         valid = false;
       } else {
-        slot = (int64_t)page * page_size + (j % page_size);
-        s = dot_row<T>(qs, k_cache + (slot * nkv + g) * d, d) * scale_log2;
+        slot = ((int64_t)page * nkv + g) * page_size + (j % page_size);   // row of (page, head, offset)
+        s = dot_row<T>(qs, k_cache + slot * d, d) * scale_log2;
       }
     }
     const float tile_max = warp_max(s);
@@ -105,7 +105,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
       const float pk = __shfl_sync(0xffffffffu, p, kk);
       const int64_t sk = __shfl_sync(0xffffffffu, slot, kk);
       if (pk == 0.f) continue;
-      const T* vrow = v_cache + (sk * nkv + g) * d;
+      const T* vrow = v_cache + sk * d;
 #pragma unroll
       for (int i = 0; i < MAX_D / 32; ++i) {
         const int idx = lane + 32 * i;
@@ -124,7 +124,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 }
 }  // namespace
 
-// q, out: [tokens, nq, d]; caches: [num_pages * page_size, nkv, d];
+// q, out: [tokens, nq, d]; caches: [num_pages, nkv, page_size, d];
 // block_table: [requests, max_pages]; positions, request_of: int32[tokens].
 VOSTI_API int vosti_attention_simt(const void* q, const void* k_cache, const void* v_cache, void* out,
                                    const int* positions, const int* request_of, const int* block_table,

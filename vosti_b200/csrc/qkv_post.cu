@@ -19,7 +19,7 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
                 T* __restrict__ v_cache, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
                 int norm_w_is_f32, float eps, const float* __restrict__ cos_table,
                 const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
-                const int* __restrict__ slot_mapping, int64_t num_slots, int nq, int nkv, int d,
+                const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv, int d,
                 unsigned* status) {
   pdl_wait();
   pdl_launch_dependents();
@@ -60,7 +60,8 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
     } else {
       if (slot < 0) continue;
       const int g = is_k ? h - nq : h - nq - nkv;
-      dst = (is_k ? k_cache : v_cache) + (slot * nkv + g) * d;
+      // caches are [pages, kv heads, page_size, d]: a head's tokens of a page are contiguous
+      dst = (is_k ? k_cache : v_cache) + (((slot / page_size) * nkv + g) * page_size + slot % page_size) * d;
     }
     if (!is_q && !is_k) {  // value head: plain copy
       for (int i = lane; i < d; i += 32) dst[i] = partial == nullptr ? src[i] : from_f32<T>(load(i));
@@ -119,16 +120,18 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
 
 // qkv: [tokens, (nq + 2*nkv) * d], or null with `partial`: float32 [splits, tokens, (nq + 2*nkv) * d],
 // the K-split partial sums of the projection, summed here in split order.
-// q_out: [tokens, nq * d]; caches: [num_slots, nkv, d].
+// q_out: [tokens, nq * d]; caches: [pages, nkv, page_size, d] with num_slots = pages * page_size;
+// slot s is (page s / page_size, offset s % page_size).
 // nkv == 0: the input holds query heads only and nothing is stored.
 // q_norm_w / k_norm_w null: no head norm. cos/sin null: no rotation; else float32
 // tables [max_positions, d/2].
 VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, void* q_out, void* k_cache, void* v_cache, const void* q_norm_w,
                              const void* k_norm_w, int norm_w_is_f32, float eps, const float* cos_table,
                              const float* sin_table, int max_positions, const int* positions,
-                             const int* slot_mapping, int64_t num_slots, int tokens, int nq, int nkv, int d,
+                             const int* slot_mapping, int64_t num_slots, int page_size, int tokens, int nq, int nkv, int d,
                              int is_f32, unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && d > 0, "qkv_post: bad sizes");
+  VOSTI_REQUIRE(nkv == 0 || page_size > 0, "qkv_post: page_size must be positive");
   VOSTI_REQUIRE((qkv != nullptr) != (partial != nullptr), "qkv_post: give the projection or its partial sums");
   VOSTI_REQUIRE(partial == nullptr || splits >= 1, "qkv_post: bad split count");
   const int64_t plane = (int64_t)tokens * (nq + 2 * nkv) * d;
@@ -142,10 +145,10 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
   if (is_f32)
     vosti_launch(qkv_post_kernel<float>, grid, dim3(128), 0, stream, (const float*)qkv, partial, splits, plane, (float*)q_out, (float*)k_cache,
         (float*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
-        slot_mapping, num_slots, nq, nkv, d, status);
+        slot_mapping, num_slots, page_size, nq, nkv, d, status);
   else
     vosti_launch(qkv_post_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)qkv, partial, splits, plane, (bf16*)q_out, (bf16*)k_cache,
         (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
-        slot_mapping, num_slots, nq, nkv, d, status);
+        slot_mapping, num_slots, page_size, nq, nkv, d, status);
   VOSTI_LAUNCH_CHECK();
 }

@@ -146,10 +146,10 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, *,
 
 
 def qkv_post(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *,
-             nq: int, nkv: int, head_dim: int, q_norm_w: Optional[torch.Tensor],
-             k_norm_w: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
-             sin: Optional[torch.Tensor], positions: Optional[torch.Tensor],
-             slot_mapping: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:
+             nq: int, nkv: int, head_dim: int, page_size: int = 1, q_norm_w: Optional[torch.Tensor] = None,
+             k_norm_w: Optional[torch.Tensor] = None, eps: float = 1.0, cos: Optional[torch.Tensor] = None,
+             sin: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
+             slot_mapping: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Head norm, rotation and cache store after the QKV projection; returns q [T, nq*d].
     `qkv` may be the projection or the unsummed partial sums of its split-K product."""
     partial, splits = None, 0
@@ -181,7 +181,7 @@ def qkv_post(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Option
     _check(library().vosti_qkv_post(
         _p(qkv), _p(partial), splits, _p(q_out), _p(k_cache), _p(v_cache), _p(q_norm_w), _p(k_norm_w), norm_flag,
         ctypes.c_float(eps), _p(cos), _p(sin), max_positions, _p(positions), _p(slot_mapping),
-        ctypes.c_int64(num_slots), tokens, nq, nkv, head_dim, flag, _p(status), _stream()), "qkv_post")
+        ctypes.c_int64(num_slots), page_size, tokens, nq, nkv, head_dim, flag, _p(status), _stream()), "qkv_post")
     return q_out
 
 

@@ -76,7 +76,7 @@ class Attention(Mixer):
         tables = self.position.rotation_tables() if self.position is not None else None
         cos, sin = tables if tables is not None else (None, None)
         eps = self.head_norm_eps if self.head_norm_eps is not None else 1.0
-        common = dict(nq=self.nq, head_dim=self.d, q_norm_w=self.q_norm, eps=eps, cos=cos, sin=sin,
+        common = dict(nq=self.nq, head_dim=self.d, page_size=group.page_size, q_norm_w=self.q_norm, eps=eps, cos=cos, sin=sin,
                       positions=ctx.positions, status=ctx.status)
         if writes_cache:
             qkv = linear(ctx, x, self.w_qkv, allow_partial=True)   # summed inside qkv_post
