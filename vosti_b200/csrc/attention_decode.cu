@@ -4,8 +4,8 @@
 //   grid = (segments, kv heads, tokens). One CTA takes one token, one kv head with the
 //   whole group of query heads that share it (they fill the MMA's 16 rows), and one
 //   segment of SEGMENT keys counted from key 0 of the request. Its four warps each take a
-//   quarter of the segment (two tiles of 16 keys, both requested from memory before any
-//   arithmetic), run the online softmax (base 2, float32) with mma.sync m16n8k16 for
+//   quarter of the segment (four tiles of 16 keys through two buffers: two tiles are
+//   requested before any arithmetic, the others as buffers become free), run the online softmax (base 2, float32) with mma.sync m16n8k16 for
 //   Q.K^T and P.V, and are merged in warp order. The CTA writes
 //   an unnormalised partial (max, sum, accumulator) per query head; a second kernel merges
 //   the segments in segment order and normalises.
@@ -23,9 +23,9 @@ namespace {
 
 constexpr int WARPS = 4;
 constexpr int TILE = 16;              // keys per MMA step
-constexpr int SEGMENT = 128;          // keys per CTA
+constexpr int SEGMENT = 256;          // keys per CTA
 constexpr int WARP_KEYS = SEGMENT / WARPS;
-constexpr int WARP_TILES = WARP_KEYS / TILE;   // tiles a warp holds in shared memory at once
+constexpr int BUFFERS = 2;                     // of which this many are in shared memory at once
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Partial record of one (token, query head, segment): [0] max (base-2 scores), [1] sum,
@@ -42,9 +42,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         const int* __restrict__ block_table, int max_pages, int page_size, int page_shift,
                         int num_pages, int nq, int nkv, int d_runtime, int max_segments, float scale_log2, int window, unsigned* status) {
   extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ __align__(8) uint64_t tile_bar[WARPS][WARP_TILES];
+  __shared__ __align__(8) uint64_t tile_bar[WARPS][BUFFERS];
   if ((threadIdx.x & 31) == 0) {
-    for (int i = 0; i < WARP_TILES; ++i) mb_init(smem_addr(&tile_bar[threadIdx.x >> 5][i]), 1);
+    for (int i = 0; i < BUFFERS; ++i) mb_init(smem_addr(&tile_bar[threadIdx.x >> 5][i]), 1);
     mb_fence_init();
   }
   __syncwarp();
@@ -63,7 +63,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 
   const int pitch = d * 2 + 16;                     // bytes per staged row: conflict-free ldmatrix
   uint8_t* q_s = smem;                              // [16][pitch]
-  uint8_t* stage_base = smem + 16 * pitch + warp * (2 * WARP_TILES * TILE * pitch);   // per warp: tiles x (K, V)
+  uint8_t* stage_base = smem + 16 * pitch + warp * (2 * BUFFERS * TILE * pitch);   // per warp: buffers x (K, V)
   const int chunks = d / 8;                         // 16-byte chunks per row
 
   const int my_begin = seg_begin + warp * WARP_KEYS;
@@ -76,7 +76,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
   // visible are zero-filled and never read from the cache.
   auto issue = [&](int tile) {
     const int key0 = first_tile + tile * TILE;
-    uint8_t* kdst = stage_base + tile * (2 * TILE * pitch);
+    uint8_t* kdst = stage_base + (tile % BUFFERS) * (2 * TILE * pitch);
     uint8_t* vdst = kdst + TILE * pitch;
     const int row = lane & 15;
     const int key = key0 + row;
@@ -88,7 +88,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
       else slot = ((int64_t)page * nkv + g) * page_size + (key - index * page_size);   // row of (page, head, offset)
     }
     const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
-    const uint32_t bar = smem_addr(&tile_bar[warp][tile]);
+    const uint32_t bar = smem_addr(&tile_bar[warp][tile % BUFFERS]);
     if (lane == 0) mb_expect_tx(bar, (uint32_t)__popc(live) * (uint32_t)(d * 2));
     __syncwarp();
     uint8_t* dst = (lane < 16 ? kdst : vdst) + row * pitch;
@@ -105,7 +105,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 #pragma unroll
   for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  for (int tile = 0; tile < tiles; ++tile) issue(tile);           // everything is requested up front
+  for (int tile = 0; tile < tiles && tile < BUFFERS; ++tile) issue(tile);   // the first tiles are requested at once
   // ---- Q rows of the group (rows >= group are zero)
   for (int i = threadIdx.x; i < 16 * chunks; i += WARPS * 32) {
     const int row = i / chunks, c = i % chunks;
@@ -126,9 +126,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
   const bool upper_rows_live = group > 8;
 
   for (int tile = 0; tile < tiles; ++tile) {
-    mb_wait(smem_addr(&tile_bar[warp][tile]), 0, status);
+    mb_wait(smem_addr(&tile_bar[warp][tile % BUFFERS]), (tile / BUFFERS) & 1, status);
     __syncwarp();
-    const uint8_t* ks = stage_base + tile * (2 * TILE * pitch);
+    const uint8_t* ks = stage_base + (tile % BUFFERS) * (2 * TILE * pitch);
     const uint8_t* vs = ks + TILE * pitch;
     const int key0 = first_tile + tile * TILE;
 
@@ -199,6 +199,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         mma_bf16(o[2 * nt], p, b[0], b[1]);
         mma_bf16(o[2 * nt + 1], p, b[2], b[3]);
       }
+    }
+    if (tile + BUFFERS < tiles) {                  // this buffer is free again: fetch the tile after next
+      __syncwarp();
+      issue(tile + BUFFERS);
     }
   }
   // ---- merge the four warps in warp order (through the staging memory)
@@ -332,7 +336,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
 
 size_t decode_smem_bytes(int d) {
   const size_t pitch = (size_t)d * 2 + 16;
-  const size_t stage = 16 * pitch + (size_t)WARPS * 2 * WARP_TILES * TILE * pitch;
+  const size_t stage = 16 * pitch + (size_t)WARPS * 2 * BUFFERS * TILE * pitch;
   const size_t merge = 16 * pitch + (size_t)WARPS * 16 * (d + 2) * sizeof(float);
   return stage > merge ? stage : merge;
 }

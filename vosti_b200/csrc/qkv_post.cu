@@ -141,7 +141,7 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
   VOSTI_REQUIRE(cos_table == nullptr || positions != nullptr, "qkv_post: rotation needs positions");
   if (tokens == 0) return VOSTI_OK;
   const int heads = nq + 2 * nkv;
-  const dim3 grid(tokens, tokens >= 2048 ? 1 : (heads + 3) / 4);   // few tokens: a warp per (token, head)
+  const dim3 grid(tokens, (heads + 3) / 4);                          // a warp per (token, head)
   if (is_f32)
     vosti_launch(qkv_post_kernel<float>, grid, dim3(128), 0, stream, (const float*)qkv, partial, splits, plane, (float*)q_out, (float*)k_cache,
         (float*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table, max_positions, positions,
