@@ -17,14 +17,7 @@ class Harness:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def context(self, entries):
-        cache = self.cache
         for e in entries:
-            if e.request_id not in cache.live:
-                cache.begin(e.request_id)
-        starts = [cache.length(e.request_id) for e in entries]
-        slots = [cache.extend(e.request_id, len(e.tokens)) for e in entries]
-        G = len(cache.groups)
-        return build_context(self.staging, entries, starts,
-                             [[slots[i][g] for i in range(len(entries))] for g in range(G)],
-                             [[cache.block_row(e.request_id, g) for e in entries] for g in range(G)],
-                             [cache.slot(e.request_id) for e in entries], cache.page_size, self.status, self.dtype)
+            if e.request_id not in self.cache.live:
+                self.cache.begin(e.request_id)
+        return build_context(self.staging, self.cache, entries, self.status, self.dtype)

@@ -133,7 +133,7 @@ def test_match_checks_tokens_not_only_hashes():
     page = pool.allocate(1)[0]
     h, _ = pool.publish(page, [1, 2, 3, 4], 0, 1, -1)
     assert h == chain_hash(0, [1, 2, 3, 4])
-    pool.published[page].tokens = (9, 9, 9, 9)         # as if another prompt hashed the same
+    pool._set_published_tokens(page, [9, 9, 9, 9])     # as if another prompt hashed the same
     assert pool.match([1, 2, 3, 4, 5], 4) == []
 
 

@@ -11,23 +11,24 @@ offset`` (kernels/triton_kernels/store_kv_cache.py:21-25); a layer's storage is
 contiguous (the reference keeps ``[pages, page_size, heads, width]``).
 
 Pages come back when a request finishes, when a window has passed them, and (for
-published prefix pages nobody holds) when an allocation needs them.
+published prefix pages nobody holds) when an allocation needs them. The accounting is
+C++ (vosti_b200/csrc/host/engine_core.cpp); device storage is allocated here.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import ctypes
+
 import torch
 
+from .. import host
+from ..host import OutOfSlots
 from ..parts.base import PagedCacheSpec, StateSpec
 from .pages import OutOfPages, PageAccountingError, PagePool
 
 RELEASED = -1  # block-table entry of a page a window has passed
-
-
-class OutOfSlots(RuntimeError):
-    pass
 
 
 @dataclass
@@ -57,7 +58,7 @@ class CacheGroup:
 
 @dataclass
 class Residency:
-    """What a live request holds."""
+    """What a live request holds (a snapshot read from the C++ core)."""
 
     request_id: object
     slot: int
@@ -65,8 +66,42 @@ class Residency:
     pages: List[List[int]] = field(default_factory=list)   # per group, by page index
     cached_prefix_pages: int = 0
     published_pages: int = 0
-    last_hash: int = 0
-    last_parent: int = -1
+
+
+class _LiveView:
+    """`manager.live`: the live requests, by request id."""
+
+    def __init__(self, manager: "CacheManager"):
+        self._m = manager
+
+    def __contains__(self, request_id) -> bool:
+        h = self._m._handles.get(request_id)
+        return h is not None and bool(self._m._lib.vh_is_live(self._m._h, ctypes.c_int64(h)))
+
+    def __getitem__(self, request_id) -> Residency:
+        m = self._m
+        if request_id not in self:
+            raise KeyError(request_id)
+        rid = ctypes.c_int64(m._handles[request_id])
+        return Residency(request_id, m._lib.vh_slot(m._h, rid), m._lib.vh_length(m._h, rid),
+                         [m.block_row(request_id, g) for g in range(len(m.groups))],
+                         m._lib.vh_residency_field(m._h, rid, 0), m._lib.vh_residency_field(m._h, rid, 1))
+
+    def _ids(self):
+        m = self._m
+        count = int(m._lib.vh_counter(m._h, 5))
+        buf = (ctypes.c_int64 * max(count, 1))()
+        m._lib.vh_live_ids(m._h, buf, count)
+        return [m._names[h] for h in buf[:count]]
+
+    def __len__(self) -> int:
+        return int(self._m._lib.vh_counter(self._m._h, 5))
+
+    def __iter__(self):
+        return iter(self._ids())
+
+    def values(self):
+        return [self[rid] for rid in self._ids()]
 
 
 class CacheManager:
@@ -77,17 +112,19 @@ class CacheManager:
         if page_size <= 0 or num_pages <= 0 or max_requests <= 0:
             raise ValueError("page_size, num_pages and max_requests must be positive")
         self.page_size, self.num_pages, self.max_requests = page_size, num_pages, max_requests
-        self.groups: List[CacheGroup] = []
         self.layer_caches: List[LayerCache] = []
+        windows: List[int] = []
+        layers_of: List[List[int]] = []
         by_window: Dict[int, int] = {}
         for layer, spec in enumerate(cache_specs):
             cache = LayerCache(page_size=page_size)
             if spec is not None:
                 if spec.window not in by_window:
-                    by_window[spec.window] = len(self.groups)
-                    self.groups.append(CacheGroup(spec.window, [], PagePool(num_pages)))
+                    by_window[spec.window] = len(windows)
+                    windows.append(spec.window)
+                    layers_of.append([])
                 cache.group = by_window[spec.window]
-                self.groups[cache.group].layers.append(layer)
+                layers_of[cache.group].append(layer)
                 if device is not None:
                     cache.tensors = tuple(
                         torch.empty((num_pages, spec.heads, page_size, spec.width), dtype=dtype, device=device)
@@ -98,16 +135,59 @@ class CacheManager:
                 self.layer_caches[layer].state = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype,
                                                              device=device)
         self.has_state = any(s is not None for s in state_specs)
-        # A published page stands for the keys of every layer; with a windowed group or
-        # per-request state a prefix would need more than pages to be reused.
-        self.prefix_reuse = (prefix_reuse and len(self.groups) == 1 and self.groups[0].window == 0
-                             and not self.has_state)
-        self.free_slots: List[int] = list(range(max_requests - 1, -1, -1))
-        self.live: Dict[object, Residency] = {}
-        self.reused_prefix_pages = 0
-        self.requests_with_reuse = 0
+        # The accounting itself is C++. A published page stands for the keys of every layer;
+        # with a windowed group or per-request state a prefix would need more than pages to
+        # be reused, so the core switches reuse off then.
+        self._lib = host.library()
+        self._ptr = self._lib.vh_create(len(windows), host.ints(windows), num_pages, page_size, max_requests,
+                                        int(prefix_reuse), int(self.has_state), max_requests, 4096, 0, 0, 0)
+        if not self._ptr:
+            raise ValueError("the host core refused the cache geometry")
+        self._h = host.handle(self._ptr)
+        self.prefix_reuse = bool(self._lib.vh_prefix_reuse(self._h))
+        self.has_windows = any(w > 0 for w in windows)
+        self.groups: List[CacheGroup] = [
+            CacheGroup(window, layers, PagePool(borrowed=self._lib.vh_group_pool(self._h, g)))
+            for g, (window, layers) in enumerate(zip(windows, layers_of))]
+        self._handles: Dict[object, int] = {}
+        self._names: Dict[int, object] = {}
+        self.live = _LiveView(self)
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            self._lib.vh_destroy(self._h)
+            self._ptr = None
+
+    def handle_of(self, request_id) -> int:
+        """The integer the C++ core knows the request by."""
+        h = self._handles.get(request_id)
+        if h is None:
+            h = len(self._handles) + 1
+            self._handles[request_id] = h
+            self._names[h] = request_id
+        return h
+
+    def _rid(self, request_id) -> ctypes.c_int64:
+        h = self._handles.get(request_id)
+        if h is None:
+            raise KeyError(f"request {request_id!r} is not live")
+        return ctypes.c_int64(h)
 
     # ------------------------------------------------------------ sizes
+    @property
+    def reused_prefix_pages(self) -> int:
+        return int(self._lib.vh_counter(self._h, 0))
+
+    @property
+    def requests_with_reuse(self) -> int:
+        return int(self._lib.vh_counter(self._h, 1))
+
+    @property
+    def free_slots(self) -> List[int]:
+        buf = (ctypes.c_int32 * self.max_requests)()
+        n = self._lib.vh_free_slots(self._h, buf, self.max_requests)
+        return list(buf[:n])
+
     def bytes_per_token(self) -> int:
         total = 0
         for cache in self.layer_caches:
@@ -119,7 +199,7 @@ class CacheManager:
         return (tokens + self.page_size - 1) // self.page_size
 
     def available_pages(self) -> int:
-        return min((g.pool.available() for g in self.groups), default=self.num_pages)
+        return self._lib.vh_available_pages(self._h)
 
     # ------------------------------------------------------------ requests
     def begin(self, request_id, prompt_for_reuse: Optional[Sequence[int]] = None) -> Residency:
@@ -127,133 +207,66 @@ class CacheManager:
         published pages that already hold the start of the prompt."""
         if request_id in self.live:
             raise ValueError(f"request {request_id!r} is already live")
-        if not self.free_slots:
-            raise OutOfSlots(f"all {self.max_requests} request slots are taken")
-        slot = self.free_slots.pop()
-        res = Residency(request_id, slot, pages=[[] for _ in self.groups])
+        rid = ctypes.c_int64(self.handle_of(request_id))
+        if prompt_for_reuse is not None and self.prefix_reuse:
+            prompt = list(prompt_for_reuse)
+            slot = host.check(self._lib.vh_begin(self._h, rid, host.ints(prompt), len(prompt)))
+        else:
+            slot = host.check(self._lib.vh_begin(self._h, rid, None, 0))
         for cache in self.layer_caches:
             if cache.state is not None:
                 cache.state[slot].zero_()
-        if self.prefix_reuse and prompt_for_reuse is not None:
-            pool = self.groups[0].pool
-            matched = pool.match(prompt_for_reuse, self.page_size)
-            for page in matched:
-                pool.acquire(page)
-            if matched:
-                res.pages[0] = list(matched)
-                res.length = len(matched) * self.page_size
-                res.cached_prefix_pages = res.published_pages = len(matched)
-                info = pool.published[matched[-1]]
-                res.last_hash, res.last_parent = info.hash_value, matched[-1]
-                self.reused_prefix_pages += len(matched)
-                self.requests_with_reuse += 1
-        self.live[request_id] = res
-        return res
+        return self.live[request_id]
 
     def pages_needed(self, request_id, new_tokens: int) -> int:
         """Fresh pages (in the most demanding group) that `extend` would take."""
-        res = self.live[request_id]
-        need = self.pages_for(res.length + new_tokens)
-        return max((need - len(res.pages[g]) for g in range(len(self.groups))), default=0)
+        return host.check(self._lib.vh_pages_needed(self._h, self._rid(request_id), new_tokens))
 
     def can_extend(self, request_id, new_tokens: int) -> bool:
-        res = self.live[request_id]
-        need = self.pages_for(res.length + new_tokens)
-        return all(need - len(res.pages[g]) <= group.pool.available()
-                   for g, group in enumerate(self.groups))
+        return bool(host.check(self._lib.vh_can_extend(self._h, self._rid(request_id), new_tokens)))
 
     def extend(self, request_id, new_tokens: int) -> List[List[int]]:
         """Reserve cache entries for the request's next `new_tokens` tokens. Returns, per
         group, the slot of each new token. All groups or none."""
-        res = self.live[request_id]
-        if new_tokens <= 0:
-            raise ValueError("extend needs at least one token")
-        if not self.can_extend(request_id, new_tokens):
-            raise OutOfPages(f"request {request_id!r}: not enough pages for {new_tokens} more tokens")
-        need = self.pages_for(res.length + new_tokens)
-        slots: List[List[int]] = []
-        P = self.page_size
-        for g, group in enumerate(self.groups):
-            extra = need - len(res.pages[g])
-            if extra > 0:
-                res.pages[g].extend(group.pool.allocate(extra))
-            row = res.pages[g]
-            slots.append([row[pos // P] * P + pos % P for pos in range(res.length, res.length + new_tokens)])
-        res.length += new_tokens
-        return slots
+        groups = len(self.groups)
+        buf = (ctypes.c_int32 * max(groups * max(new_tokens, 0), 1))()
+        host.check(self._lib.vh_extend(self._h, self._rid(request_id), new_tokens, buf))
+        return [list(buf[g * new_tokens:(g + 1) * new_tokens]) for g in range(groups)]
 
     def trim(self, request_id) -> int:
         """Give back the pages a window has passed: every query from now on sits at a
         position >= length and reads keys > position - window only."""
-        res = self.live[request_id]
-        freed = 0
-        for g, group in enumerate(self.groups):
-            if group.window <= 0:
-                continue
-            first_needed = res.length - group.window + 1
-            if first_needed <= 0:
-                continue
-            for index in range(min(first_needed // self.page_size, len(res.pages[g]))):
-                page = res.pages[g][index]
-                if page != RELEASED:
-                    group.pool.release(page)
-                    res.pages[g][index] = RELEASED
-                    freed += 1
-        return freed
+        return host.check(self._lib.vh_trim(self._h, self._rid(request_id)))
 
     def publish(self, request_id, tokens: Sequence[int]) -> int:
         """Make the request's full pages findable by later prompts; `tokens` are the
         tokens whose cache entries exist (at least `length` of them)."""
         if not self.prefix_reuse:
             return 0
-        res = self.live[request_id]
-        pool, P = self.groups[0].pool, self.page_size
-        full = res.length // P
-        done = 0
-        while res.published_pages < full:
-            i = res.published_pages
-            page = res.pages[0][i]
-            res.last_hash, res.last_parent = pool.publish(
-                page, tokens[i * P:(i + 1) * P], res.last_hash, i + 1, res.last_parent)
-            res.published_pages += 1
-            done += 1
-        return done
+        tokens = list(tokens)
+        return host.check(self._lib.vh_publish(self._h, self._rid(request_id), host.ints(tokens), len(tokens)))
 
     def finish(self, request_id) -> None:
         """The request ends: all its pages and its slot are given back."""
-        res = self.live.pop(request_id)
-        for g, group in enumerate(self.groups):
-            for page in reversed(res.pages[g]):   # leaves before their parents
-                if page != RELEASED:
-                    group.pool.release(page)
-        self.free_slots.append(res.slot)
+        host.check(self._lib.vh_finish(self._h, self._rid(request_id)))
 
     # ------------------------------------------------------------ views for the step
     def block_row(self, request_id, group: int) -> List[int]:
-        return self.live[request_id].pages[group]
+        capacity = self.num_pages + 1024
+        buf = (ctypes.c_int32 * capacity)()
+        n = host.check(self._lib.vh_block_row(self._h, self._rid(request_id), group, buf, capacity))
+        if n > capacity:
+            buf = (ctypes.c_int32 * n)()
+            host.check(self._lib.vh_block_row(self._h, self._rid(request_id), group, buf, n))
+        return list(buf[:n])
 
     def length(self, request_id) -> int:
-        return self.live[request_id].length
+        return host.check(self._lib.vh_length(self._h, self._rid(request_id)))
 
     def slot(self, request_id) -> int:
-        return self.live[request_id].slot
+        return host.check(self._lib.vh_slot(self._h, self._rid(request_id)))
 
     # ------------------------------------------------------------ checks
     def check(self) -> None:
         """No page lost, held twice without being shared on purpose, or vacant while held."""
-        slots = [r.slot for r in self.live.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self.free_slots):
-            raise PageAccountingError("a state slot is held twice or is also free")
-        if len(slots) + len(self.free_slots) != self.max_requests:
-            raise PageAccountingError("a state slot was lost")
-        for g, group in enumerate(self.groups):
-            holders: Dict[int, int] = {}
-            for res in self.live.values():
-                own = [p for p in res.pages[g] if p != RELEASED]
-                if len(set(own)) != len(own):
-                    raise PageAccountingError(f"request {res.request_id!r} lists a page twice")
-                for page in own:
-                    holders[page] = holders.get(page, 0) + 1
-            if not self.prefix_reuse and any(c > 1 for c in holders.values()):
-                raise PageAccountingError("a page is held by two requests without prefix reuse")
-            group.pool.check(holders)
+        host.check(self._lib.vh_check(self._h))

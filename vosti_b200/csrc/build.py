@@ -116,5 +116,36 @@ def library_path(build: bool = True, verbose: bool = True) -> Path:
     return lib
 
 
+HOST_LIB_NAME = "libvosti_b200_host.so"
+
+
+def host_library_path(verbose: bool = True) -> Path:
+    """The C++ host core (no CUDA in it), compiled with g++ on first use."""
+    out_dir = _build_dir()
+    lib, stamp = out_dir / HOST_LIB_NAME, out_dir / "host_stamp.txt"
+    sources = sorted((HERE / "host").glob("*.cpp"))
+    h = hashlib.sha256()
+    for path in sources:
+        h.update(path.read_bytes())
+    digest = h.hexdigest()
+    if lib.is_file() and stamp.is_file() and stamp.read_text().strip() == digest:
+        return lib
+    compiler = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if not compiler:
+        raise RuntimeError("vosti_b200 needs a C++ compiler (g++) for its host core and found none")
+    if verbose:
+        _say(f"compiling the C++ host core into {out_dir}")
+    tmp = out_dir / (HOST_LIB_NAME + f".tmp{os.getpid()}")
+    cmd = [compiler, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-o", str(tmp),
+           *[str(s) for s in sources]]
+    result = subprocess.run(cmd, capture_output=True, text=True)
+    if result.returncode != 0:
+        raise RuntimeError(f"compiling the host core failed:\n{result.stdout}\n{result.stderr}")
+    os.replace(tmp, lib)
+    stamp.write_text(digest)
+    return lib
+
+
 if __name__ == "__main__":
     print(library_path())
+    print(host_library_path())

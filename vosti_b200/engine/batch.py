@@ -12,8 +12,12 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
+import ctypes
+
 import numpy as np
 import torch
+
+from .. import host
 
 
 @dataclass
@@ -110,20 +114,33 @@ def _round_up(value: int, multiple: int) -> int:
     return (value + multiple - 1) // multiple * multiple
 
 
-def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: Sequence[int],
-                  slots_per_group: Sequence[Sequence[Sequence[int]]], block_rows: Sequence[Sequence[Sequence[int]]],
-                  state_slots: Sequence[int], page_size: int, status: torch.Tensor, dtype: torch.dtype,
-                  extras: Optional[dict] = None, min_pages: int = 0, kv_bucket: int = 0) -> StepContext:
-    """Lay the batch out and copy it. `starts[i]` is the position of entry i's first token;
-    `slots_per_group[g][i]` the cache slots of its tokens in group g; `block_rows[g][i]` its
-    page ids in group g."""
+def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], status: torch.Tensor,
+                  dtype: torch.dtype, extras: Optional[dict] = None, min_pages: int = 0, kv_bucket: int = 0,
+                  position_limit: int = 0) -> StepContext:
+    """Reserve cache entries for the step's tokens (all requests or none), lay the batch out
+    in the pinned staging buffer and copy it. The reservation and the index arrays
+    (positions, slots, block tables, ...) are written by the C++ host core straight into the
+    staging buffer; tokens and wanted rows come from the entries."""
     B = len(entries)
+    if B == 0:
+        raise ValueError("a step needs at least one entry")
     q_lens = [len(e.tokens) for e in entries]
+    handles = []
+    for e in entries:
+        h = cache._handles.get(e.request_id)
+        if h is None:
+            raise KeyError(f"request {e.request_id!r} is not live")
+        handles.append(h)
+    G = len(cache.groups)
+    ids = (ctypes.c_int64 * B)(*handles)
+    counts = (ctypes.c_int32 * B)(*q_lens)
+    starts = (ctypes.c_int32 * B)()
+    widest = (ctypes.c_int32 * max(G, 1))()
+    lib = host.library()
+    host.check(lib.vh_step_extend(cache._h, ids, counts, B, position_limit, starts, widest))
     T = sum(q_lens)
     W = sum(len(e.want) for e in entries)
-    G = len(slots_per_group)
-    max_pages = [max(min_pages, _round_up(max((len(r) for r in block_rows[g]), default=1) or 1, 4))
-                 for g in range(G)]
+    max_pages = [max(min_pages, _round_up(max(widest[g], 1), 4)) for g in range(G)]
     # sections are padded to 4 ints so that every section starts 16-byte aligned
     sizes = [T, T, T, B + 1, B, B, W] + [x for g in range(G) for x in (T, B * max_pages[g])]
     offsets, total = [], 0
@@ -138,8 +155,7 @@ def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: 
         else:
             long_rows.append(i)
         cursor += n
-    mixed = bool(short_tokens) and bool(long_rows)
-    if mixed:
+    if short_tokens and long_rows:
         extras["_short_tokens"] = np.asarray(short_tokens, dtype=np.int32)
         extras["_long_rows"] = np.asarray(long_rows, dtype=np.int32)
     extra_at = {}
@@ -151,53 +167,41 @@ def build_context(staging: StagingBuffer, entries: Sequence[StepEntry], starts: 
     buf = staging.host_np
     o_tok, o_pos, o_req, o_cu, o_kv, o_slot, o_want = offsets[:7]
     cursor, wcursor = 0, 0
-    buf[o_cu] = 0
-    kv_lens = []
     for i, e in enumerate(entries):
         n = q_lens[i]
-        buf[o_tok + cursor:o_tok + cursor + n] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
-        buf[o_pos + cursor:o_pos + cursor + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
-        buf[o_req + cursor:o_req + cursor + n] = i
+        buf[o_tok + cursor:o_tok + cursor + n] = e.tokens
         for w in e.want:
             if not 0 <= w < n:
                 raise ValueError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
             buf[o_want + wcursor] = cursor + w
             wcursor += 1
         cursor += n
-        buf[o_cu + i + 1] = cursor
-        buf[o_kv + i] = starts[i] + n
-        kv_lens.append(starts[i] + n)
-        buf[o_slot + i] = state_slots[i]
-    group_offsets = []
-    for g in range(G):
-        o_sm, o_bt = offsets[7 + 2 * g], offsets[8 + 2 * g]
-        cursor = 0
-        for i in range(B):
-            n = q_lens[i]
-            buf[o_sm + cursor:o_sm + cursor + n] = slots_per_group[g][i]
-            cursor += n
-            row = block_rows[g][i]
-            base = o_bt + i * max_pages[g]
-            buf[base:base + len(row)] = row
-            buf[base + len(row):base + max_pages[g]] = 0
-        group_offsets.append((o_sm, o_bt))
-    for name, (at, words, _) in extra_at.items():
-        buf[at:at + words.size] = words
+    base = staging.host.data_ptr()
+    at = lambda offset: ctypes.cast(base + 4 * offset, host.i32p)
+    slot_ptrs = (host.i32p * max(G, 1))(*[at(offsets[7 + 2 * g]) for g in range(G)])
+    table_ptrs = (host.i32p * max(G, 1))(*[at(offsets[8 + 2 * g]) for g in range(G)])
+    widths = (ctypes.c_int32 * max(G, 1))(*max_pages)
+    host.check(lib.vh_step_fill(cache._h, ids, counts, starts, B, at(o_pos), at(o_req), at(o_cu), at(o_kv),
+                                at(o_slot), slot_ptrs, table_ptrs, widths))
+    for name, (where, words, _) in extra_at.items():
+        buf[where:where + words.size] = words
     staging.upload(total)
     dev = staging.dev
     torch_types = {np.dtype(np.float32): torch.float32, np.dtype(np.int64): torch.int64,
                    np.dtype(np.int32): torch.int32}
-    extra_views = {name: dev[at:at + words.size].view(torch_types[np.dtype(kind)])
-                   for name, (at, words, kind) in extra_at.items()}
-    groups = [GroupView(block_table=dev[o_bt:o_bt + B * max_pages[g]].view(B, max_pages[g]),
-                        slot_mapping=dev[o_sm:o_sm + T], page_size=page_size, max_pages=max_pages[g])
-              for g, (o_sm, o_bt) in enumerate(group_offsets)]
+    extra_views = {name: dev[where:where + words.size].view(torch_types[np.dtype(kind)])
+                   for name, (where, words, kind) in extra_at.items()}
+    groups = [GroupView(block_table=dev[offsets[8 + 2 * g]:offsets[8 + 2 * g] + B * max_pages[g]].view(B, max_pages[g]),
+                        slot_mapping=dev[offsets[7 + 2 * g]:offsets[7 + 2 * g] + T], page_size=cache.page_size,
+                        max_pages=max_pages[g]) for g in range(G)]
+    kv_lens = [starts[i] + q_lens[i] for i in range(B)]
+    state_slots = buf[o_slot:o_slot + B].tolist()
     return StepContext(
         num_tokens=T, num_requests=B, tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T],
         request_of=dev[o_req:o_req + T], cu_q=dev[o_cu:o_cu + B + 1], kv_len=dev[o_kv:o_kv + B],
         state_slots=dev[o_slot:o_slot + B], want_rows=dev[o_want:o_want + W], groups=groups, status=status,
         dtype=dtype, device=staging.device, host_q_lens=q_lens, host_kv_lens=kv_lens,
-        host_state_slots=list(state_slots), max_q_len=max(q_lens, default=0),
+        host_state_slots=state_slots, max_q_len=max(q_lens, default=0),
         max_kv_len=max(kv_bucket, max(kv_lens, default=0)), all_decode=all(n == 1 for n in q_lens), extras=extra_views,
         short_tokens=extra_views.pop("_short_tokens", None), num_short_tokens=len(short_tokens),
         long_rows=extra_views.pop("_long_rows", None), num_long_rows=len(long_rows),

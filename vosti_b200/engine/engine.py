@@ -87,7 +87,7 @@ class Engine:
         entries, temps, seeds, counters = [], [], [], []
         for row in plan.rows:
             request = row.request
-            tokens = request.tokens()[row.start:row.start + row.count]
+            tokens = request.token_range(row.start, row.count)
             entries.append(StepEntry(request.request_id, tokens, [row.count - 1] if row.sample else []))
             if row.sample:
                 temps.append(request.temperature)
@@ -99,7 +99,7 @@ class Engine:
         sampled: List[Optional[int]] = [None] * len(plan.rows)
         count = len(temps)
         if self.graphs is not None and all(row.count == 1 and row.sample for row in plan.rows):
-            self.graphs.step(entries, extras)
+            self.graphs.step(entries, extras, longest=max(row.start for row in plan.rows) + 1)
         else:
             ctx = runner.prepare(entries, extras=extras)
             logits = runner.run(ctx)
@@ -117,8 +117,9 @@ class Engine:
         for i, row in enumerate(plan.rows):
             if row.sample:
                 sampled[i] = next(it)
-        for e in entries:
-            runner.cache.trim(e.request_id)
+        if runner.cache.has_windows:
+            for e in entries:
+                runner.cache.trim(e.request_id)
         emitted = self.scheduler.commit(plan, sampled)
         self._trace(plan, emitted)
         return emitted

@@ -48,11 +48,12 @@ class DecodeGraphs:
         sample_rows(logits, ex.get("temperature"), ex.get("seeds"), ex.get("counters"),
                     out=runner.result[1:1 + count])
 
-    def step(self, entries: Sequence[StepEntry], extras: Optional[dict]) -> None:
+    def step(self, entries: Sequence[StepEntry], extras: Optional[dict], longest: Optional[int] = None) -> None:
         """Run a decode-only step; the sampled tokens are left in runner.result[1:1+B]."""
         runner, cache = self.runner, self.runner.cache
         count = len(entries)
-        longest = max(cache.length(e.request_id) for e in entries) + 1
+        if longest is None:
+            longest = max(cache.length(e.request_id) for e in entries) + 1
         pages = _round_up(cache.pages_for(longest), PAGES_BUCKET)
         kv_bucket = _round_up(longest, KV_BUCKET)
         key = (count, tuple(sorted(extras)) if extras else (), pages, kv_bucket)

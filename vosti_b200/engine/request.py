@@ -47,6 +47,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt_tokens + self.generated
 
+    def token_range(self, start: int, count: int) -> List[int]:
+        """tokens()[start:start + count] without building the whole list."""
+        p = len(self.prompt_tokens)
+        if start >= p:
+            return self.generated[start - p:start - p + count]
+        if start + count <= p:
+            return self.prompt_tokens[start:start + count]
+        return self.prompt_tokens[start:] + self.generated[:start + count - p]
+
     def num_tokens(self) -> int:
         return len(self.prompt_tokens) + len(self.generated)
 

@@ -92,39 +92,8 @@ class ModelRunner:
                 kv_bucket: int = 0) -> StepContext:
         """Reserve cache entries for the step's tokens (all requests or none) and copy the
         batch to the device."""
-        cache = self.cache
-        if not entries:
-            raise ValueError("a step needs at least one entry")
-        seen = set()
-        for e in entries:
-            if e.request_id in seen:
-                raise ValueError(f"request {e.request_id!r} appears twice in one step")
-            seen.add(e.request_id)
-            if e.request_id not in cache.live:
-                raise KeyError(f"request {e.request_id!r} is not live")
-            if len(e.tokens) == 0:
-                raise ValueError(f"request {e.request_id!r} brings no tokens")
-        for g, group in enumerate(cache.groups):
-            need = 0
-            for e in entries:
-                res = cache.live[e.request_id]
-                need += max(0, cache.pages_for(res.length + len(e.tokens)) - len(res.pages[g]))
-            if need > group.pool.available():
-                raise OutOfPages(f"step needs {need} pages in group {g}, {group.pool.available()} available")
-        starts = [cache.length(e.request_id) for e in entries]
-        limit = self.spec.max_positions
-        for e, start in zip(entries, starts):
-            if start + len(e.tokens) > limit:
-                raise ValueError(f"request {e.request_id!r} would reach position {start + len(e.tokens)}, "
-                                 f"the model's limit is {limit}")
-        slots = [cache.extend(e.request_id, len(e.tokens)) for e in entries]
-        G = len(cache.groups)
-        slots_per_group = [[slots[i][g] for i in range(len(entries))] for g in range(G)]
-        block_rows = [[cache.block_row(e.request_id, g) for e in entries] for g in range(G)]
-        state_slots = [cache.slot(e.request_id) for e in entries]
-        return build_context(self.staging, entries, starts, slots_per_group, block_rows, state_slots,
-                             cache.page_size, self.status, self.dtype, extras=extras, min_pages=min_pages,
-                             kv_bucket=kv_bucket)
+        return build_context(self.staging, self.cache, entries, self.status, self.dtype, extras=extras,
+                             min_pages=min_pages, kv_bucket=kv_bucket, position_limit=self.spec.max_positions)
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """The model over the prepared batch; float32 logits [wanted, vocab] or None."""
@@ -137,8 +106,9 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         ctx = self.prepare(entries)
         logits = self.run(ctx)
-        for e in entries:
-            self.cache.trim(e.request_id)
+        if self.cache.has_windows:
+            for e in entries:
+                self.cache.trim(e.request_id)
         return logits
 
     # ------------------------------------------------------------ status

@@ -26,9 +26,11 @@ cache is finished with reason "capacity".
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+from .. import host
 from ..cache import CacheManager
 from .request import MAX_EOS_TOKEN_IDS, AdmissionStatus, Request
 
@@ -66,162 +68,136 @@ class StepPlan:
         return sum(r.count for r in self.rows)
 
 
+_ADMISSION = [AdmissionStatus.ACCEPTED, AdmissionStatus.DUPLICATE_ID, AdmissionStatus.EMPTY_PROMPT,
+              AdmissionStatus.BAD_EOS, AdmissionStatus.ZERO_BUDGET, AdmissionStatus.TOO_LONG,
+              AdmissionStatus.BAD_TOKEN, AdmissionStatus.BAD_SAMPLING]
+_FINISH = {1: "length", 2: "eos", 3: "capacity", 4: "aborted"}
+
+
 class Scheduler:
+    """Python face of the C++ scheduler (vosti_b200/csrc/host/engine_core.cpp), which shares
+    its state with the cache manager's core. `Request` objects are kept here and updated from
+    what the core decides."""
+
     def __init__(self, cache: CacheManager, config: SchedulerConfig):
         config.validate()
         self.cache, self.config = cache, config
-        self.waiting: List[Request] = []
-        self.running: List[Request] = []
+        self._lib, self._h = host.library(), cache._h
+        self._lib.vh_configure_scheduler(self._h, config.max_num_seqs, config.max_num_batched_tokens,
+                                         config.prefill_chunk_size, config.vocab_size, config.max_context)
+        self._requests: Dict[object, Request] = {}
         self.accepted_ids = set()            # ids are never reused (src/exec/cache_scheduler/types.rs:162-165)
         self.finished: Dict[object, Request] = {}
-        self.admitted_requests = 0
-        self.preemptions = 0
+        capacity = max(config.max_num_seqs, cache.max_requests, 1) + 8
+        self._capacity = capacity
+        self._ids = (ctypes.c_int64 * capacity)()
+        self._rows = (ctypes.c_int32 * (3 * capacity))()
+        self._side = (ctypes.c_int64 * 4096)()
+        self._side2 = (ctypes.c_int64 * 4096)()
+
+    # ------------------------------------------------------------ counters and queues
+    @property
+    def admitted_requests(self) -> int:
+        return int(self._lib.vh_counter(self._h, 2))
+
+    @property
+    def preemptions(self) -> int:
+        return int(self._lib.vh_counter(self._h, 3))
+
+    def _queue(self, which: int) -> List[Request]:
+        buf = (ctypes.c_int64 * 65536)()
+        n = min(self._lib.vh_queue(self._h, which, buf, 65536), 65536)
+        return [self._requests[self.cache._names[h]] for h in buf[:n]]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._queue(0)
+
+    @property
+    def running(self) -> List[Request]:
+        return self._queue(1)
 
     # ------------------------------------------------------------ admission
     def add_request(self, request: Request) -> AdmissionStatus:
-        cfg = self.config
         if request.request_id in self.accepted_ids:
             return AdmissionStatus.DUPLICATE_ID
-        if len(request.prompt_tokens) == 0:
-            return AdmissionStatus.EMPTY_PROMPT
-        if not request.ignore_eos and not 1 <= len(request.eos_token_ids) <= MAX_EOS_TOKEN_IDS:
-            return AdmissionStatus.BAD_EOS
-        if len(request.eos_token_ids) > MAX_EOS_TOKEN_IDS:
-            return AdmissionStatus.BAD_EOS
-        if request.max_tokens <= 0:
-            return AdmissionStatus.ZERO_BUDGET
-        if not (request.temperature >= 0.0 and request.temperature < float("inf")):
-            return AdmissionStatus.BAD_SAMPLING
-        if cfg.max_context and len(request.prompt_tokens) + request.max_tokens > cfg.max_context:
-            return AdmissionStatus.TOO_LONG
-        if cfg.vocab_size and any(not 0 <= int(t) < cfg.vocab_size for t in request.prompt_tokens):
+        prompt = [int(t) for t in request.prompt_tokens]
+        if any(not -2 ** 31 <= t < 2 ** 31 for t in prompt):
             return AdmissionStatus.BAD_TOKEN
-        self.accepted_ids.add(request.request_id)
-        self.waiting.append(request)
-        return AdmissionStatus.ACCEPTED
+        eos = [int(t) for t in request.eos_token_ids]
+        rid = self.cache.handle_of(request.request_id)
+        temperature = request.temperature if request.temperature == request.temperature else -1.0
+        code = self._lib.vh_add_request(self._h, ctypes.c_int64(rid), host.ints(prompt), len(prompt),
+                                        int(request.max_tokens) if request.max_tokens < 2 ** 31 else 2 ** 31 - 1,
+                                        host.ints(eos[:4]), len(eos), int(request.ignore_eos),
+                                        ctypes.c_float(temperature))
+        status = _ADMISSION[code]
+        if status is AdmissionStatus.ACCEPTED:
+            self.accepted_ids.add(request.request_id)
+            self._requests[request.request_id] = request
+        return status
 
     def abort(self, request_id) -> bool:
         """End a request now: it leaves its queue and gives back what it holds."""
-        for queue in (self.waiting, self.running):
-            for request in queue:
-                if request.request_id == request_id:
-                    queue.remove(request)
-                    if request_id in self.cache.live:
-                        self.cache.finish(request_id)
-                    request.finished, request.finish_reason = True, "aborted"
-                    self.finished[request_id] = request
-                    return True
-        return False
+        request = self._requests.get(request_id)
+        if request is None or request.finished:
+            return False
+        if not self._lib.vh_abort(self._h, ctypes.c_int64(self.cache.handle_of(request_id))):
+            return False
+        request.finished, request.finish_reason = True, "aborted"
+        self.finished[request_id] = request
+        return True
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.vh_unfinished(self._h))
 
     # ------------------------------------------------------------ planning
-    def _chunk(self, remaining: int, budget: int) -> int:
-        """Tokens of the next portion: everything if it fits, else whole pages."""
-        cap = budget
-        if self.config.prefill_chunk_size:
-            cap = min(cap, self.config.prefill_chunk_size)
-        if remaining <= cap:
-            return remaining
-        return cap // self.cache.page_size * self.cache.page_size
-
-    def _plan_once(self) -> StepPlan:
-        cache, cfg = self.cache, self.config
-        plan = StepPlan()
-        budget = cfg.max_num_batched_tokens
-        reserved = 0
-
-        # 1. decode rows: a prefix of the running requests
-        for request in self.running:
-            if not request.is_decoding():
-                continue
-            if len(plan.rows) >= cfg.max_num_seqs:
-                break
-            need = cache.pages_needed(request.request_id, 1)
-            if reserved + need > cache.available_pages():
-                break
-            plan.rows.append(PlanRow(request, request.computed, 1, True))
-            reserved += need
-            budget -= 1
-
-        # 2. running requests in the middle of their prompt
-        for request in self.running:
-            if request.is_decoding() or len(plan.rows) >= cfg.max_num_seqs:
-                continue
-            count = self._chunk(request.remaining(), max(budget, 0))
-            if count <= 0:
-                continue
-            need = cache.pages_needed(request.request_id, count)
-            if reserved + need > cache.available_pages():
-                continue
-            plan.rows.append(PlanRow(request, request.computed, count, count == request.remaining()))
-            reserved += need
-            budget -= count
-
-        # 3. admissions: the head of the waiting queue only
-        while self.waiting and len(plan.rows) < cfg.max_num_seqs and budget > 0:
-            if len(self.running) >= cache.max_requests or not cache.free_slots:
-                break
-            request = self.waiting[0]
-            tokens = request.tokens()
-            cache.begin(request.request_id, tokens)
-            request.computed = cache.length(request.request_id)
-            count = self._chunk(request.remaining(), budget)
-            need = cache.pages_needed(request.request_id, count) if count > 0 else 0
-            if count <= 0 or reserved + need > cache.available_pages():
-                cache.finish(request.request_id)      # roll back: nothing of it is held
-                request.computed = 0
-                break
-            self.waiting.pop(0)
-            self.running.append(request)
-            self.admitted_requests += 1
-            plan.rows.append(PlanRow(request, request.computed, count, count == request.remaining()))
-            reserved += need
-            budget -= count
-        return plan
-
     def plan(self) -> StepPlan:
         """Decide the next step's batch. Never returns an empty plan while a request is
         live: it preempts (or, for a request no cache could hold, drops) until a row fits."""
-        preempted, dropped = [], []
-        while True:
-            plan = self._plan_once()
-            if plan.rows or not self.has_unfinished():
-                break
-            if self.running:
-                victim = self.running.pop()           # the youngest
-                self.cache.finish(victim.request_id)
-                victim.computed = 0
-                victim.preemptions += 1
-                self.preemptions += 1
-                self.waiting.insert(0, victim)
-                preempted.append(victim.request_id)
-                continue
-            # nothing runs and the head still does not fit: no cache of this size can hold it
-            victim = self.waiting.pop(0)
-            victim.finished, victim.finish_reason = True, "capacity"
-            self.finished[victim.request_id] = victim
-            dropped.append(victim.request_id)
-        plan.preempted, plan.dropped = preempted, dropped
+        n_pre, n_drop = ctypes.c_int32(0), ctypes.c_int32(0)
+        n = host.check(self._lib.vh_plan(self._h, self._ids, self._rows, self._capacity, self._side,
+                                         ctypes.byref(n_pre), self._side2, ctypes.byref(n_drop), 4096))
+        names = self.cache._names
+        plan = StepPlan()
+        for h in self._side[:n_pre.value]:
+            request = self._requests[names[h]]
+            request.computed = 0
+            request.preemptions += 1
+            plan.preempted.append(request.request_id)
+        for h in self._side2[:n_drop.value]:
+            request = self._requests[names[h]]
+            request.finished, request.finish_reason = True, "capacity"
+            self.finished[request.request_id] = request
+            plan.dropped.append(request.request_id)
+        rows = self._rows
+        for i in range(n):
+            request = self._requests[names[self._ids[i]]]
+            request.computed = rows[3 * i]
+            plan.rows.append(PlanRow(request, rows[3 * i], rows[3 * i + 1], bool(rows[3 * i + 2])))
         return plan
 
     # ------------------------------------------------------------ commit
     def commit(self, plan: StepPlan, sampled: Sequence[Optional[int]]) -> Dict[object, int]:
         """Apply a step's results: `sampled[i]` is the token of row i (ignored for rows that
         do not sample). Returns request id -> emitted token."""
-        emitted: Dict[object, int] = {}
+        count = len(plan.rows)
+        tokens = []
         for row, token in zip(plan.rows, sampled):
+            if row.sample and token is None:
+                raise ValueError(f"row of request {row.request.request_id!r} samples but got no token")
+            tokens.append(int(token) if row.sample else -1)
+        finished = (ctypes.c_int32 * max(count, 1))()
+        host.check(self._lib.vh_commit(self._h, host.ints(tokens), count, finished))
+        emitted: Dict[object, int] = {}
+        for i, row in enumerate(plan.rows):
             request = row.request
             request.computed += row.count
-            self.cache.publish(request.request_id, request.tokens()[:request.computed])
             if not row.sample:
                 continue
-            if token is None:
-                raise ValueError(f"row of request {request.request_id!r} samples but got no token")
-            emitted[request.request_id] = int(token)
-            if request.record(int(token)):
-                self.running.remove(request)
-                self.cache.finish(request.request_id)
+            request.generated.append(tokens[i])
+            emitted[request.request_id] = tokens[i]
+            if finished[i]:
+                request.finished, request.finish_reason = True, _FINISH[finished[i]]
                 self.finished[request.request_id] = request
         return emitted
