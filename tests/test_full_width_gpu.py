@@ -1,0 +1,43 @@
+"""The engine at the benchmark model's layer sizes (hidden 4096, 32 query / 8 kv heads of
+128, intermediate 12288) with two layers and a smaller vocabulary that is no power of two,
+against the plain implementation: a whole prompt, a decoded tail and portions, in float32
+and bfloat16. This is where the kernels meet the tile sizes they are tuned for."""
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import replay_util as R
+from tiny_configs import _config
+
+pytestmark = pytest.mark.gpu
+
+WIDE = _config(num_hidden_layers=2, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=12288, vocab_size=20011, rope_theta=1000000.0, rms_norm_eps=1e-6,
+               tie_word_embeddings=False, max_position_embeddings=4096)
+
+
+@pytest.fixture(scope="module")
+def wide_model(tmp_path_factory):
+    from vosti_b200.weights import write_random_model
+    folder = tmp_path_factory.mktemp("wide")
+    write_random_model(folder, WIDE, seed=3)
+    return str(folder), plain.load_model(folder)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_benchmark_layer_sizes(wide_model, dtype, tmp_path):
+    path, plain_model = wide_model
+    requests = {"p": R.random_tokens(WIDE["vocab_size"], 333, seed=9), "q": R.random_tokens(WIDE["vocab_size"], 150, seed=10)}
+    steps, alias = [], {}
+    for kind, make in (("whole", R.whole_steps), ("tail", R.tail_steps),
+                       ("portion", lambda reqs: R.portion_steps(reqs, sizes=(130, 2, 64, 7, 200))),
+                       ("mixed", lambda reqs: R.mixed_steps(reqs, seed=5))):
+        renamed = {f"{kind}-{rid}": tokens for rid, tokens in requests.items()}
+        alias.update({f"{kind}-{rid}": rid for rid in requests})
+        steps.extend(make(renamed))
+    steps = R.number(steps)
+    R.run_in_process(path, dtype, steps, R.max_live_tokens(steps), 16, tmp_path)
+    rows = R.collect(steps, tmp_path, WIDE["vocab_size"])
+    assert len(rows) == 4 * sum(len(t) for t in requests.values())
+    worst = R.compare_with_plain(rows, requests, plain_model, dtype, alias=lambda rid: alias[rid])
+    print(f"benchmark layer sizes, {dtype}: worst error {worst:.3e} of the largest logit")
