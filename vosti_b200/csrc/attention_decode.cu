@@ -7,8 +7,8 @@
 //   quarter of the segment (four tiles of 16 keys through two buffers: two tiles are
 //   requested before any arithmetic, the others as buffers become free), run the online softmax (base 2, float32) with mma.sync m16n8k16 for
 //   Q.K^T and P.V, and are merged in warp order. The CTA writes
-//   an unnormalised partial (max, sum, accumulator) per query head; a second kernel merges
-//   the segments in segment order and normalises.
+//   an unnormalised partial (max, sum, accumulator) per query head; the CTA that finishes
+//   last for a (token, kv head) merges the segments in segment order and normalises.
 //
 // The segmentation depends on the key index only, so a row's arithmetic does not depend
 // on its batch companions. Formulas as in kernels/triton_kernels/fattn_paged.py:176-252:
@@ -32,12 +32,73 @@ constexpr float LOG2E = 1.4426950408889634f;
 // [2 .. 2+d) accumulator.
 __host__ __device__ inline int record_floats(int d) { return d + 2; }
 
+// One warp combines the segments first..last of one (token, query head): lane s holds
+// segment s's max and weight; the sums run over segments in segment order, whichever CTA
+// runs this. `base` points at the head's records, `dst` at its output row.
+__device__ __forceinline__ void merge_segments(const float* __restrict__ base, bf16* __restrict__ dst, int first,
+                                               int last, int d) {
+  const int lane = threadIdx.x & 31;
+  const int rec = d + 2;
+  // pass 1: the overall maximum
+  float m = -INFINITY;
+  for (int s0 = first; s0 <= last; s0 += 32) {
+    const int s = s0 + lane;
+    m = fmaxf(m, s <= last ? __ldcg(base + (int64_t)s * rec) : -INFINITY);
+  }
+  m = warp_max(m);
+  // pass 2: weights, sum and accumulator
+  float l = 0.f;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int s0 = first; s0 <= last; s0 += 32) {
+    const int mine = s0 + lane;
+    float w_mine = 0.f, l_mine = 0.f;
+    if (mine <= last) {
+      const float ms = __ldcg(base + (int64_t)mine * rec);
+      if (ms != -INFINITY) {
+        w_mine = fast_exp2(ms - m);
+        l_mine = __ldcg(base + (int64_t)mine * rec + 1) * w_mine;
+      }
+    }
+    const int n = min(32, last - s0 + 1);
+    // segments in batches of 4: their loads are issued together, then summed in segment order
+    for (int j0 = 0; j0 < n; j0 += 4) {
+      float v[4][8];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = lane + 32 * i;
+          v[b][i] = (c < d) ? __ldcg(row + c) : 0.f;       // other CTAs wrote these: read past L1
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const bool live = j0 + b < n;
+        const float w = live ? __shfl_sync(0xffffffffu, w_mine, (j0 + b) & 31) : 0.f;
+        l += live ? __shfl_sync(0xffffffffu, l_mine, (j0 + b) & 31) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[b][i], w, acc[i]);
+      }
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = lane + 32 * i;
+    if (c < d) dst[c] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
 // DMAX bounds the head size; with EXACT the head size is DMAX itself, which turns the index
 // arithmetic of the staging loops into shifts.
 template <int DMAX, bool EXACT>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                        float* __restrict__ partial, const int* __restrict__ token_list,
+                        float* __restrict__ partial, bf16* __restrict__ out, int* __restrict__ arrivals,
+                        const int* __restrict__ token_list,
                         const int* __restrict__ positions, const int* __restrict__ request_of,
                         const int* __restrict__ block_table, int max_pages, int page_size, int page_shift,
                         int num_pages, int nq, int nkv, int d_runtime, int max_segments, float scale_log2, int window, unsigned* status) {
@@ -260,77 +321,25 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
       dst[c] = value;
     }
   }
-}
-
-// One warp per (token, query head): combine the segments. Lane s holds segment s's max and
-// weight; the sums run over segments in segment order.
-__global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
-                                       const int* __restrict__ token_list, const int* __restrict__ positions,
-                                       int count, int nq, int d, int max_segments, int window) {
-  pdl_wait();
-  pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (wid >= (int64_t)count * nq) return;
-  const int item = (int)(wid / nq);
-  const int t = token_list ? token_list[item] : item;
-  const int h = (int)(wid % nq);
-  const int pos = positions[t];
-  const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int first = kstart / SEGMENT, last = pos / SEGMENT;
-  const int rec = d + 2;
-  const float* base = partial + ((int64_t)item * nq + h) * max_segments * rec;
-  // pass 1: the overall maximum
-  float m = -INFINITY;
-  for (int s0 = first; s0 <= last; s0 += 32) {
-    const int s = s0 + lane;
-    m = fmaxf(m, s <= last ? base[(int64_t)s * rec] : -INFINITY);
+  // ---- the CTA that finishes last for this (token, kv head) merges the segments. No CTA
+  // waits for another: each counts itself in after its records are visible device-wide.
+  __shared__ int last_to_arrive;
+  __threadfence();
+  __syncthreads();
+  const int first_segment = kstart / SEGMENT, last_segment = pos / SEGMENT;
+  if (threadIdx.x == 0) {
+    int* counter = arrivals + (int64_t)blockIdx.z * nkv + g;
+    const int before = atomicAdd(counter, 1);
+    last_to_arrive = before == last_segment - first_segment;
+    if (last_to_arrive) *counter = 0;               // ready for the next launch
   }
-  m = warp_max(m);
-  // pass 2: weights, sum and accumulator
-  float l = 0.f;
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int s0 = first; s0 <= last; s0 += 32) {
-    const int mine = s0 + lane;
-    float w_mine = 0.f, l_mine = 0.f;
-    if (mine <= last) {
-      const float ms = base[(int64_t)mine * rec];
-      if (ms != -INFINITY) {
-        w_mine = fast_exp2(ms - m);
-        l_mine = base[(int64_t)mine * rec + 1] * w_mine;
-      }
-    }
-    const int n = min(32, last - s0 + 1);
-    // segments in batches of 4: their loads are issued together, then summed in segment order
-    for (int j0 = 0; j0 < n; j0 += 4) {
-      float v[4][8];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int c = lane + 32 * i;
-          v[b][i] = (c < d) ? row[c] : 0.f;
-        }
-      }
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const bool live = j0 + b < n;
-        const float w = live ? __shfl_sync(0xffffffffu, w_mine, (j0 + b) & 31) : 0.f;
-        l += live ? __shfl_sync(0xffffffffu, l_mine, (j0 + b) & 31) : 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[b][i], w, acc[i]);
-      }
-    }
-  }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  bf16* dst = out + ((int64_t)t * nq + h) * d;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int c = lane + 32 * i;
-    if (c < d) dst[c] = __float2bfloat16_rn(acc[i] * inv);
+  __syncthreads();
+  if (!last_to_arrive) return;
+  __threadfence();
+  for (int row = warp; row < group; row += WARPS) {
+    const int h = g * group + row;
+    merge_segments(partial + ((int64_t)blockIdx.z * nq + h) * max_segments * rec, out + ((int64_t)t * nq + h) * d,
+                   first_segment, last_segment, d);
   }
 }
 
@@ -353,11 +362,12 @@ VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int d, int m
 }
 
 // caches: bf16 [pages, kv heads, page_size, d] (a head's tokens of a page are contiguous).
+// arrivals: int32[count * nkv], all zero before the first launch; every launch leaves it zero.
 // q, out: bf16 [tokens_total, nq, d]; the kernel serves `count` tokens: those listed in
 // token_list (int32[count]) or tokens 0..count-1. scratch holds the partial records of the
 // launch (vosti_attention_decode_scratch elements) and may be reused by the next launch.
 VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* scratch,
-                                     int64_t scratch_elems, const int* token_list, int count, int tokens_total,
+                                     int64_t scratch_elems, int* arrivals, const int* token_list, int count, int tokens_total,
                                      const int* positions, const int* request_of, const int* block_table, int max_pages,
                                      int page_size, int num_pages, int nq, int nkv, int d, int max_kv_len, float scale,
                                      int window, unsigned* status, cudaStream_t stream) {
@@ -368,6 +378,7 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   if (count == 0) return VOSTI_OK;
   const int segments = vosti_attention_decode_segments(max_kv_len);
   VOSTI_REQUIRE(segments >= 1 && segments <= 65535, "attention_decode: context %d too long", max_kv_len);
+  VOSTI_REQUIRE(arrivals != nullptr, "attention_decode: the arrival counters are missing");
   VOSTI_REQUIRE(scratch != nullptr && scratch_elems >= vosti_attention_decode_scratch(count, nq, d, max_kv_len),
                 "attention_decode: scratch too small");
   const size_t smem = decode_smem_bytes(d);
@@ -385,7 +396,8 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
       configured = true;                                                                                            \
     }                                                                                                               \
     vosti_launch(attention_decode_kernel<DMAX, EXACT>, grid, dim3(WARPS * 32), smem, stream,                        \
-        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, scratch, token_list, positions, request_of,      \
+        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, scratch, (bf16*)out, arrivals, token_list,      \
+        positions, request_of,                                                                                      \
         block_table, max_pages, page_size, page_shift, num_pages, nq, nkv, d, segments, scale * LOG2E, window,      \
         status);                                                                                                    \
   } while (0)
@@ -396,8 +408,5 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   else if (d < 128) LAUNCH_DECODE(128, false);
   else LAUNCH_DECODE(256, false);
 #undef LAUNCH_DECODE
-  const int64_t warps = (int64_t)count * nq;
-  vosti_launch(attention_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)scratch,
-               (bf16*)out, token_list, positions, count, nq, d, segments, window);
   VOSTI_LAUNCH_CHECK();
 }

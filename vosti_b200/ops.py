@@ -239,6 +239,22 @@ def _workspace(device: torch.device, elems: int, purpose: str = "attention") -> 
     return buf
 
 
+_COUNTERS = {}
+
+
+def _counters(device: torch.device, count: int) -> torch.Tensor:
+    """Zeroed int32 counters that kernels leave zeroed (arrival counts of the decode
+    attention), one buffer per device, grown on demand."""
+    key = (device.type, device.index)
+    buf = _COUNTERS.get(key)
+    if buf is None or buf.numel() < count:
+        global WORKSPACE_GENERATION
+        WORKSPACE_GENERATION += 1
+        buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+        _COUNTERS[key] = buf
+    return buf
+
+
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 _SPLIT_GENERATION = 0   # counts split-K products: a PartialSum is valid until the next one runs
 
@@ -324,12 +340,14 @@ def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, 
     lib.vosti_attention_decode_scratch.restype = ctypes.c_int64
     elems = lib.vosti_attention_decode_scratch(count, nq, head_dim, max_kv_len)
     scratch = _workspace(q.device, elems)
+    arrivals = _counters(q.device, count * nkv)
     num_pages = k_cache.numel() // (page_size * nkv * head_dim)
     _check(lib.vosti_attention_decode(
-        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), ctypes.c_int64(scratch.numel()), _p(token_list),
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), ctypes.c_int64(scratch.numel()), _p(arrivals),
+        _p(token_list),
         count, tokens_total, _p(positions), _p(request_of), _p(block_table), block_table.shape[1], page_size,
         num_pages, nq, nkv, head_dim, max_kv_len, ctypes.c_float(scale), window, _p(status), _stream()),
-        "attention_decode", kernels=2)
+        "attention_decode")
 
 
 def attention_prefill(q, k_cache, v_cache, out, *, row_list, count, cu_q, kv_len, block_table, page_size, nq, nkv,
