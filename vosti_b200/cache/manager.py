@@ -126,8 +126,10 @@ class CacheManager:
                 cache.group = by_window[spec.window]
                 layers_of[cache.group].append(layer)
                 if device is not None:
+                    # zeros, not empty: the decode kernel reads whole boxes of 16 keys and masks
+                    # afterwards, so slots nobody wrote yet must hold finite values
                     cache.tensors = tuple(
-                        torch.empty((num_pages, spec.heads, page_size, spec.width), dtype=dtype, device=device)
+                        torch.zeros((num_pages, spec.heads, page_size, spec.width), dtype=dtype, device=device)
                         for _ in range(spec.entries))
             self.layer_caches.append(cache)
         for layer, spec in enumerate(state_specs):

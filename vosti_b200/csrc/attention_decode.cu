@@ -1,32 +1,65 @@
 // Paged attention for single query tokens (decode rows and very short portions),
-// bfloat16, on the tensor cores with split keys ("flash decoding"):
+// bfloat16, on the tensor cores with split keys ("flash decoding"), as a persistent,
+// warp-specialised kernel:
 //
-//   grid = (segments, kv heads, tokens). One CTA takes one token, one kv head with the
-//   whole group of query heads that share it (they fill the MMA's 16 rows), and one
-//   segment of SEGMENT keys counted from key 0 of the request. Its four warps each take a
-//   quarter of the segment (four tiles of 16 keys through two buffers: two tiles are
-//   requested before any arithmetic, the others as buffers become free), run the online softmax (base 2, float32) with mma.sync m16n8k16 for
-//   Q.K^T and P.V, and are merged in warp order. The CTA writes
-//   an unnormalised partial (max, sum, accumulator) per query head; the CTA that finishes
-//   last for a (token, kv head) merges the segments in segment order and normalises.
+//   A work item is one token, one kv head with the whole group of query heads that share it
+//   (they fill the MMA's 16 rows), and one segment of `segment_keys` keys counted from key 0
+//   of the request. CTA c walks over the items c, c + grid, ... Warp 0 is the producer: it
+//   resolves the block table (page ids of the next item are fetched while the current one
+//   streams) and feeds each consumer warp's ring of tile buffers by TMA, one box per 16 keys
+//   and 64 columns straight from the page (128-byte swizzle), across item boundaries. Warps
+//   1..4 are the consumers: each takes a quarter of the segment, runs the online softmax
+//   (base 2, float32) with mma.sync m16n8k16 for Q.K^T and P.V, and they are merged in warp
+//   order into an unnormalised partial (max, sum, accumulator) per query head. The CTA that
+//   finishes last for a (token, kv head) merges the segments in segment order and normalises;
+//   a CTA counts itself in one item late, so that the wait for its own stores overlaps the
+//   next item.
 //
-// The segmentation depends on the key index only, so a row's arithmetic does not depend
-// on its batch companions. Formulas as in kernels/triton_kernels/fattn_paged.py:176-252:
-// kv head = query head * nkv / nq, scale * log2(e), causal up to the token's own position,
-// optional window, P rounded to bfloat16 before P.V (:246), out = acc / l (0 if l = 0).
-// K and V rows are staged in shared memory by bulk copies (one per cache row, completing
-// on an mbarrier per tile) straight from the pages; masked keys are never read from the cache.
+// The segmentation depends on the key index and on the launch (its length is chosen from the
+// number of tokens and the longest context), never on the companions' contents. Formulas as
+// in kernels/triton_kernels/fattn_paged.py:176-252: kv head = query head * nkv / nq,
+// scale * log2(e), causal up to the token's own position, optional window, P rounded to
+// bfloat16 before P.V (:246), out = acc / l (0 if l = 0).
+//
+// A box of 16 keys is read whole when pages hold a multiple of 16 tokens: keys of the page
+// beyond the token's position (or before its window) are read and masked, so the cache must
+// hold finite values in every slot of a held page. Other page sizes read row by row, masked
+// keys not at all.
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 #include "mma_util.cuh"
+#include "tensor_map.cuh"
 
 namespace {
 
-constexpr int WARPS = 4;
-constexpr int TILE = 16;              // keys per MMA step
-constexpr int SEGMENT = 256;          // keys per CTA
-constexpr int WARP_KEYS = SEGMENT / WARPS;
-constexpr int BUFFERS = 2;                     // of which this many are in shared memory at once
+constexpr int CONSUMERS = 4;                          // consumer warps; one producer warp beside them
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int TILE = 16;                              // keys per MMA step and per TMA box
+constexpr int RING = 2;                               // K/V tile buffers per consumer warp
+constexpr int Q_BUFFERS = 2;
+constexpr int SEGMENT_STEP = CONSUMERS * TILE;        // 64: segment lengths are multiples of this
+constexpr int MIN_SEGMENT = SEGMENT_STEP * RING;      // 128: both buffers of every warp in use
+constexpr int MAX_SEGMENT = 4096;
+constexpr int MAX_SEGMENT_PAGES = MAX_SEGMENT / TILE; // page ids the producer stages per item
+constexpr int BOX_COLS = 64;                          // 128 bytes: the swizzle width
+constexpr int BLOCK_BYTES = TILE * 128;               // one column block of a tile
 constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void mb_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// A wait that ran out marks the CTA as abandoned: later waits return at once, so that a fault
+// costs one timeout and not one per tile, while every warp still walks through the same
+// barriers (the results are garbage then and the status word says so).
+__device__ __forceinline__ void wait_or_abandon(uint32_t bar, uint32_t parity, unsigned* status, volatile int* abandoned) {
+  if (*abandoned) return;
+  if (!mb_wait(bar, parity, status)) *abandoned = 1;
+}
+// A barrier among the consumer warps only (the producer never joins it).
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
 
 // Partial record of one (token, query head, segment): [0] max (base-2 scores), [1] sum,
 // [2 .. 2+d) accumulator.
@@ -92,276 +125,548 @@ __device__ __forceinline__ void merge_segments(const float* __restrict__ base, b
   }
 }
 
-// DMAX bounds the head size; with EXACT the head size is DMAX itself, which turns the index
-// arithmetic of the staging loops into shifts.
+struct ItemMeta {
+  int t, pos, item, g, seg, kstart, request, pad;    // t < 0: no more items
+};
+
+// DMAX bounds the head size; with EXACT the head size is DMAX itself.
 template <int DMAX, bool EXACT>
-__global__ void __launch_bounds__(WARPS * 32)
-attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                        float* __restrict__ partial, bf16* __restrict__ out, int* __restrict__ arrivals,
-                        const int* __restrict__ token_list,
+__global__ void __launch_bounds__(THREADS)
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const bf16* __restrict__ q, float* __restrict__ partial, bf16* __restrict__ out,
+                        int* __restrict__ arrivals, const int* __restrict__ token_list,
                         const int* __restrict__ positions, const int* __restrict__ request_of,
                         const int* __restrict__ block_table, int max_pages, int page_size, int page_shift,
-                        int num_pages, int nq, int nkv, int d_runtime, int max_segments, float scale_log2, int window, unsigned* status) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ __align__(8) uint64_t tile_bar[WARPS][BUFFERS];
-  if ((threadIdx.x & 31) == 0) {
-    for (int i = 0; i < BUFFERS; ++i) mb_init(smem_addr(&tile_bar[threadIdx.x >> 5][i]), 1);
-    mb_fence_init();
-  }
-  __syncwarp();
-  pdl_wait();
-  pdl_launch_dependents();
+                        int num_pages, int whole_pages, int whole_rows, int count, int nq, int nkv, int d_runtime,
+                        int segment_keys, int max_segments, float scale_log2, int window, unsigned* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[CONSUMERS][RING];
+  __shared__ __align__(8) uint64_t q_full[Q_BUFFERS], q_empty[Q_BUFFERS];
+  __shared__ ItemMeta item_meta[Q_BUFFERS];
+  __shared__ ItemMeta consumer_meta;       // the consumers' common copy: they all take the same decisions
+  __shared__ int tile_rows[Q_BUFFERS][MAX_SEGMENT_PAGES];   // cache row of each tile's first key (whole pages)
+  __shared__ int segment_pages[MAX_SEGMENT_PAGES];
+  __shared__ int last_to_arrive;
+  __shared__ volatile int abandoned;
   const int d = EXACT ? DMAX : d_runtime;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = token_list ? token_list[blockIdx.z] : blockIdx.z;
-  const int g = blockIdx.y, seg = blockIdx.x;
   const int group = nq / nkv;                       // query heads per kv head, <= 16
-  const int pos = positions[t];
-  const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int seg_begin = seg * SEGMENT, seg_end = min(seg_begin + SEGMENT, pos + 1);
-  if (seg_begin > pos || seg_end <= kstart) return;            // nothing visible in this segment
-  const int* table = block_table + (int64_t)request_of[t] * max_pages;
+  const int nb = (d + BOX_COLS - 1) / BOX_COLS;     // column blocks per K or V tile
+  const int slot_bytes = 2 * nb * BLOCK_BYTES;      // one ring slot: K blocks, then V blocks
+  const int q_pitch = d * 2 + 16;                   // bytes per staged Q row: conflict-free ldmatrix
+  const int rec = d + 2;
+  uint8_t* ring_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_base = ring_base + CONSUMERS * RING * slot_bytes;                         // [Q_BUFFERS][16][q_pitch]
+  float* merge = reinterpret_cast<float*>(q_base + Q_BUFFERS * 16 * q_pitch);         // [CONSUMERS][group][rec]
 
-  const int pitch = d * 2 + 16;                     // bytes per staged row: conflict-free ldmatrix
-  uint8_t* q_s = smem;                              // [16][pitch]
-  uint8_t* stage_base = smem + 16 * pitch + warp * (2 * BUFFERS * TILE * pitch);   // per warp: buffers x (K, V)
-  const int chunks = d / 8;                         // 16-byte chunks per row
-
-  const int my_begin = seg_begin + warp * WARP_KEYS;
-  const int my_end = min(my_begin + WARP_KEYS, seg_end);
-  const int first_tile = max(my_begin, (kstart / TILE) * TILE);       // tiles stay aligned to the key index
-  const int tiles = my_end > first_tile ? (my_end - first_tile + TILE - 1) / TILE : 0;
-
-  // A tile's 16 key rows and 16 value rows are fetched by one bulk copy each (lane r: key
-  // row r, lane 16 + r: value row r) that signals the tile's mbarrier; rows that are not
-  // visible are zero-filled and never read from the cache.
-  auto issue = [&](int tile) {
-    const int key0 = first_tile + tile * TILE;
-    uint8_t* kdst = stage_base + (tile % BUFFERS) * (2 * TILE * pitch);
-    uint8_t* vdst = kdst + TILE * pitch;
-    const int row = lane & 15;
-    const int key = key0 + row;
-    int64_t slot = -1;
-    if (key >= kstart && key <= pos) {
-      const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
-      const int page = index < max_pages ? table[index] : -1;
-      if (page < 0 || page >= num_pages) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
-      else slot = ((int64_t)page * nkv + g) * page_size + (key - index * page_size);   // row of (page, head, offset)
+  if (threadIdx.x == 0) {
+    abandoned = 0;
+    for (int w = 0; w < CONSUMERS; ++w)
+      for (int r = 0; r < RING; ++r) mb_init(smem_addr(&full_bar[w][r]), 1);
+    for (int b = 0; b < Q_BUFFERS; ++b) {
+      mb_init(smem_addr(&q_full[b]), 1);
+      mb_init(smem_addr(&q_empty[b]), CONSUMERS);
     }
-    const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
-    const uint32_t bar = smem_addr(&tile_bar[warp][tile % BUFFERS]);
-    if (lane == 0) mb_expect_tx(bar, (uint32_t)__popc(live) * (uint32_t)(d * 2));
-    __syncwarp();
-    uint8_t* dst = (lane < 16 ? kdst : vdst) + row * pitch;
-    if (slot >= 0) {
-      const bf16* src = (lane < 16 ? k_cache : v_cache) + slot * d;
-      bulk_copy_g2s(smem_addr(dst), src, (uint32_t)(d * 2), bar);
+    mb_fence_init();
+  }
+  // rows of the MMA tile beyond the group stay zero for the whole kernel
+  for (int i = threadIdx.x; i < Q_BUFFERS * 16 * q_pitch / 16; i += THREADS)
+    reinterpret_cast<uint4*>(q_base)[i] = make_uint4(0, 0, 0, 0);
+  if (!whole_pages)       // rows of masked keys are not loaded: what they held before must be finite
+    for (int i = threadIdx.x; i < CONSUMERS * RING * slot_bytes / 16; i += THREADS)
+      reinterpret_cast<uint4*>(ring_base)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  pdl_wait();
+  pdl_launch_dependents();
+
+  // items in segment-major order: the short last segments of the requests come last, which
+  // evens out what the CTAs get
+  const int64_t pairs = (int64_t)count * nkv;
+  const int64_t total_items = pairs * max_segments;
+  const int quarter = segment_keys / CONSUMERS;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    // It describes the items to the consumers one item ahead: token, position, the cache row
+    // of every tile (block table resolved) and the query rows. The consumers fetch K and V.
+    uint32_t q_issued = 0;
+    const int my_items = blockIdx.x < total_items ? (int)((total_items - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+    for (int base = 0; base < my_items; base += 32) {
+      // token, position and request of 32 items at once: lane l holds item base + l
+      int t_l = 0, pos_l = -1, req_l = 0;
+      if (base + lane < my_items) {
+        const int64_t idx = blockIdx.x + (int64_t)(base + lane) * gridDim.x;
+        const int item = (int)((idx % pairs) / nkv);
+        t_l = token_list ? token_list[item] : item;
+        pos_l = positions[t_l];
+        req_l = request_of[t_l];
+      }
+      const int n = min(32, my_items - base);
+      // page ids of an item's segment, MAX_SEGMENT_PAGES / 32 per lane; -1 where none is needed
+      int next_pages[MAX_SEGMENT_PAGES / 32];
+      auto fetch_pages = [&](int j) {
+        const int pos = __shfl_sync(0xffffffffu, pos_l, j), req = __shfl_sync(0xffffffffu, req_l, j);
+        const int64_t idx = blockIdx.x + (int64_t)(base + j) * gridDim.x;
+        const int seg = (int)(idx / pairs);
+        const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int seg_begin = seg * segment_keys;
+        const int first_index = seg_begin / page_size;
+        const int lo = kstart / page_size, hi = min(pos, seg_begin + segment_keys - 1) / page_size;
+        const int* table = block_table + (int64_t)req * max_pages;
+#pragma unroll
+        for (int k = 0; k < MAX_SEGMENT_PAGES / 32; ++k) {
+          const int index = first_index + lane + 32 * k;
+          next_pages[k] = (index >= lo && index <= hi && index < max_pages) ? table[index] : -1;
+        }
+      };
+      if (whole_pages) fetch_pages(0);
+      for (int j = 0; j < n; ++j) {
+        const int t = __shfl_sync(0xffffffffu, t_l, j), pos = __shfl_sync(0xffffffffu, pos_l, j);
+        const int req = __shfl_sync(0xffffffffu, req_l, j);
+        const int64_t idx = blockIdx.x + (int64_t)(base + j) * gridDim.x;
+        const int seg = (int)(idx / pairs);
+        const int g = (int)((idx % pairs) % nkv);
+        const int item = (int)((idx % pairs) / nkv);
+        const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int seg_begin = seg * segment_keys, seg_end = min(seg_begin + segment_keys, pos + 1);
+        if (whole_pages) {
+          __syncwarp();
+#pragma unroll
+          for (int k = 0; k < MAX_SEGMENT_PAGES / 32; ++k) segment_pages[lane + 32 * k] = next_pages[k];
+          __syncwarp();
+          if (j + 1 < n) fetch_pages(j + 1);         // in flight while this item is described
+        }
+        if (seg_begin > pos || seg_end <= kstart) continue;          // nothing visible in this segment
+        const uint32_t qb = q_issued % Q_BUFFERS;
+        if (q_issued >= Q_BUFFERS)
+          wait_or_abandon(smem_addr(&q_empty[qb]), ((q_issued / Q_BUFFERS) - 1) & 1, status, &abandoned);
+        if (whole_pages) {
+          const int first_index = seg_begin / page_size;
+          for (int i = lane; i < segment_keys / TILE; i += 32) {
+            const int key0 = seg_begin + i * TILE;
+            const int index = page_shift >= 0 ? key0 >> page_shift : key0 / page_size;
+            const int page = segment_pages[min(index - first_index, MAX_SEGMENT_PAGES - 1)];
+            tile_rows[qb][i] = (page < 0 || page >= num_pages) ? -1 : (page * nkv + g) * page_size + (key0 - index * page_size);
+          }
+          __syncwarp();
+        }
+        if (lane == 0) {
+          item_meta[qb] = ItemMeta{t, pos, item, g, seg, kstart, req, 0};
+          mb_expect_tx(smem_addr(&q_full[qb]), (uint32_t)(group * d * 2));
+          // the item's query rows are contiguous in q: the heads of one group
+          for (int row = 0; row < group; ++row)
+            bulk_copy_g2s(smem_addr(q_base + (qb * 16 + row) * q_pitch), q + ((int64_t)t * nq + g * group + row) * d,
+                          (uint32_t)(d * 2), smem_addr(&q_full[qb]));
+        }
+        ++q_issued;
+      }
+    }
+    // ---- no more items
+    const uint32_t qb = q_issued % Q_BUFFERS;
+    if (q_issued >= Q_BUFFERS)
+      wait_or_abandon(smem_addr(&q_empty[qb]), ((q_issued / Q_BUFFERS) - 1) & 1, status, &abandoned);
+    if (lane == 0) {
+      item_meta[qb] = ItemMeta{-1, 0, 0, 0, 0, 0, 0, 0};
+      mb_arrive(smem_addr(&q_full[qb]));
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int cw = warp - 1;
+  const int ctid = threadIdx.x - 32;                 // 0..127 among the consumers
+  const bool upper_rows_live = group > 8;
+  // swizzled addresses of this lane's ldmatrix rows: byte (row, chunk) of a column block sits at
+  // row * 128 + ((chunk ^ (row & 7)) << 4)
+  const int k_row = (lane & 7) + (lane >> 4) * 8, k_half = (lane >> 3) & 1;
+  const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_half = lane >> 4;
+  const uint32_t k_lane = k_row * 128, k_xor = (uint32_t)((k_half ^ (k_row & 7)) << 4);
+  const uint32_t v_lane = v_row * 128, v_xor = (uint32_t)((v_half ^ (v_row & 7)) << 4);
+  uint32_t seen = 0, n_issued = 0, q_seen = 0;       // tiles consumed and requested by this warp, items seen
+  int ahead = 0;                                     // tiles of the next item already requested
+  bool pending = false;                              // an item whose partials are written but not counted in
+  int p_item = 0, p_g = 0, p_t = 0, p_first = 0, p_last = 0;
+
+  // This warp's tiles of an item: first key of its first tile, and their number.
+  auto my_tiles = [&](const ItemMeta& m, int& first_tile, int& tiles) {
+    const int seg_begin = m.seg * segment_keys, seg_end = min(seg_begin + segment_keys, m.pos + 1);
+    const int my_begin = seg_begin + cw * quarter;
+    const int my_end = min(my_begin + quarter, seg_end);
+    first_tile = max(my_begin, (m.kstart / TILE) * TILE);             // tiles stay aligned to the key index
+    tiles = my_end > first_tile ? (my_end - first_tile + TILE - 1) / TILE : 0;
+  };
+  // Request the 16 keys from key0 of the item described in buffer `qslot` into the next ring slot.
+  auto request_tile = [&](const ItemMeta& m, int qslot, int key0) {
+    const uint32_t slot = n_issued % RING;
+    const uint32_t dst = smem_addr(ring_base + (cw * RING + slot) * slot_bytes);
+    const uint32_t bar = smem_addr(&full_bar[cw][slot]);
+    if (whole_pages) {
+      // the 16 keys lie in one page: one box for K and one for V (one per 64 columns if the
+      // head size is no multiple of 64)
+      int row = tile_rows[qslot][(key0 - m.seg * segment_keys) / TILE];
+      if (row < 0) {
+        raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
+        row = 0;
+      }
+      if (lane == 0) {
+        mb_expect_tx(bar, (uint32_t)slot_bytes);
+        if (whole_rows) {
+          tma_load_3d(dst, &map_k, 0, row, 0, bar);
+          tma_load_3d(dst + nb * BLOCK_BYTES, &map_v, 0, row, 0, bar);
+        } else {
+          for (int cb = 0; cb < nb; ++cb) {
+            tma_load_2d(dst + cb * BLOCK_BYTES, &map_k, cb * BOX_COLS, row, bar);
+            tma_load_2d(dst + (nb + cb) * BLOCK_BYTES, &map_v, cb * BOX_COLS, row, bar);
+          }
+        }
+      }
     } else {
-      for (int c = 0; c < chunks; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0, 0, 0, 0);
+      // any page size: one box of one row per key; lanes 0-15 fetch K rows, 16-31 V rows
+      const int key = key0 + (lane & 15);
+      int row = -1;
+      if (key >= m.kstart && key <= m.pos) {
+        const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
+        const int page = index < max_pages ? block_table[(int64_t)m.request * max_pages + index] : -1;
+        if (page < 0 || page >= num_pages) raise_fault(status, VOSTI_FAULT_PAGE_RANGE);
+        else row = (page * nkv + m.g) * page_size + (key - index * page_size);
+      }
+      const unsigned live = __ballot_sync(0xffffffffu, row >= 0);
+      if (lane == 0) mb_expect_tx(bar, (uint32_t)__popc(live) * (uint32_t)(nb * 128));
+      __syncwarp();
+      if (row >= 0)
+        for (int cb = 0; cb < nb; ++cb)
+          tma_load_2d(dst + (lane < 16 ? 0 : nb * BLOCK_BYTES) + cb * BLOCK_BYTES + (lane & 15) * 128,
+                      lane < 16 ? &map_k : &map_v, cb * BOX_COLS, row, bar);
+    }
+    __syncwarp();
+    ++n_issued;
+  };
+  // Count the CTA in for the pending item (thread 0; the others learn of it after the next
+  // barrier); the last one to arrive merges its segments. No CTA waits for another: each
+  // counts itself in after its records are visible device-wide.
+  auto count_in = [&]() {
+    if (ctid == 0) {
+      __threadfence();
+      int* counter = arrivals + (int64_t)p_item * nkv + p_g;
+      const int before = atomicAdd(counter, 1);
+      last_to_arrive = before == p_last - p_first;
+      if (last_to_arrive) *counter = 0;               // ready for the next launch
+    }
+  };
+  auto merge_if_last = [&]() {
+    if (last_to_arrive) {
+      __threadfence();
+      for (int row = cw; row < group; row += CONSUMERS) {
+        const int h = p_g * group + row;
+        merge_segments(partial + ((int64_t)p_item * nq + h) * max_segments * rec, out + ((int64_t)p_t * nq + h) * d,
+                       p_first, p_last, d);
+      }
     }
   };
 
-  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
-  float o[DMAX / 8][4];
-#pragma unroll
-  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  while (true) {
+    const uint32_t qb = q_seen % Q_BUFFERS;
+    if (ctid == 0) {
+      wait_or_abandon(smem_addr(&q_full[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
+      consumer_meta = item_meta[qb];
+    }
+    consumer_sync();                                 // also: everyone is done with the previous item's merge area
+    const ItemMeta meta = consumer_meta;
+    if (meta.t < 0) break;
+    wait_or_abandon(smem_addr(&q_full[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
+    const int pos = meta.pos, kstart = meta.kstart, seg = meta.seg, g = meta.g;
+    int first_tile, tiles;
+    my_tiles(meta, first_tile, tiles);
+    // tiles of this item requested so far: those the previous item's tail asked for, then up to a full ring
+    int requested = ahead;
+    while (requested < min(tiles, RING)) request_tile(meta, qb, first_tile + (requested++) * TILE);
+    ahead = 0;
+    // what is known of the item after this one (its description may arrive while this one runs)
+    const uint32_t nqb = (q_seen + 1) % Q_BUFFERS;
+    bool next_known = false;
+    ItemMeta next_meta = ItemMeta{-1, 0, 0, 0, 0, 0, 0, 0};
+    int next_first = 0, next_tiles = 0;
 
-  for (int tile = 0; tile < tiles && tile < BUFFERS; ++tile) issue(tile);   // the first tiles are requested at once
-  // ---- Q rows of the group (rows >= group are zero)
-  for (int i = threadIdx.x; i < 16 * chunks; i += WARPS * 32) {
-    const int row = i / chunks, c = i % chunks;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < group) v = *reinterpret_cast<const uint4*>(q + ((int64_t)t * nq + g * group + row) * d + c * 8);
-    *reinterpret_cast<uint4*>(q_s + row * pitch + c * 16) = v;
-  }
-  __syncthreads();                                                  // (the K/V requests above are in flight meanwhile)
-  // up to head size 128 the Q fragments stay in registers for both tiles
-  constexpr bool Q_IN_REGISTERS = DMAX <= 128;
-  uint32_t qa[Q_IN_REGISTERS ? DMAX / 16 : 1][4];
-  if (Q_IN_REGISTERS) {
+    // ---- Q fragments of this item into registers (up to head size 128)
+    const uint8_t* q_s = q_base + qb * 16 * q_pitch;
+    constexpr bool Q_IN_REGISTERS = DMAX <= 128;
+    uint32_t qa[Q_IN_REGISTERS ? DMAX / 16 : 1][4];
+    if (Q_IN_REGISTERS) {
 #pragma unroll
-    for (int kk = 0; kk < DMAX / 16; ++kk)
-      if (kk * 16 < d) ldmatrix_x4(qa[Q_IN_REGISTERS ? kk : 0], smem_addr(q_s + (lane & 15) * pitch + (kk * 16 + (lane >> 4) * 8) * 2));
-  }
-  // rows 8..15 of the MMA tile hold query heads only if the group has more than 8
-  const bool upper_rows_live = group > 8;
+      for (int kk = 0; kk < DMAX / 16; ++kk)
+        if (kk * 16 < d)
+          ldmatrix_x4(qa[Q_IN_REGISTERS ? kk : 0], smem_addr(q_s + (lane & 15) * q_pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+    }
 
-  for (int tile = 0; tile < tiles; ++tile) {
-    mb_wait(smem_addr(&tile_bar[warp][tile % BUFFERS]), (tile / BUFFERS) & 1, status);
-    __syncwarp();
-    const uint8_t* ks = stage_base + (tile % BUFFERS) * (2 * TILE * pitch);
-    const uint8_t* vs = ks + TILE * pitch;
-    const int key0 = first_tile + tile * TILE;
-
-    // ---- S = Q K^T for 16 keys: two 8-key column tiles
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+    float o[DMAX / 8][4];
 #pragma unroll
-    for (int kk = 0; kk < DMAX / 16; ++kk) {
-      if (kk * 16 < d) {
-        uint32_t a[4], b[4];
-        // A: rows lane%16 of Q, columns kk*16 + (lane/16)*8
-        if (Q_IN_REGISTERS) {
-          a[0] = qa[Q_IN_REGISTERS ? kk : 0][0]; a[1] = qa[Q_IN_REGISTERS ? kk : 0][1];
-          a[2] = qa[Q_IN_REGISTERS ? kk : 0][2]; a[3] = qa[Q_IN_REGISTERS ? kk : 0][3];
-        } else {
-          ldmatrix_x4(a, smem_addr(q_s + (lane & 15) * pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    for (int tile = 0; tile < tiles; ++tile, ++seen) {
+      const uint32_t slot = seen % RING;
+      wait_or_abandon(smem_addr(&full_bar[cw][slot]), (seen / RING) & 1, status, &abandoned);
+      const uint32_t ks = smem_addr(ring_base + (cw * RING + slot) * slot_bytes);
+      const uint32_t vs = ks + nb * BLOCK_BYTES;
+      const int key0 = first_tile + tile * TILE;
+      bool edge = false;
+      if (whole_pages && (key0 < kstart || key0 + TILE - 1 > pos)) {
+        // a box brought keys that are masked: their V rows must not reach the MMA (0 * NaN)
+        edge = true;
+        uint8_t* vrows = ring_base + (cw * RING + slot) * slot_bytes + nb * BLOCK_BYTES;
+        for (int i = lane; i < nb * TILE * 8; i += 32) {
+          const int r = (i >> 3) % TILE;
+          if (key0 + r < kstart || key0 + r > pos) reinterpret_cast<uint4*>(vrows)[i] = make_uint4(0, 0, 0, 0);
         }
-        // B: matrices (keys 0-7, k lo), (keys 0-7, k hi), (keys 8-15, k lo), (keys 8-15, k hi)
-        ldmatrix_x4(b, smem_addr(ks + ((lane & 7) + (lane >> 4) * 8) * pitch + (kk * 16 + ((lane >> 3) & 1) * 8) * 2));
-        mma_bf16(s[0], a, b[0], b[1]);
-        mma_bf16(s[1], a, b[2], b[3]);
+        __syncwarp();
+      }
+
+      // ---- S = Q K^T for 16 keys: two 8-key column tiles
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < DMAX / 16; ++kk) {
+        if (kk * 16 < d) {
+          uint32_t a[4], b[4];
+          if (Q_IN_REGISTERS) {
+            a[0] = qa[Q_IN_REGISTERS ? kk : 0][0]; a[1] = qa[Q_IN_REGISTERS ? kk : 0][1];
+            a[2] = qa[Q_IN_REGISTERS ? kk : 0][2]; a[3] = qa[Q_IN_REGISTERS ? kk : 0][3];
+          } else {
+            ldmatrix_x4(a, smem_addr(q_s + (lane & 15) * q_pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+          }
+          // B: matrices (keys 0-7, k lo), (keys 0-7, k hi), (keys 8-15, k lo), (keys 8-15, k hi)
+          ldmatrix_x4(b, ks + (kk >> 2) * BLOCK_BYTES + k_lane + ((uint32_t)((kk & 3) << 5) ^ k_xor));
+          mma_bf16(s[0], a, b[0], b[1]);
+          mma_bf16(s[1], a, b[2], b[3]);
+        }
+      }
+      // ---- online softmax (rows lane/4 and lane/4 + 8)
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const bool visible = key >= kstart && key <= pos;
+          s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
+        }
+      float alpha[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        if (r == 1 && !upper_rows_live) {              // padding rows: no exponentials (warp-uniform)
+          alpha[r] = 1.f;
+          s[0][2] = s[0][3] = s[1][2] = s[1][3] = 0.f;
+          continue;
+        }
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float m_new = fmaxf(m_row[r], tile_max[r]);
+        const float safe = m_new == -INFINITY ? 0.f : m_new;
+        alpha[r] = fast_exp2(m_row[r] - safe);
+        m_row[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          s[nt][2 * r] = fast_exp2(s[nt][2 * r] - safe);
+          s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - safe);
+          sum += s[nt][2 * r] + s[nt][2 * r + 1];
+        }
+        l_row[r] = l_row[r] * alpha[r] + sum;          // per-thread share; reduced over the quad at the end
+      }
+      uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                       pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+      // ---- O = O * alpha + P V
+#pragma unroll
+      for (int nt = 0; nt < DMAX / 16; ++nt) {
+        if (nt * 16 < d) {
+          o[2 * nt][0] *= alpha[0]; o[2 * nt][1] *= alpha[0]; o[2 * nt][2] *= alpha[1]; o[2 * nt][3] *= alpha[1];
+          o[2 * nt + 1][0] *= alpha[0]; o[2 * nt + 1][1] *= alpha[0]; o[2 * nt + 1][2] *= alpha[1]; o[2 * nt + 1][3] *= alpha[1];
+          uint32_t b[4];
+          // transposed: matrices (keys 0-7, cols lo), (keys 8-15, cols lo), (keys 0-7, cols hi), (keys 8-15, cols hi)
+          ldmatrix_x4_trans(b, vs + (nt >> 2) * BLOCK_BYTES + v_lane + ((uint32_t)((nt & 3) << 5) ^ v_xor));
+          mma_bf16(o[2 * nt], p, b[0], b[1]);
+          mma_bf16(o[2 * nt + 1], p, b[2], b[3]);
+        }
+      }
+      __syncwarp();                                  // every lane is done with this slot: refill it
+      if (edge) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (requested < tiles) {
+        request_tile(meta, qb, first_tile + (requested++) * TILE);
+      } else {
+        // this item's tiles are all on their way: start on the next item's if it has been described
+        if (!next_known && !abandoned && mb_try_wait(smem_addr(&q_full[nqb]), ((q_seen + 1) / Q_BUFFERS) & 1)) {
+          next_known = true;
+          next_meta = item_meta[nqb];
+          if (next_meta.t >= 0) my_tiles(next_meta, next_first, next_tiles);
+        }
+        if (next_known && ahead < next_tiles) request_tile(next_meta, nqb, next_first + (ahead++) * TILE);
       }
     }
-    // ---- online softmax (rows lane/4 and lane/4 + 8)
-    float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-        const bool visible = key >= kstart && key <= pos;
-        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
-        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
-      }
-    float alpha[2];
+    // the description (and with head sizes above 128 the Q rows) of this item is not needed any more
+    __syncwarp();
+    if (lane == 0) mb_arrive(smem_addr(&q_empty[qb]));
+    ++q_seen;
+
+    // ---- merge the four consumers in warp order
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      if (r == 1 && !upper_rows_live) {              // padding rows: no exponentials (warp-uniform)
-        alpha[r] = 1.f;
-        s[0][2] = s[0][3] = s[1][2] = s[1][3] = 0.f;
-        continue;
-      }
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-      const float m_new = fmaxf(m_row[r], tile_max[r]);
-      const float safe = m_new == -INFINITY ? 0.f : m_new;
-      alpha[r] = fast_exp2(m_row[r] - safe);
-      m_row[r] = m_new;
-      float sum = 0.f;
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        s[nt][2 * r] = fast_exp2(s[nt][2 * r] - safe);
-        s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - safe);
-        sum += s[nt][2 * r] + s[nt][2 * r + 1];
-      }
-      l_row[r] = l_row[r] * alpha[r] + sum;          // per-thread share; reduced over the quad at the end
+      l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
+      l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
     }
-    uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
-                     pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
-    // ---- O = O * alpha + P V
+    // the item before this one is counted in now: its stores have had an item's time to land
+    if (pending) count_in();
 #pragma unroll
-    for (int nt = 0; nt < DMAX / 16; ++nt) {
-      if (nt * 16 < d) {
-        o[2 * nt][0] *= alpha[0]; o[2 * nt][1] *= alpha[0]; o[2 * nt][2] *= alpha[1]; o[2 * nt][3] *= alpha[1];
-        o[2 * nt + 1][0] *= alpha[0]; o[2 * nt + 1][1] *= alpha[0]; o[2 * nt + 1][2] *= alpha[1]; o[2 * nt + 1][3] *= alpha[1];
-        uint32_t b[4];
-        // transposed: matrices (keys 0-7, cols lo), (keys 8-15, cols lo), (keys 0-7, cols hi), (keys 8-15, cols hi)
-        ldmatrix_x4_trans(b, smem_addr(vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (nt * 16 + (lane >> 4) * 8) * 2));
-        mma_bf16(o[2 * nt], p, b[0], b[1]);
-        mma_bf16(o[2 * nt + 1], p, b[2], b[3]);
-      }
-    }
-    if (tile + BUFFERS < tiles) {                  // this buffer is free again: fetch the tile after next
-      __syncwarp();
-      issue(tile + BUFFERS);
-    }
-  }
-  // ---- merge the four warps in warp order (through the staging memory)
+    for (int r = 0; r < 2; ++r) {
+      const int row = (lane >> 2) + 8 * r;
+      if (row < group) {
+        float* dst = merge + ((int64_t)cw * group + row) * rec;
+        if ((lane & 3) == 0) {
+          dst[0] = m_row[r];
+          dst[1] = l_row[r];
+        }
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
-    l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
-  }
-  __syncthreads();
-  float* merge = reinterpret_cast<float*>(smem + 16 * pitch);     // [WARPS][16][d + 2]
-  const int rec = d + 2;
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = (lane >> 2) + 8 * r;
-    if (row < group) {
-      float* dst = merge + ((int64_t)warp * 16 + row) * rec;
-      if ((lane & 3) == 0) {
-        dst[0] = m_row[r];
-        dst[1] = l_row[r];
-      }
-#pragma unroll
-      for (int nt = 0; nt < DMAX / 8; ++nt) {
-        if (nt * 8 < d) {
-          dst[2 + nt * 8 + (lane & 3) * 2] = o[nt][2 * r];
-          dst[2 + nt * 8 + (lane & 3) * 2 + 1] = o[nt][2 * r + 1];
+        for (int nt = 0; nt < DMAX / 8; ++nt) {
+          if (nt * 8 < d) {
+            dst[2 + nt * 8 + (lane & 3) * 2] = o[nt][2 * r];
+            dst[2 + nt * 8 + (lane & 3) * 2 + 1] = o[nt][2 * r + 1];
+          }
         }
       }
     }
-  }
-  __syncthreads();
-  // per (row, warp): the row's maximum over the warps and this warp's weight 2^(m_w - m)
-  __shared__ float row_max[16], row_weight[WARPS][16];
-  if (threadIdx.x < 16 * WARPS) {
-    const int row = threadIdx.x & 15, w = threadIdx.x >> 4;
-    if (row < group) {
+    consumer_sync();
+    for (int row = 0; row < group; ++row) {
+      // the row's maximum over the warps and each warp's weight 2^(m_w - m)
+      float weight[CONSUMERS];
       float m = -INFINITY;
-      for (int v = 0; v < WARPS; ++v) m = fmaxf(m, merge[((int64_t)v * 16 + row) * rec]);
-      const float mw = merge[((int64_t)w * 16 + row) * rec];
-      row_weight[w][row] = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
-      if (w == 0) row_max[row] = m;
-    }
-  }
-  __syncthreads();
-  for (int row = 0; row < group; ++row) {
-    float* dst = partial + (((int64_t)blockIdx.z * nq + g * group + row) * max_segments + seg) * rec;
-    for (int c = threadIdx.x; c < rec; c += WARPS * 32) {
-      float value;
-      if (c == 0) {
-        value = row_max[row];
-      } else {
-        value = 0.f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) value += merge[((int64_t)w * 16 + row) * rec + c] * row_weight[w][row];
+      for (int w = 0; w < CONSUMERS; ++w) m = fmaxf(m, merge[((int64_t)w * group + row) * rec]);
+#pragma unroll
+      for (int w = 0; w < CONSUMERS; ++w) {
+        const float mw = merge[((int64_t)w * group + row) * rec];
+        weight[w] = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
       }
-      dst[c] = value;
+      float* dst = partial + (((int64_t)meta.item * nq + g * group + row) * max_segments + seg) * rec;
+      for (int c = ctid; c < rec; c += CONSUMERS * 32) {
+        float value;
+        if (c == 0) {
+          value = m;
+        } else {
+          value = 0.f;
+#pragma unroll
+          for (int w = 0; w < CONSUMERS; ++w) value += merge[((int64_t)w * group + row) * rec + c] * weight[w];
+        }
+        dst[c] = value;
+      }
     }
+    if (pending) merge_if_last();
+    pending = true;
+    p_item = meta.item; p_g = g; p_t = meta.t;
+    p_first = kstart / segment_keys; p_last = pos / segment_keys;
   }
-  // ---- the CTA that finishes last for this (token, kv head) merges the segments. No CTA
-  // waits for another: each counts itself in after its records are visible device-wide.
-  __shared__ int last_to_arrive;
-  __threadfence();
-  __syncthreads();
-  const int first_segment = kstart / SEGMENT, last_segment = pos / SEGMENT;
-  if (threadIdx.x == 0) {
-    int* counter = arrivals + (int64_t)blockIdx.z * nkv + g;
-    const int before = atomicAdd(counter, 1);
-    last_to_arrive = before == last_segment - first_segment;
-    if (last_to_arrive) *counter = 0;               // ready for the next launch
-  }
-  __syncthreads();
-  if (!last_to_arrive) return;
-  __threadfence();
-  for (int row = warp; row < group; row += WARPS) {
-    const int h = g * group + row;
-    merge_segments(partial + ((int64_t)blockIdx.z * nq + h) * max_segments * rec, out + ((int64_t)t * nq + h) * d,
-                   first_segment, last_segment, d);
+  if (pending) {
+    consumer_sync();                                 // every consumer has written its share of the last item
+    count_in();
+    consumer_sync();
+    merge_if_last();
   }
 }
 
-size_t decode_smem_bytes(int d) {
-  const size_t pitch = (size_t)d * 2 + 16;
-  const size_t stage = 16 * pitch + (size_t)WARPS * 2 * BUFFERS * TILE * pitch;
-  const size_t merge = 16 * pitch + (size_t)WARPS * 16 * (d + 2) * sizeof(float);
-  return stage > merge ? stage : merge;
+// Bytes of dynamic shared memory: ring, Q buffers, merge area, and room to align the ring.
+size_t decode_smem_bytes(int d, int group) {
+  const size_t nb = (d + BOX_COLS - 1) / BOX_COLS;
+  return 1024 + (size_t)CONSUMERS * RING * 2 * nb * BLOCK_BYTES + (size_t)Q_BUFFERS * 16 * ((size_t)d * 2 + 16) +
+         (size_t)CONSUMERS * group * (d + 2) * sizeof(float);
+}
+
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  return sms;
+}
+
+int ctas_per_sm(int d, int group) {
+  const size_t per_sm = 228 * 1024;
+  const size_t per_cta = decode_smem_bytes(d, group) + 2048;        // static arrays and the reserved kilobyte
+  const int by_smem = (int)(per_sm / per_cta);
+  return by_smem >= 2 ? 2 : 1;                                       // registers allow two
+}
+
+// Keys per segment for a launch: items are spread over the persistent CTAs in rounds; a round
+// costs the segment's length plus a fixed share for starting and finishing an item.
+int choose_segment_keys(int count, int nkv, int d, int group, int max_kv_len) {
+  if (const char* forced = getenv("VOSTI_DECODE_SEGMENT")) {
+    const int keys = atoi(forced);
+    if (keys >= SEGMENT_STEP && keys <= MAX_SEGMENT && keys % SEGMENT_STEP == 0) return keys;
+  }
+  const int64_t ctas = (int64_t)sm_count() * ctas_per_sm(d, group);
+  const int64_t pairs = (int64_t)count * nkv;
+  const int item_overhead = 64;
+  int best = MIN_SEGMENT;
+  int64_t best_cost = -1;
+  for (int keys = MIN_SEGMENT; keys <= MAX_SEGMENT; keys += SEGMENT_STEP) {
+    const int64_t segments = (max_kv_len + keys - 1) / keys;
+    const int64_t rounds = (pairs * segments + ctas - 1) / ctas;
+    const int64_t cost = rounds * (keys + item_overhead);
+    if (best_cost < 0 || cost <= best_cost) {          // ties: the longer segment, fewer records
+      best_cost = cost;
+      best = keys;
+    }
+    if (segments == 1) break;
+  }
+  return best;
+}
+
+struct CacheMapKey {
+  const void* p;
+  int64_t rows;
+  int d, box_rows;                                   // box_rows < 0: the whole-row (3-D) map of -box_rows rows
+  bool operator==(const CacheMapKey& o) const { return p == o.p && rows == o.rows && d == o.d && box_rows == o.box_rows; }
+};
+struct CacheMapKeyHash {
+  size_t operator()(const CacheMapKey& key) const {
+    return std::hash<const void*>()(key.p) ^ ((size_t)key.rows * 1000003u) ^ ((size_t)key.d << 20) ^ (size_t)key.box_rows;
+  }
+};
+
+// Tensor map of a cache seen as [pages * kv heads * page_size, d]; cached by address and shape.
+bool cache_map(const void* cache, int64_t rows, int d, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<CacheMapKey, CUtensorMap, CacheMapKeyHash> maps;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  CacheMapKey key{cache, rows, d, box_rows};
+  auto it = maps.find(key);
+  if (it != maps.end()) {
+    *out = it->second;
+    return true;
+  }
+  if (maps.size() > 4096) maps.clear();
+  if (box_rows < 0 ? !encode_tensor_map_rows(out, cache, rows, d, -box_rows)
+                   : !encode_tensor_map_2d(out, cache, rows, d, box_rows, BOX_COLS))
+    return false;
+  maps.emplace(key, *out);
+  return true;
 }
 
 }  // namespace
 
-// Number of key segments (and so partial records per token and head) a launch with keys
-// up to `max_kv_len` uses.
-VOSTI_API int vosti_attention_decode_segments(int max_kv_len) { return (max_kv_len + SEGMENT - 1) / SEGMENT; }
-
-// float32 scratch elements needed: count * nq * segments * (d + 2).
-VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int d, int max_kv_len) {
-  return (int64_t)count * nq * vosti_attention_decode_segments(max_kv_len) * record_floats(d);
+// Keys per segment, and so (max_kv_len + keys - 1) / keys partial records per token and
+// head, of a launch with `count` tokens and keys up to `max_kv_len`.
+VOSTI_API int vosti_attention_decode_segment_keys(int count, int nq, int nkv, int d, int max_kv_len) {
+  return choose_segment_keys(count, nkv, d, nq / nkv, max_kv_len);
 }
 
-// caches: bf16 [pages, kv heads, page_size, d] (a head's tokens of a page are contiguous).
+// float32 scratch elements needed: count * nq * segments * (d + 2).
+VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int nkv, int d, int max_kv_len) {
+  const int keys = vosti_attention_decode_segment_keys(count, nq, nkv, d, max_kv_len);
+  return (int64_t)count * nq * ((max_kv_len + keys - 1) / keys) * record_floats(d);
+}
+
+// caches: bf16 [pages, kv heads, page_size, d] (a head's tokens of a page are contiguous),
+// 16-byte aligned, finite in every slot of a page a live request holds.
 // arrivals: int32[count * nkv], all zero before the first launch; every launch leaves it zero.
 // q, out: bf16 [tokens_total, nq, d]; the kernel serves `count` tokens: those listed in
 // token_list (int32[count]) or tokens 0..count-1. scratch holds the partial records of the
@@ -375,15 +680,28 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   VOSTI_REQUIRE(nq / nkv <= 16, "attention_decode: at most 16 query heads per kv head, got %d", nq / nkv);
   VOSTI_REQUIRE(d > 0 && d % 16 == 0 && d <= 256, "attention_decode: head_dim %d must be a multiple of 16 and <= 256", d);
   VOSTI_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0 && window >= 0, "attention_decode: bad cache geometry");
+  VOSTI_REQUIRE(max_kv_len > 0, "attention_decode: max_kv_len %d must be positive", max_kv_len);
   if (count == 0) return VOSTI_OK;
-  const int segments = vosti_attention_decode_segments(max_kv_len);
-  VOSTI_REQUIRE(segments >= 1 && segments <= 65535, "attention_decode: context %d too long", max_kv_len);
+  const int group = nq / nkv;
+  const int segment_keys = choose_segment_keys(count, nkv, d, group, max_kv_len);
+  const int segments = (max_kv_len + segment_keys - 1) / segment_keys;
   VOSTI_REQUIRE(arrivals != nullptr, "attention_decode: the arrival counters are missing");
-  VOSTI_REQUIRE(scratch != nullptr && scratch_elems >= vosti_attention_decode_scratch(count, nq, d, max_kv_len),
+  VOSTI_REQUIRE(scratch != nullptr && scratch_elems >= (int64_t)count * nq * segments * record_floats(d),
                 "attention_decode: scratch too small");
-  const size_t smem = decode_smem_bytes(d);
-  dim3 grid(segments, nkv, count);
-  VOSTI_REQUIRE(count <= 65535, "attention_decode: too many tokens (%d) for one launch", count);
+  const int64_t cache_rows = (int64_t)num_pages * nkv * page_size;
+  VOSTI_REQUIRE(cache_rows < (int64_t)1 << 31, "attention_decode: cache of %lld rows is too large", (long long)cache_rows);
+  VOSTI_REQUIRE((reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0,
+                "attention_decode: the caches must be 16-byte aligned");
+  const int whole_pages = page_size % TILE == 0 ? 1 : 0;
+  const int whole_rows = whole_pages && d % BOX_COLS == 0 ? 1 : 0;
+  const int box_rows = whole_rows ? -TILE : whole_pages ? TILE : 1;
+  CUtensorMap map_k, map_v;
+  VOSTI_REQUIRE(cache_map(k_cache, cache_rows, d, box_rows, &map_k) && cache_map(v_cache, cache_rows, d, box_rows, &map_v),
+                "attention_decode: cuTensorMapEncodeTiled failed");
+  const size_t smem = decode_smem_bytes(d, group);
+  const int64_t items = (int64_t)count * nkv * segments;
+  const int64_t ctas = (int64_t)sm_count() * ctas_per_sm(d, group);
+  dim3 grid((unsigned)(items < ctas ? items : ctas));
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
@@ -392,14 +710,13 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
     static bool configured = false;                                                                                 \
     if (!configured) {                                                                                              \
       cudaFuncSetAttribute(attention_decode_kernel<DMAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
-                           (int)decode_smem_bytes(DMAX));                                                           \
+                           (int)decode_smem_bytes(DMAX, 16));                                                       \
       configured = true;                                                                                            \
     }                                                                                                               \
-    vosti_launch(attention_decode_kernel<DMAX, EXACT>, grid, dim3(WARPS * 32), smem, stream,                        \
-        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, scratch, (bf16*)out, arrivals, token_list,      \
-        positions, request_of,                                                                                      \
-        block_table, max_pages, page_size, page_shift, num_pages, nq, nkv, d, segments, scale * LOG2E, window,      \
-        status);                                                                                                    \
+    vosti_launch(attention_decode_kernel<DMAX, EXACT>, grid, dim3(THREADS), smem, stream, map_k, map_v,             \
+        (const bf16*)q, scratch, (bf16*)out, arrivals, token_list, positions, request_of,                          \
+        block_table, max_pages, page_size, page_shift, num_pages, whole_pages, whole_rows, count, nq, nkv, d, segment_keys,     \
+        segments, scale * LOG2E, window, status);                                                                   \
   } while (0)
   if (d == 64) LAUNCH_DECODE(64, true);
   else if (d == 128) LAUNCH_DECODE(128, true);

@@ -25,7 +25,7 @@ from ..sampling import sample_rows
 from .batch import StepEntry
 
 PAGES_BUCKET = 32      # block-table width is rounded up to this many pages
-KV_BUCKET = 1024       # the key length kernels size their grids for is rounded up to this
+KV_BUCKET = 512        # the key length kernels size their grids for is rounded up to this
 
 
 def _round_up(value: int, multiple: int) -> int:

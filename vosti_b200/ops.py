@@ -338,7 +338,7 @@ def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, 
     lib = library()
     tokens_total = q.shape[0]
     lib.vosti_attention_decode_scratch.restype = ctypes.c_int64
-    elems = lib.vosti_attention_decode_scratch(count, nq, head_dim, max_kv_len)
+    elems = lib.vosti_attention_decode_scratch(count, nq, nkv, head_dim, max_kv_len)
     scratch = _workspace(q.device, elems)
     arrivals = _counters(q.device, count * nkv)
     num_pages = k_cache.numel() // (page_size * nkv * head_dim)
