@@ -351,10 +351,15 @@ def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, 
 
 
 def attention_prefill(q, k_cache, v_cache, out, *, row_list, count, cu_q, kv_len, block_table, page_size, nq, nkv,
-                      head_dim, max_q_len, scale, window, status) -> None:
-    """Attention of whole portions for `count` requests (bfloat16)."""
+                      head_dim, max_q_len, scale, window, status, kernel: Optional[str] = None) -> None:
+    """Attention of whole portions for `count` requests (bfloat16): the mma.sync kernel ("mma"),
+    or for head sizes 64 and 128 the tcgen05 kernel ("tc") when `kernel` asks for it."""
+    lib = library()
     num_pages = k_cache.numel() // (page_size * nkv * head_dim)
-    _check(library().vosti_attention_prefill(
+    if kernel is None:
+        kernel = "mma"
+    entry = lib.vosti_attention_prefill_tc if kernel == "tc" else lib.vosti_attention_prefill
+    _check(entry(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(row_list), count, _p(cu_q), _p(kv_len), _p(block_table),
         block_table.shape[1], page_size, num_pages, nq, nkv, head_dim, max_q_len, ctypes.c_float(scale), window,
         _p(status), _stream()), "attention_prefill")
