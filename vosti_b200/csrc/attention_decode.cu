@@ -26,8 +26,6 @@
 // hold finite values in every slot of a held page. Other page sizes read row by row, masked
 // keys not at all.
 #include <cstdlib>
-#include <mutex>
-#include <unordered_map>
 
 #include "common.cuh"
 #include "mma_util.cuh"
@@ -620,37 +618,6 @@ int choose_segment_keys(int count, int nkv, int d, int group, int max_kv_len) {
   return best;
 }
 
-struct CacheMapKey {
-  const void* p;
-  int64_t rows;
-  int d, box_rows;                                   // box_rows < 0: the whole-row (3-D) map of -box_rows rows
-  bool operator==(const CacheMapKey& o) const { return p == o.p && rows == o.rows && d == o.d && box_rows == o.box_rows; }
-};
-struct CacheMapKeyHash {
-  size_t operator()(const CacheMapKey& key) const {
-    return std::hash<const void*>()(key.p) ^ ((size_t)key.rows * 1000003u) ^ ((size_t)key.d << 20) ^ (size_t)key.box_rows;
-  }
-};
-
-// Tensor map of a cache seen as [pages * kv heads * page_size, d]; cached by address and shape.
-bool cache_map(const void* cache, int64_t rows, int d, int box_rows, CUtensorMap* out) {
-  static std::unordered_map<CacheMapKey, CUtensorMap, CacheMapKeyHash> maps;
-  static std::mutex mutex;
-  std::lock_guard<std::mutex> lock(mutex);
-  CacheMapKey key{cache, rows, d, box_rows};
-  auto it = maps.find(key);
-  if (it != maps.end()) {
-    *out = it->second;
-    return true;
-  }
-  if (maps.size() > 4096) maps.clear();
-  if (box_rows < 0 ? !encode_tensor_map_rows(out, cache, rows, d, -box_rows)
-                   : !encode_tensor_map_2d(out, cache, rows, d, box_rows, BOX_COLS))
-    return false;
-  maps.emplace(key, *out);
-  return true;
-}
-
 }  // namespace
 
 // Keys per segment, and so (max_kv_len + keys - 1) / keys partial records per token and
@@ -696,7 +663,8 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   const int whole_rows = whole_pages && d % BOX_COLS == 0 ? 1 : 0;
   const int box_rows = whole_rows ? -TILE : whole_pages ? TILE : 1;
   CUtensorMap map_k, map_v;
-  VOSTI_REQUIRE(cache_map(k_cache, cache_rows, d, box_rows, &map_k) && cache_map(v_cache, cache_rows, d, box_rows, &map_v),
+  VOSTI_REQUIRE(cached_tensor_map(k_cache, cache_rows, d, box_rows, &map_k) &&
+                    cached_tensor_map(v_cache, cache_rows, d, box_rows, &map_v),
                 "attention_decode: cuTensorMapEncodeTiled failed");
   const size_t smem = decode_smem_bytes(d, group);
   const int64_t items = (int64_t)count * nkv * segments;

@@ -4,6 +4,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -55,6 +56,49 @@ inline bool encode_tensor_map_rows(CUtensorMap* map, const void* base, int64_t r
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// General form: `rank` dimensions (innermost first), byte strides of dimensions 1.. (multiples
+// of 16), box extents; bfloat16, 128-byte swizzle (the innermost box extent at most 64).
+inline bool encode_tensor_map_nd(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
+                                 const cuuint64_t* strides, const cuuint32_t* box) {
+  VostiEncodeTiledFn fn = tensor_map_encoder();
+  if (!fn) return false;
+  const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tensor maps of long-lived matrices (weights, caches) are kept by address and shape.
+// box_rows < 0 asks for the whole-row map of -box_rows rows.
+struct TensorMapKey {
+  const void* p;
+  int64_t rows;
+  int cols, box_rows;
+  bool operator==(const TensorMapKey& o) const { return p == o.p && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct TensorMapKeyHash {
+  size_t operator()(const TensorMapKey& key) const {
+    return std::hash<const void*>()(key.p) ^ ((size_t)key.rows * 1000003u) ^ ((size_t)key.cols << 20) ^ (size_t)key.box_rows;
+  }
+};
+inline bool cached_tensor_map(const void* base, int64_t rows, int cols, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<TensorMapKey, CUtensorMap, TensorMapKeyHash> maps;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  TensorMapKey key{base, rows, cols, box_rows};
+  auto it = maps.find(key);
+  if (it != maps.end()) {
+    *out = it->second;
+    return true;
+  }
+  if (maps.size() > 8192) maps.clear();
+  if (box_rows < 0 ? !encode_tensor_map_rows(out, base, rows, cols, -box_rows)
+                   : !encode_tensor_map_2d(out, base, rows, cols, box_rows, 64))
+    return false;
+  maps.emplace(key, *out);
+  return true;
+}
+
 // Tiled load of one box at (c0 = column, c1 = row); c0 * 2 must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
@@ -66,5 +110,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
 }

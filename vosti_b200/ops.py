@@ -352,14 +352,20 @@ def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, 
 
 def attention_prefill(q, k_cache, v_cache, out, *, row_list, count, cu_q, kv_len, block_table, page_size, nq, nkv,
                       head_dim, max_q_len, scale, window, status, kernel: Optional[str] = None) -> None:
-    """Attention of whole portions for `count` requests (bfloat16): the mma.sync kernel ("mma"),
-    or for head sizes 64 and 128 the tcgen05 kernel ("tc") when `kernel` asks for it."""
+    """Attention of whole portions for `count` requests (bfloat16). Head sizes 64 and 128 with
+    pages of a multiple of 16 tokens run on the tcgen05 kernel ("tc"), everything else on the
+    mma.sync kernel ("mma"); `kernel` forces one."""
     lib = library()
     num_pages = k_cache.numel() // (page_size * nkv * head_dim)
     if kernel is None:
-        kernel = "mma"
-    entry = lib.vosti_attention_prefill_tc if kernel == "tc" else lib.vosti_attention_prefill
-    _check(entry(
+        kernel = "tc" if lib.vosti_attention_prefill_tc_supported(head_dim, page_size) and nq // nkv <= 16 else "mma"
+    if kernel == "tc":
+        _check(lib.vosti_attention_prefill_tc(
+            _p(q), _p(k_cache), _p(v_cache), _p(out), _p(row_list), count, _p(cu_q), _p(kv_len), _p(block_table),
+            block_table.shape[1], page_size, num_pages, nq, nkv, head_dim, max_q_len, q.shape[0],
+            ctypes.c_float(scale), window, _p(status), _stream()), "attention_prefill_tc")
+        return
+    _check(lib.vosti_attention_prefill(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(row_list), count, _p(cu_q), _p(kv_len), _p(block_table),
         block_table.shape[1], page_size, num_pages, nq, nkv, head_dim, max_q_len, ctypes.c_float(scale), window,
         _p(status), _stream()), "attention_prefill")
