@@ -14,10 +14,11 @@
 //     * four loader warps: each brings 16 keys of a tile, one TMA box per 64 features of K
 //       and of V straight from the page, into the tensor cores' 128-byte-swizzled layout
 //       (four stages). The query rows come as one 4-D box per 64 features.
-//     * one thread issues the MMAs: S = Q K^T (M 128, N 64) into the score buffer of the
-//       tile's group in tensor memory, and P V (M 128, N = head size, V read as an MN-major
-//       operand straight from its [key][feature] rows) into the group's product buffer. The
-//       scores of tile j+2 are issued as soon as tile j's have been read, before P of tile j.
+//     * four threads (one per warp) issue the MMAs: S = Q K^T (M 128, N 64) into the score
+//       buffer of the tile's group in tensor memory, and P V (M 128, N = head size, V read as
+//       an MN-major operand straight from its [key][feature] rows) into the group's product
+//       buffer; scores and products, even and odd tiles have a thread each. The scores of a
+//       group's next tile are issued as soon as it has read the last ones.
 //   Registers move from the loader and MMA warpgroups to the softmax ones (setmaxnreg).
 //
 // Semantics as in attention_prefill.cu (bottom-right causal alignment, optional window,
@@ -115,7 +116,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (warp < 8) {
     // ------------------------------------------------------------ softmax and accumulation
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int wg = warp >> 2;                                    // takes tiles wg, wg + 2, ...
     const int r = threadIdx.x & 127;                             // row of the tile and lane of tensor memory
     const int token = token0 + r / group;
@@ -231,7 +232,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
   } else if (warp < MMA_WARP) {
     // ------------------------------------------------------------ loaders
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     const int w = warp - 8;                              // keys 16 w .. 16 w + 15 of every tile
     if (w == 0 && lane == 0) {
       // Q rows: row r is token r / group, head r % group: a box [tokens][heads of the group][64]
@@ -286,49 +287,57 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
   } else {
     // ------------------------------------------------------------ MMA issue
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == MMA_WARP && lane == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (lane == 0) {
+      // Four issuing threads, one per warp: scores of the even tiles, scores of the odd tiles,
+      // products of the even tiles, products of the odd tiles. One thread alone cannot issue
+      // a tile's twelve MMAs and wait on its barriers as fast as the tensor core retires them.
+      const int role = warp - MMA_WARP, wg = role & 1;
       constexpr uint32_t idesc_s = umma_instr_desc(ROWS, KT, false);
       constexpr uint32_t idesc_pv = umma_instr_desc(ROWS, D, true);
-      bool ok = mbar_wait(smem_u32(&q_full), 0, &abort_flag, status);
-      const uint32_t q_addr = smem_u32(q_s), kv_addr = smem_u32(kv_s), p_addr = smem_u32(p_s);
-      // S_t = Q K_t^T into the score buffer of the tile's group
-      auto issue_scores = [&](int t) {
-        const int stage = t % STAGES, wg = t & 1, k = t >> 1;
-        ok = ok && mbar_wait(smem_u32(&kv_full[stage]), (t / STAGES) & 1, &abort_flag, status);
-        if (ok && k >= 1) ok = mbar_wait(smem_u32(&s_empty[wg]), (k - 1) & 1, &abort_flag, status);
-        if (!ok) return;
-        tc_fence_after();
-        const uint32_t k_addr = kv_addr + stage * STAGE_BYTES;
+      // descriptors differ in their start address only: bits [0,14) in units of 16 bytes
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s)), k_desc = smem_desc_sw128(smem_u32(kv_s));
+      const uint64_t p_desc = smem_desc_sw128(smem_u32(p_s) + wg * P_BYTES);
+      const uint64_t v_desc = smem_desc_sw128_mn(smem_u32(kv_s) + K_BYTES, KT * 128);
+      bool ok = true;
+      if (role < 2) {
+        // S_t = Q K_t^T into the score buffer of the tile's group
+        ok = mbar_wait(smem_u32(&q_full), 0, &abort_flag, status);
+        int k = 0;
+        for (int t = wg; t < tiles && ok; t += 2, ++k) {
+          const int stage = t % STAGES;
+          ok = mbar_wait(smem_u32(&kv_full[stage]), (t / STAGES) & 1, &abort_flag, status);
+          if (ok && k >= 1) ok = mbar_wait(smem_u32(&s_empty[wg]), (k - 1) & 1, &abort_flag, status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t kd = k_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int kb = 0; kb < NB; ++kb)
+          for (int kb = 0; kb < NB; ++kb)
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_bf16(tmem_base + S_COL + wg * KT, smem_desc_sw128(q_addr + kb * (ROWS * 128) + ks * 32),
-                      smem_desc_sw128(k_addr + kb * (KT * 128) + ks * 32), idesc_s, (kb | ks) ? 1u : 0u);
-        umma_commit(smem_u32(&s_full[wg]));
-      };
-      // (P V) of tile i, 16 keys per MMA; V rows are [key][64 features] blocks: MN-major
-      auto issue_product = [&](int i) {
-        const int stage = i % STAGES, wg = i & 1, k = i >> 1;
-        ok = ok && mbar_wait(smem_u32(&p_full[wg]), k & 1, &abort_flag, status);
-        if (ok && k >= 1) ok = mbar_wait(smem_u32(&pv_empty[wg]), (k - 1) & 1, &abort_flag, status);
-        if (!ok) return;
-        tc_fence_after();
-        const uint32_t v_addr = kv_addr + stage * STAGE_BYTES + K_BYTES;
+            for (int ks = 0; ks < 4; ++ks)
+              umma_bf16(tmem_base + S_COL + wg * KT, q_desc + (uint64_t)((kb * (ROWS * 128) + ks * 32) >> 4),
+                        kd + (uint64_t)((kb * (KT * 128) + ks * 32) >> 4), idesc_s, (kb | ks) ? 1u : 0u);
+          umma_commit(smem_u32(&s_full[wg]));
+        }
+      } else {
+        // (P V) of tile t, 16 keys per MMA; V rows are [key][64 features] blocks: MN-major
+        int k = 0;
+        for (int t = wg; t < tiles && ok; t += 2, ++k) {
+          const int stage = t % STAGES;
+          ok = mbar_wait(smem_u32(&kv_full[stage]), (t / STAGES) & 1, &abort_flag, status);
+          if (ok) ok = mbar_wait(smem_u32(&p_full[wg]), k & 1, &abort_flag, status);
+          if (ok && k >= 1) ok = mbar_wait(smem_u32(&pv_empty[wg]), (k - 1) & 1, &abort_flag, status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t vd = v_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int ks = 0; ks < KT / 16; ++ks)
-          umma_bf16(tmem_base + PV_COL + wg * D, smem_desc_sw128(p_addr + wg * P_BYTES + ks * 32),
-                    smem_desc_sw128_mn(v_addr + ks * (16 * 128), KT * 128), idesc_pv, ks ? 1u : 0u);
-        umma_commit(smem_u32(&pv_full[wg]));
-        umma_commit(smem_u32(&p_empty[wg]));
-        umma_commit(smem_u32(&kv_empty[stage]));
-      };
-      issue_scores(0);
-      if (tiles > 1) issue_scores(1);
-      for (int i = 0; i < tiles && ok; ++i) {
-        if (i + 2 < tiles) issue_scores(i + 2);
-        issue_product(i);
+          for (int ks = 0; ks < KT / 16; ++ks)
+            umma_bf16(tmem_base + PV_COL + wg * D, p_desc + (uint64_t)((ks * 32) >> 4),
+                      vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, ks ? 1u : 0u);
+          umma_commit(smem_u32(&pv_full[wg]));
+          umma_commit(smem_u32(&p_empty[wg]));
+          umma_commit(smem_u32(&kv_empty[stage]));
+        }
       }
     }
   }
