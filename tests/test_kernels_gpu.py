@@ -336,7 +336,7 @@ def test_gemm_tc_rows_do_not_depend_on_their_companions(dev, status):
 
 
 # ---------------------------------------------------------------- tensor-core attention
-def _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, which):
+def _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, which, kernel=None):
     """Drive the decode (one query at a time) or the portion kernel directly."""
     from vosti_b200 import ops
     q = case["q"].to(dev, torch.bfloat16)
@@ -350,7 +350,8 @@ def _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale
     else:
         cu = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device=dev)
         ops.attention_prefill(q, kc, vc, out, row_list=None, count=len(lens_q), cu_q=cu,
-                              kv_len=torch.tensor(lens_k, dtype=torch.int32, device=dev), max_q_len=max(lens_q), **common)
+                              kv_len=torch.tensor(lens_k, dtype=torch.int32, device=dev), max_q_len=max(lens_q),
+                              kernel=kernel, **common)
     return out
 
 
@@ -368,6 +369,46 @@ def test_attention_tensor_cores(dev, status, which, nq, nkv, d, page, window):
     assert torch.isfinite(out).all(), "a row was not written or an unused (NaN) cache entry was read"
     assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), (out.float().cpu() - want).abs().max()
     assert status.item() == 0
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 4, 128, 16, 0), (8, 4, 64, 32, 0), (16, 2, 128, 64, 0),
+                                                   (16, 1, 64, 16, 45), (5, 1, 128, 16, 0), (14, 2, 64, 48, 129),
+                                                   (32, 8, 128, 16, 1000)])
+def test_prefill_attention_on_tcgen05(dev, status, nq, nkv, d, page, window):
+    """The tensor-memory kernel against the plain formula and against the mma.sync kernel: every
+    group size (also ones that do not divide 128 rows), pages of 16, 32, 48 and 64 tokens,
+    windows, whole prompts and portions that continue a cached prefix."""
+    from vosti_b200 import ops
+    assert ops.library().vosti_attention_prefill_tc_supported(d, page)
+    lens_k = [1, 33, 64, 130, 17, 95, 700, 257, 256, 1500]
+    lens_q = [1, 33, 5, 7, 17, 40, 300, 129, 2, 1000]
+    case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page)
+    scale = 0.41 * d ** -0.5
+    out = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, "prefill", kernel="tc")
+    other = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, "prefill", kernel="mma")
+    want = reference_attention(case, scale, window)
+    assert torch.isfinite(out).all(), "a row was not written or an unused (NaN) cache entry was read"
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), (out.float().cpu() - want).abs().max()
+    assert torch.allclose(out.float(), other.float(), atol=2e-2, rtol=2e-2)
+    assert status.item() == 0
+
+
+def test_prefill_attention_on_tcgen05_rows_do_not_depend_on_companions(dev, status):
+    """A request's rows are the same bits whether it runs alone or beside others."""
+    nq, nkv, d, page = 8, 2, 128, 16
+    lens_k, lens_q = [300, 1000, 513], [300, 200, 13]
+    case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page)
+    full = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, d ** -0.5, 0, "prefill", kernel="tc")
+    from vosti_b200 import ops
+    q = case["q"].to(dev, torch.bfloat16)
+    kc, vc = dev_cache(case, "k_cache", dev, torch.bfloat16), dev_cache(case, "v_cache", dev, torch.bfloat16)
+    out = torch.zeros_like(q)
+    cu = torch.tensor([0, 300, 500, 513], dtype=torch.int32, device=dev)
+    ops.attention_prefill(q, kc, vc, out, row_list=torch.tensor([1], dtype=torch.int32, device=dev), count=1, cu_q=cu,
+                          kv_len=torch.tensor(lens_k, dtype=torch.int32, device=dev), block_table=case["table"].to(dev),
+                          page_size=page, nq=nq, nkv=nkv, head_dim=d, max_q_len=200, scale=d ** -0.5, window=0,
+                          status=status, kernel="tc")
+    assert torch.equal(out[300:500], full[300:500]) and out[:300].abs().max() == 0 and out[500:].abs().max() == 0
 
 
 @pytest.mark.parametrize("which", ["decode", "prefill"])
@@ -389,6 +430,26 @@ def test_attention_tensor_cores_find_one_far_key(dev, status, which):
             assert torch.allclose(last, torch.full_like(last, 3.0), atol=3e-2), (L, far, window)
         else:
             assert (last - 3.0).abs().mean() > 0.5, (L, far, window)
+
+
+@pytest.mark.parametrize("segment", [None, 64, 192, 1024, 4096])
+def test_attention_decode_many_tokens_and_every_segment_length(dev, status, segment, monkeypatch):
+    """More work items than resident CTAs (each CTA walks over several and prefetches across
+    them), requests of very different lengths, and segment lengths from one tile per warp to
+    one segment per request."""
+    if segment is not None:
+        monkeypatch.setenv("VOSTI_DECODE_SEGMENT", str(segment))
+    nq, nkv, d, page = 8, 2, 128, 16
+    generator = torch.Generator().manual_seed(7)
+    lens_k = [int(x) for x in torch.randint(1, 3000, (90,), generator=generator)] + [1, 16, 17, 64, 65, 4095, 4096, 4097]
+    lens_q = [1] * len(lens_k)
+    case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page)
+    scale = d ** -0.5
+    out = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, 0, "decode")
+    want = reference_attention(case, scale, 0)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), (out.float().cpu() - want).abs().max()
+    assert status.item() == 0
 
 
 def test_attention_decode_is_independent_of_the_batch(dev, status):
