@@ -45,7 +45,7 @@ def test_embedding(dev, status, dtype, hidden, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [80, 96, 1000, 4096 + 24])
+@pytest.mark.parametrize("width", [80, 100, 1000, 4096 + 24, 8192 + 40])   # vector and scalar paths
 @pytest.mark.parametrize("weight_f32", [False, True])
 def test_rmsnorm(dev, dtype, width, weight_f32):
     from vosti_b200 import ops
@@ -109,11 +109,13 @@ def test_gemm_simt_is_true_float32_and_row_independent(dev, status):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [19, 150])          # few tokens: a warp per head; many: a block per token
 @pytest.mark.parametrize("nq,nkv,d,use_norm,use_rope", [(6, 3, 48, True, True), (4, 4, 16, False, True),
-                                                         (5, 1, 128, True, False), (8, 2, 256, True, True)])
-def test_qkv_post(dev, status, dtype, nq, nkv, d, use_norm, use_rope):
+                                                         (5, 1, 128, True, False), (8, 2, 256, True, True),
+                                                         (9, 3, 64, True, True), (32, 8, 128, True, True)])
+def test_qkv_post(dev, status, dtype, T, nq, nkv, d, use_norm, use_rope):
     from vosti_b200 import ops
-    T, slots_total, eps, theta = 19, 64, 2e-6, 50000.0
+    slots_total, eps, theta = 2 * T + 26, 2e-6, 50000.0
     qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev).to(dtype)
     qw = (1 + 0.1 * torch.randn(d, device=dev)).to(dtype) if use_norm else None
     kw = (1 + 0.1 * torch.randn(d, device=dev)).to(dtype) if use_norm else None

@@ -116,6 +116,107 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
     }
   }
 }
+
+// The same pass for many tokens (prompts), bfloat16, head sizes 64, 128 and 256: one block per
+// token, a warp takes every eighth head and two heads at a time, so that the loads of both are
+// in flight together; a lane holds VE consecutive elements of each half of the head and moves
+// them as one 2-, 4- or 8-byte word.
+template <int VE>
+__global__ void __launch_bounds__(256)
+qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
+                     bf16* __restrict__ v_cache, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
+                     int norm_w_is_f32, float eps, const float* __restrict__ cos_table,
+                     const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
+                     const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv,
+                     unsigned* status) {
+  constexpr int HALF = 32 * VE, D = 2 * HALF;
+  struct alignas(2 * VE) Word { bf16 v[VE]; };
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int heads = nq + 2 * nkv;
+  const bf16* row = qkv + (int64_t)t * heads * D;
+  int pos = positions ? positions[t] : 0;
+  if (cos_table && (pos < 0 || pos >= max_positions)) {
+    if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
+    pos = 0;
+  }
+  int64_t slot = -1;
+  if (nkv > 0 && slot_mapping) {
+    slot = slot_mapping[t];
+    if (slot >= num_slots || slot < -1) {
+      if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+      slot = -1;
+    }
+  }
+  // this lane's rotation factors and norm weights serve every head
+  float c[VE], sn[VE], wq1[VE], wq2[VE], wk1[VE], wk2[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    const int i = lane * VE + e;
+    c[e] = cos_table ? cos_table[(int64_t)pos * HALF + i] : 1.f;
+    sn[e] = sin_table ? sin_table[(int64_t)pos * HALF + i] : 0.f;
+    wq1[e] = q_norm_w ? load_flex(q_norm_w, norm_w_is_f32, i) : 1.f;
+    wq2[e] = q_norm_w ? load_flex(q_norm_w, norm_w_is_f32, i + HALF) : 1.f;
+    wk1[e] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i) : 1.f;
+    wk2[e] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i + HALF) : 1.f;
+  }
+  constexpr int UNROLL = 2;
+  for (int h0 = warp; h0 < heads; h0 += 8 * UNROLL) {
+    Word a[UNROLL], b[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int h = h0 + 8 * u;
+      if (h < heads) {
+        a[u] = *reinterpret_cast<const Word*>(row + (int64_t)h * D + lane * VE);
+        b[u] = *reinterpret_cast<const Word*>(row + (int64_t)h * D + HALF + lane * VE);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int h = h0 + 8 * u;
+      if (h >= heads) continue;
+      const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+      bf16* dst;
+      if (is_q) {
+        dst = q_out + ((int64_t)t * nq + h) * D;
+      } else {
+        if (slot < 0) continue;
+        const int g = is_k ? h - nq : h - nq - nkv;
+        dst = (is_k ? k_cache : v_cache) + (((slot / page_size) * nkv + g) * page_size + slot % page_size) * D;
+      }
+      if (is_q || is_k) {
+        float x1[VE], x2[VE], ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < VE; ++e) {
+          x1[e] = to_f32(a[u].v[e]);
+          x2[e] = to_f32(b[u].v[e]);
+          ss += x1[e] * x1[e] + x2[e] * x2[e];
+        }
+        const bool normed = is_q ? q_norm_w != nullptr : k_norm_w != nullptr;
+        const float rrms = normed ? rsqrtf(warp_sum(ss) / (float)D + eps) : 1.f;
+#pragma unroll
+        for (int e = 0; e < VE; ++e) {
+          float p = x1[e], r = x2[e];
+          if (normed) {
+            p = p * rrms * (is_q ? wq1[e] : wk1[e]);
+            r = r * rrms * (is_q ? wq2[e] : wk2[e]);
+          }
+          if (cos_table) {
+            const float ra = p * c[e] - r * sn[e], rb = r * c[e] + p * sn[e];
+            p = ra;
+            r = rb;
+          }
+          a[u].v[e] = from_f32<bf16>(p);
+          b[u].v[e] = from_f32<bf16>(r);
+        }
+      }
+      *reinterpret_cast<Word*>(dst + lane * VE) = a[u];
+      *reinterpret_cast<Word*>(dst + HALF + lane * VE) = b[u];
+    }
+  }
+}
 }  // namespace
 
 // qkv: [tokens, (nq + 2*nkv) * d], or null with `partial`: float32 [splits, tokens, (nq + 2*nkv) * d],
@@ -141,6 +242,18 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
   VOSTI_REQUIRE(cos_table == nullptr || positions != nullptr, "qkv_post: rotation needs positions");
   if (tokens == 0) return VOSTI_OK;
   const int heads = nq + 2 * nkv;
+  if (!is_f32 && partial == nullptr && tokens >= 64 && (d == 64 || d == 128 || d == 256)) {
+    // many tokens: a block per token, vector accesses
+#define LAUNCH_QKV_POST_WIDE(VE)                                                                                   \
+    vosti_launch(qkv_post_wide_kernel<VE>, dim3(tokens), dim3(256), 0, stream, (const bf16*)qkv, (bf16*)q_out,     \
+        (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table,              \
+        max_positions, positions, slot_mapping, num_slots, page_size, nq, nkv, status)
+    if (d == 64) LAUNCH_QKV_POST_WIDE(1);
+    else if (d == 128) LAUNCH_QKV_POST_WIDE(2);
+    else LAUNCH_QKV_POST_WIDE(4);
+#undef LAUNCH_QKV_POST_WIDE
+    VOSTI_LAUNCH_CHECK();
+  }
   const dim3 grid(tokens, (heads + 3) / 4);                          // a warp per (token, head)
   if (is_f32)
     vosti_launch(qkv_post_kernel<float>, grid, dim3(128), 0, stream, (const float*)qkv, partial, splits, plane, (float*)q_out, (float*)k_cache,
