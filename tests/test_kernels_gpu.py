@@ -455,7 +455,9 @@ def test_attention_decode_many_tokens_and_every_segment_length(dev, status, segm
 
 
 def test_attention_decode_is_independent_of_the_batch(dev, status):
-    """The same token alone and among others, and listed out of order, gives the same bits."""
+    """The same token alone and among others, and listed out of order, gives the same bits, as
+    long as both launches cut the keys into segments of the same length (the length is a
+    function of the number of tokens and the longest context of a launch, not of their contents)."""
     from vosti_b200 import ops
     nq, nkv, d, page = 8, 2, 128, 16
     lens_k = [300, 1000, 40, 513]
@@ -465,6 +467,8 @@ def test_attention_decode_is_independent_of_the_batch(dev, status):
     kc, vc = dev_cache(case, "k_cache", dev, torch.bfloat16), dev_cache(case, "v_cache", dev, torch.bfloat16)
     out = torch.zeros_like(q)
     listed = torch.tensor([3, 1], dtype=torch.int32, device=dev)
+    keys = ops.library().vosti_attention_decode_segment_keys
+    assert keys(4, nq, nkv, d, 1000) == keys(2, nq, nkv, d, 1000)
     ops.attention_decode(q, kc, vc, out, token_list=listed, count=2, positions=case["positions"].to(dev),
                          request_of=case["request_of"].to(dev), block_table=case["table"].to(dev), page_size=page,
                          nq=nq, nkv=nkv, head_dim=d, max_kv_len=1000, scale=d ** -0.5, window=0, status=status)
