@@ -471,9 +471,17 @@ VOSTI_API int vosti_gemm_tc_supported(int features, int k) { return features >= 
 VOSTI_API int vosti_gemm_tc_splits(int tokens, int features, int k) {
   const int k_blocks = (k + BK - 1) / BK;
   const int tiles = ((features + BM - 1) / BM) * ((tokens + token_tile(tokens) - 1) / token_tile(tokens));
-  if (tokens > 128 || tiles >= 96) return 1;
-  int splits = (148 + tiles - 1) / tiles;
-  if (splits > k_blocks / 8) splits = k_blocks / 8;   // at least 8 k-blocks (512 elements) per split
+  if (tokens > 128) return 1;
+  int splits;
+  if (token_tile(tokens) <= 64) {
+    // two CTAs of this tile size fit an SM: fill both slots of every SM, never a second round
+    splits = (2 * 148) / tiles;
+    if (splits > k_blocks / 4) splits = k_blocks / 4;   // at least 4 k-blocks (256 elements) per split
+  } else {
+    if (tiles >= 96) return 1;
+    splits = (148 + tiles - 1) / tiles;
+    if (splits > k_blocks / 8) splits = k_blocks / 8;
+  }
   if (splits > 16) splits = 16;
   return splits < 1 ? 1 : splits;
 }

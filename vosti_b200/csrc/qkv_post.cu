@@ -77,18 +77,30 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
         x2[j] = i < half ? to_f32(src[i + half]) : 0.f;
       }
     } else {
-      // splits outermost so that the loads of one split are independent of each other
+      // the loads of up to four splits are issued together; the sums still run in split order
 #pragma unroll
       for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) x1[j] = x2[j] = 0.f;
-      for (int s = 0; s < splits; ++s) {
+      constexpr int FLIGHT = 4;
+      for (int s0 = 0; s0 < splits; s0 += FLIGHT) {
+        float v1[FLIGHT][MAX_PAIRS_PER_LANE], v2[FLIGHT][MAX_PAIRS_PER_LANE];
 #pragma unroll
-        for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
-          const int i = lane + 32 * j;
-          if (i < half) {
-            x1[j] += psrc[s * plane + i];
-            x2[j] += psrc[s * plane + i + half];
+        for (int f = 0; f < FLIGHT; ++f)
+#pragma unroll
+          for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            const bool live = s0 + f < splits && i < half;
+            v1[f][j] = live ? psrc[(s0 + f) * plane + i] : 0.f;
+            v2[f][j] = live ? psrc[(s0 + f) * plane + i + half] : 0.f;
           }
-        }
+#pragma unroll
+        for (int f = 0; f < FLIGHT; ++f)
+          if (s0 + f < splits) {
+#pragma unroll
+            for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
+              x1[j] += v1[f][j];
+              x2[j] += v2[f][j];
+            }
+          }
       }
     }
 #pragma unroll
