@@ -36,12 +36,35 @@ sample_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, c
   // ---- maximum and its lowest index (needed by both modes)
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = tid; i < vocab; i += THREADS) {
-    const float v = row[i];
+  auto consider = [&](float v, int i) {
     if (v > best || (v == best && i < best_i)) {
       best = v;
       best_i = i;
     }
+  };
+  if ((row_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    // 16-byte loads, four of them in flight per thread
+    const int quads = vocab >> 2;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int q0 = tid; q0 < quads; q0 += 4 * THREADS) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (q0 + j * THREADS < quads) v[j] = row4[q0 + j * THREADS];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int q = q0 + j * THREADS;
+        if (q < quads) {
+          consider(v[j].x, 4 * q);
+          consider(v[j].y, 4 * q + 1);
+          consider(v[j].z, 4 * q + 2);
+          consider(v[j].w, 4 * q + 3);
+        }
+      }
+    }
+    for (int i = 4 * quads + tid; i < vocab; i += THREADS) consider(row[i], i);
+  } else {
+    for (int i = tid; i < vocab; i += THREADS) consider(row[i], i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
