@@ -136,11 +136,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       ok = ok && mbar_wait(smem_u32(&pv_full[wg]), k & 1, &abort_flag, status);
       tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        tmem_load32(lane_base + PV_COL + wg * D + c0, v);
+      for (int c0 = 0; c0 < D; c0 += 64) {
+        uint32_t v[2][32];                              // two loads in flight
+        tmem_load32_async(lane_base + PV_COL + wg * D + c0, v[0]);
+        tmem_load32_async(lane_base + PV_COL + wg * D + c0 + 32, v[1]);
+        tmem_wait_loads();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[c0 + j] = fmaf(o[c0 + j], alpha, __uint_as_float(v[j]));
+        for (int j = 0; j < 64; ++j) o[c0 + j] = fmaf(o[c0 + j], alpha, __uint_as_float(v[j >> 5][j & 31]));
       }
       tc_fence_before();
       __syncwarp();
@@ -161,37 +163,54 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_empty[wg]));       // the scores are in registers
       const bool masked = key0 + KT - 1 > pos || key0 < kstart;
-      float tile_max = -INFINITY;
+      // the maximum is exact in any order: four independent chains, scaled once at the end
+      // (scale_log2 > 0, so max(s * scale) = max(s) * scale bit for bit)
+      float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (masked) {
 #pragma unroll
         for (int i = 0; i < KT; ++i)
-          if (key0 + i <= pos && key0 + i >= kstart)
-            tile_max = fmaxf(tile_max, __uint_as_float(raw[i >> 5][i & 31]) * scale_log2);
+          if (key0 + i <= pos && key0 + i >= kstart) part_max[i & 3] = fmaxf(part_max[i & 3], __uint_as_float(raw[i >> 5][i & 31]));
       } else {
 #pragma unroll
-        for (int i = 0; i < KT; ++i) tile_max = fmaxf(tile_max, __uint_as_float(raw[i >> 5][i & 31]) * scale_log2);
+        for (int i = 0; i < KT; ++i) part_max[i & 3] = fmaxf(part_max[i & 3], __uint_as_float(raw[i >> 5][i & 31]));
       }
+      const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * scale_log2;
       const float m_new = fmaxf(m_run, tile_max);
       const float safe = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = fast_exp2(m_run - safe);
       m_run = m_new;
       // ---- P (rounded to bfloat16) into shared memory as the A operand of the second MMA
       if (k >= 1) ok = mbar_wait(smem_u32(&p_empty[wg]), (k - 1) & 1, &abort_flag, status);
-      float sum = 0.f;
+      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};         // four chains, combined in a fixed order
+      if (masked) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float p[8];
+        for (int c = 0; c < 8; ++c) {
+          float p[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int i = 8 * c + e;
-          p[e] = fast_exp2(__uint_as_float(raw[i >> 5][i & 31]) * scale_log2 - safe);
-          if (masked && !(key0 + i <= pos && key0 + i >= kstart)) p[e] = 0.f;
-          sum += p[e];
+          for (int e = 0; e < 8; ++e) {
+            const int i = 8 * c + e;
+            p[e] = fast_exp2(__uint_as_float(raw[i >> 5][i & 31]) * scale_log2 - safe);
+            if (!(key0 + i <= pos && key0 + i >= kstart)) p[e] = 0.f;
+            part_sum[e & 3] += p[e];
+          }
+          *reinterpret_cast<uint4*>(p_dst + swizzled(r, c)) =
+              make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
         }
-        *reinterpret_cast<uint4*>(p_dst + swizzled(r, c)) =
-            make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float p[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int i = 8 * c + e;
+            p[e] = fast_exp2(__uint_as_float(raw[i >> 5][i & 31]) * scale_log2 - safe);
+            part_sum[e & 3] += p[e];
+          }
+          *reinterpret_cast<uint4*>(p_dst + swizzled(r, c)) =
+              make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
+        }
       }
-      l_run = l_run * alpha + sum;
+      l_run = l_run * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&p_full[wg]));
@@ -377,6 +396,7 @@ VOSTI_API int vosti_attention_prefill_tc(const void* q, const void* k_cache, con
   VOSTI_REQUIRE(vosti_attention_prefill_tc_supported(d, page_size),
                 "attention_prefill_tc: head_dim %d must be 64 or 128 and page_size %d a multiple of 16", d, page_size);
   VOSTI_REQUIRE(max_pages > 0 && num_pages > 0 && window >= 0 && tokens_total > 0, "attention_prefill_tc: bad geometry");
+  VOSTI_REQUIRE(scale > 0.f, "attention_prefill_tc: the score scale must be positive");
   VOSTI_REQUIRE(count <= 65535 && nkv <= 65535, "attention_prefill_tc: too many requests or heads for one launch");
   if (count == 0 || max_q_len <= 0) return VOSTI_OK;
   const int group = nq / nkv;
