@@ -1,7 +1,9 @@
 """The engine at the benchmark model's layer sizes (hidden 4096, 32 query / 8 kv heads of
-128, intermediate 12288) with two layers and a smaller vocabulary that is no power of two,
-against the plain implementation: a whole prompt, a decoded tail and portions, in float32
-and bfloat16. This is where the kernels meet the tile sizes they are tuned for."""
+128, intermediate 12288) and at the next larger size of the family (hidden 5120, 40 query /
+8 kv heads: five query heads per kv head, intermediate 17408), with two layers and a smaller
+vocabulary that is no power of two, against the plain implementation: a whole prompt, a
+decoded tail and portions, in float32 and bfloat16. This is where the kernels meet the tile
+sizes they are tuned for, and sizes that divide none of them."""
 import pytest
 import torch
 
@@ -16,17 +18,24 @@ WIDE = _config(num_hidden_layers=2, hidden_size=4096, num_attention_heads=32, nu
                tie_word_embeddings=False, max_position_embeddings=4096)
 
 
-@pytest.fixture(scope="module")
-def wide_model(tmp_path_factory):
+WIDER = _config(num_hidden_layers=2, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                intermediate_size=17408, vocab_size=10007, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=4096)
+CONFIGS = {"8b": WIDE, "14b": WIDER}
+
+
+@pytest.fixture(scope="module", params=["8b", "14b"])
+def wide_model(request, tmp_path_factory):
     from vosti_b200.weights import write_random_model
-    folder = tmp_path_factory.mktemp("wide")
-    write_random_model(folder, WIDE, seed=3)
-    return str(folder), plain.load_model(folder)
+    config = CONFIGS[request.param]
+    folder = tmp_path_factory.mktemp("wide_" + request.param)
+    write_random_model(folder, config, seed=3)
+    return str(folder), plain.load_model(folder), config
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_benchmark_layer_sizes(wide_model, dtype, tmp_path):
-    path, plain_model = wide_model
+    path, plain_model, WIDE = wide_model
     requests = {"p": R.random_tokens(WIDE["vocab_size"], 333, seed=9), "q": R.random_tokens(WIDE["vocab_size"], 150, seed=10)}
     steps, alias = [], {}
     for kind, make in (("whole", R.whole_steps), ("tail", R.tail_steps),
