@@ -321,6 +321,26 @@ def test_gemm_tc_fused_silu_mul(dev, status, tokens, inter, k):
     assert y.shape == (tokens, inter) and torch.allclose(y.double(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("tokens", [5, 70, 300])
+@pytest.mark.parametrize("features,k", [(1000, 1000), (384, 64), (4096 + 128, 4096), (96, 200)])
+def test_gemm_tc_tile_packed_weight_gives_the_same_bits(dev, status, tokens, features, k):
+    """A weight stored tile by tile (zero-padded to whole tiles) multiplies to the same bits
+    as the row-major weight, in both kernels, with split K and with the fused SiLU epilogue."""
+    from vosti_b200 import ops
+    x = torch.randn(tokens, k, device=dev).bfloat16()
+    w = (torch.randn(features, k, device=dev) / 16).bfloat16()
+    packed = ops.PackedWeight(w)
+    assert packed.shape == (features, k) and packed.data.shape[2:] == (128, 64)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        assert torch.equal(ops.gemm_tc(x, w, status, out_dtype=out_dtype), ops.gemm_tc(x, packed, status, out_dtype=out_dtype))
+    a = ops.materialize(ops.gemm_tc(x, w, status, allow_partial=True))      # one deferred result at a time
+    b = ops.materialize(ops.gemm_tc(x, packed, status, allow_partial=True))
+    assert torch.equal(a, b)
+    if features % 32 == 0:
+        assert torch.equal(ops.gemm_tc(x, w, status, swiglu=True), ops.gemm_tc(x, packed, status, swiglu=True))
+    assert status.item() == 0
+
+
 def test_gemm_tc_rows_do_not_depend_on_their_companions(dev, status):
     """Within one tile size and split count a row's bits do not depend on the other rows."""
     from vosti_b200 import ops

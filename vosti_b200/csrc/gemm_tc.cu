@@ -46,7 +46,9 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ out, int tokens, int features, int k_blocks, int ld_out, int epilogue,
-               unsigned* status) {
+               int w_tiles, unsigned* status) {
+  // w_tiles > 0: the weight is stored tile by tile ([k block][feature tile][128][64], w_tiles
+  // feature tiles) and map_w sees it as a matrix of 64 columns; 0: row-major [features, k]
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -89,7 +91,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int i = 0; i < ahead; ++i) {
         const uint32_t bar = smem_u32(&full_bar[i]);
         mbar_expect_tx(bar, STAGE_BYTES);
-        tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb_begin + i) * BK, m0, bar);
+        if (w_tiles) tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, 0, ((kb_begin + i) * w_tiles + (int)blockIdx.x) * BM, bar);
+        else tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb_begin + i) * BK, m0, bar);
       }
       pdl_wait();
       for (int i = 0; i < ahead; ++i)
@@ -102,7 +105,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         mbar_expect_tx(bar, STAGE_BYTES);
         const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
         const int k0 = (kb_begin + i) * BK;          // multiple of 64 elements: 16-byte aligned
-        tma_load_2d(a_dst, &map_w, k0, m0, bar);
+        if (w_tiles) tma_load_2d(a_dst, &map_w, 0, ((kb_begin + i) * w_tiles + (int)blockIdx.x) * BM, bar);
+        else tma_load_2d(a_dst, &map_w, k0, m0, bar);
         tma_load_2d(a_dst + A_BYTES, &map_x, k0, n0, bar);
       }
     }
@@ -205,7 +209,7 @@ constexpr int WIDE_STAGE_BYTES = A_BYTES + WIDE_B_BYTES;
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     void* __restrict__ out, int tokens, int features, int k_blocks, int ld_out, int epilogue,
-                    unsigned* status) {
+                    int w_tiles, unsigned* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[WIDE_STAGES];
@@ -256,7 +260,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           mbar_expect_tx(bar, WIDE_STAGE_BYTES);
           const uint32_t a_dst = smem_u32(smem + s * WIDE_STAGE_BYTES);
           tma_load_2d(a_dst, &map_x, kb * BK, m0, bar);
-          tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, bar);
+          if (w_tiles) tma_load_2d(a_dst + A_BYTES, &map_w, 0, (kb * w_tiles + n0 / BM) * BM, bar);
+          else tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, bar);
         }
       }
     }
@@ -443,7 +448,7 @@ int token_tile(int tokens) { return tokens <= 32 ? 32 : tokens <= 64 ? 64 : toke
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int k_blocks, int ld_out,
-           int epilogue, int splits, unsigned* status, cudaStream_t stream) {
+           int epilogue, int splits, int w_tiles, unsigned* status, cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -456,7 +461,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
   }
   dim3 grid((features + BM - 1) / BM, (tokens + BN - 1) / BN, splits);
   vosti_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, mw, mx, out, tokens, features, k_blocks, ld_out,
-               epilogue, status);
+               epilogue, w_tiles, status);
   return 0;
 }
 
@@ -492,7 +497,7 @@ VOSTI_API int vosti_gemm_tc_splits(int tokens, int features, int k) {
 // With `defer_reduce` and more than one split the partial sums stay in the workspace
 // ([splits, tokens, features] float32) for a consumer that sums them itself; y is not written.
 VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, int features, int k, int epilogue,
-                            float* workspace, int64_t workspace_elems, int defer_reduce, unsigned* status,
+                            float* workspace, int64_t workspace_elems, int defer_reduce, int w_packed, unsigned* status,
                             cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && vosti_gemm_tc_supported(features, k), "gemm_tc: unsupported sizes F=%d K=%d", features, k);
   VOSTI_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "gemm_tc: unknown epilogue %d", epilogue);
@@ -506,9 +511,13 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
                 "gemm_tc: workspace too small for %d splits", splits);
   CUtensorMap mw_storage, mx;
   const CUtensorMap* mw = &mw_storage;
+  // a packed weight is [k blocks][feature tiles][128][64], zero-padded to whole tiles: its
+  // tensor map is that of a matrix of 64 columns
+  const int w_tiles = w_packed ? (features + BM - 1) / BM : 0;
+  const int w_rows = w_packed ? k_blocks * w_tiles * BM : features, w_cols = w_packed ? BK : k;
   if (tokens > 128) {
     // many tokens: persistent kernel with tokens on the M side
-    VOSTI_REQUIRE(weight_map(w, features, k, WIDE_BN, &mw_storage) && make_map(&mx, x, tokens, k, BM),
+    VOSTI_REQUIRE(weight_map(w, w_rows, w_cols, WIDE_BN, &mw_storage) && make_map(&mx, x, tokens, k, BM),
                   "gemm_tc: cuTensorMapEncodeTiled failed");
     constexpr size_t smem = (size_t)WIDE_STAGES * WIDE_STAGE_BYTES + 1024;
     static int sms = 0;
@@ -525,21 +534,21 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
     }
     const int tiles = ((tokens + BM - 1) / BM) * ((features + WIDE_BN - 1) / WIDE_BN);
     vosti_launch(gemm_tc_wide_kernel, dim3(tiles < sms ? tiles : sms), dim3(THREADS), smem, stream, mx, *mw, y, tokens,
-                 features, k_blocks, ld_out, epilogue, status);
+                 features, k_blocks, ld_out, epilogue, w_tiles, status);
     VOSTI_LAUNCH_CHECK();
   }
   const int bn = token_tile(tokens);
-  VOSTI_REQUIRE(weight_map(w, features, k, BM, &mw_storage) && make_map(&mx, x, tokens, k, bn),
+  VOSTI_REQUIRE(weight_map(w, w_rows, w_cols, BM, &mw_storage) && make_map(&mx, x, tokens, k, bn),
                 "gemm_tc: cuTensorMapEncodeTiled failed");
   void* dst = splits > 1 ? (void*)workspace : y;
   const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
   const int ld = splits > 1 ? features : ld_out;
   int rc;
   switch (bn) {
-    case 32: rc = launch<32, 5>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
-    case 64: rc = launch<64, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
-    case 128: rc = launch<128, 6>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
-    default: rc = launch<256, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, status, stream); break;
+    case 32: rc = launch<32, 5>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
+    case 64: rc = launch<64, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
+    case 128: rc = launch<128, 6>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
+    default: rc = launch<256, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
   }
   if (rc != 0) return rc;
   if (splits > 1 && !defer_reduce) {
@@ -621,9 +630,9 @@ VOSTI_API int vosti_gemm_tc_split_static(const void* x, const void* w, void* y, 
   const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
   int rc;
   switch (bn) {
-    case 32: rc = launch<32, 5>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, status, stream); break;
-    case 64: rc = launch<64, 4>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, status, stream); break;
-    default: rc = launch<128, 6>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, status, stream); break;
+    case 32: rc = launch<32, 5>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, status, stream); break;
+    case 64: rc = launch<64, 4>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, status, stream); break;
+    default: rc = launch<128, 6>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, status, stream); break;
   }
   if (rc != 0) return rc;
   if (splits > 1) {

@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..config.schema import ModelSpec
-from ..parts import build_block, build_norm, linear
+from ..parts import build_block, build_norm, linear, prepare_weight
 from ..weights.loader import WeightSpec
 
 
@@ -59,7 +59,8 @@ class DecoderModel:
             block.load({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, dtype)
         prefix = self._final_norm_prefix()
         self.final_norm.load({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, dtype)
-        self.head = self.embed if spec.tie_word_embeddings else tensors[spec.lm_head_name]
+        # a tied head is also read by rows (the embedding): it stays a plain tensor
+        self.head = self.embed if spec.tie_word_embeddings else prepare_weight(tensors[spec.lm_head_name], dtype)
         self.device, self.dtype = self.embed.device, dtype
         for block in self.blocks:
             block.setup(self.device, dtype)
@@ -71,6 +72,8 @@ class DecoderModel:
         def visit(obj):
             nonlocal total
             for value in vars(obj).values():
+                if isinstance(value, ops.PackedWeight):
+                    value = value.data
                 if isinstance(value, torch.Tensor) and value.is_cuda:
                     base = value.untyped_storage().data_ptr()
                     if base not in seen:
@@ -81,9 +84,10 @@ class DecoderModel:
                 visit(part)
         visit(self.final_norm)
         if self.head is not None:
-            seen_head = self.head.untyped_storage().data_ptr()
+            head = self.head.data if isinstance(self.head, ops.PackedWeight) else self.head
+            seen_head = head.untyped_storage().data_ptr()
             if seen_head not in seen:
-                total += self.head.untyped_storage().nbytes()
+                total += head.untyped_storage().nbytes()
         return total
 
     # ------------------------------------------------------------ forward

@@ -291,12 +291,46 @@ def materialize(x):
     return x.materialize() if isinstance(x, PartialSum) else x
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
+class PackedWeight:
+    """A [features, k] bfloat16 weight stored tile by tile for the tensor-core product:
+    [k blocks of 64][feature tiles of 128][128][64], zero-padded to whole tiles, so that every
+    tile a CTA streams is one contiguous 16 KiB piece of memory instead of 128 row pieces of
+    128 bytes."""
+
+    TILE_F, TILE_K = 128, 64
+
+    def __init__(self, w: torch.Tensor):
+        if w.dtype != torch.bfloat16 or w.dim() != 2:
+            raise KernelError("PackedWeight takes a 2-d bfloat16 matrix")
+        features, k = w.shape
+        ft, kb = -(-features // self.TILE_F), -(-k // self.TILE_K)
+        padded = w
+        if features != ft * self.TILE_F or k != kb * self.TILE_K:
+            padded = torch.zeros((ft * self.TILE_F, kb * self.TILE_K), dtype=w.dtype, device=w.device)
+            padded[:features, :k] = w
+        self.data = padded.view(ft, self.TILE_F, kb, self.TILE_K).permute(2, 0, 1, 3).contiguous()
+        self.shape = (features, k)
+        self.dtype, self.device = w.dtype, w.device
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.data.is_cuda
+
+    def numel(self) -> int:
+        return self.data.numel()
+
+    def element_size(self) -> int:
+        return self.data.element_size()
+
+
+def gemm_tc(x: torch.Tensor, w, status: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
             swiglu: bool = False, allow_partial: bool = False):
-    """y = x @ w.T on the tensor cores (bfloat16 operands, float32 accumulation). With
-    `swiglu` the rows of w are blocks of 16 gate rows followed by their 16 up rows and
-    y = silu(gate) * up has half as many columns."""
-    _contig(x, w)
+    """y = x @ w.T on the tensor cores (bfloat16 operands, float32 accumulation); w is a
+    [features, k] tensor or a `PackedWeight`. With `swiglu` the rows of w are blocks of 16 gate
+    rows followed by their 16 up rows and y = silu(gate) * up has half as many columns."""
+    packed = isinstance(w, PackedWeight)
+    w_data = w.data if packed else w
+    _contig(x, w_data)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc takes bfloat16 operands")
     tokens, k = x.shape
@@ -319,8 +353,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, *, out_dtype
     out = None if defer else torch.empty((tokens, width), dtype=out_dtype, device=x.device)
     if splits > 1:
         _SPLIT_GENERATION += 1
-    _check(lib.vosti_gemm_tc(_p(x), _p(w), _p(out), tokens, features, k, epilogue, _p(ws),
-                             ctypes.c_int64(ws.numel() if ws is not None else 0), int(defer), _p(status), _stream()),
+    _check(lib.vosti_gemm_tc(_p(x), _p(w_data), _p(out), tokens, features, k, epilogue, _p(ws),
+                             ctypes.c_int64(ws.numel() if ws is not None else 0), int(defer), int(packed), _p(status),
+                             _stream()),
            "gemm_tc", kernels=2 if splits > 1 and not defer else 1)
     if defer:
         return PartialSum(ws, splits, tokens, features, out_dtype, status)

@@ -1,7 +1,7 @@
 from .base import (FeedForward, Mixer, Norm, PagedCacheSpec, Part, PositionEncoding, StateSpec,
                    build_feed_forward, build_mixer, build_norm, build_position, part_factory,
                    register_part, unregister_part)
-from .linear import linear
+from .linear import linear, prepare_weight
 from .norm import RMSNorm
 from .rope import RotaryEncoding
 from .attention import Attention

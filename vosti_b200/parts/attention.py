@@ -19,7 +19,7 @@ from .. import ops
 from ..config.schema import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
 from .base import Mixer, PagedCacheSpec, PositionEncoding, register_part
-from .linear import linear
+from .linear import linear, prepare_weight
 
 
 class Attention(Mixer):
@@ -56,9 +56,12 @@ class Attention(Mixer):
         parts = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
         common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
         # one [ (nq + 2 nkv) d, hidden ] matrix: the projection is a single product
-        self.w_qkv = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
-        self.w_q = self.w_qkv[: self.nq * self.d]
-        self.w_o = tensors["o_proj.weight"]
+        w_qkv = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
+        self.w_qkv = prepare_weight(w_qkv, dtype)
+        # a layer that reads another layer's cache needs q only: the first rows of the matrix,
+        # or (tile-packed weight) the whole product, whose k and v are then dropped
+        self.w_q = w_qkv[: self.nq * self.d] if self.w_qkv is w_qkv else None
+        self.w_o = prepare_weight(tensors["o_proj.weight"], dtype)
         if self.head_norm_eps is not None:
             self.q_norm, self.k_norm = tensors["q_norm.weight"], tensors["k_norm.weight"]
             if self.q_norm.dtype != self.k_norm.dtype:
@@ -82,9 +85,12 @@ class Attention(Mixer):
             qkv = linear(ctx, x, self.w_qkv, allow_partial=True)   # summed inside qkv_post
             q = ops.qkv_post(qkv, cache.k, cache.v, nkv=self.nkv, k_norm_w=self.k_norm,
                              slot_mapping=group.slot_mapping, **common)
-        else:
+        elif self.w_q is not None:
             q = ops.qkv_post(linear(ctx, x, self.w_q), None, None, nkv=0, k_norm_w=None,
                              slot_mapping=None, **common)
+        else:
+            q = ops.qkv_post(linear(ctx, x, self.w_qkv, allow_partial=True), None, None, nkv=self.nkv,
+                             k_norm_w=self.k_norm, slot_mapping=None, **common)
         attn = ops.attention(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, head_dim=self.d,
                              scale=self.scale, window=self.window)
         return linear(ctx, attn, self.w_o, allow_partial=True)       # summed by the norm that follows

@@ -15,7 +15,7 @@ from .. import ops
 from ..config.schema import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
 from .base import FeedForward, register_part
-from .linear import linear, uses_tensor_cores
+from .linear import linear, prepare_weight, uses_tensor_cores
 
 
 class SwiGLU(FeedForward):
@@ -35,7 +35,7 @@ class SwiGLU(FeedForward):
     def load(self, tensors, dtype):
         gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         common = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
-        self.w_down = tensors["down_proj.weight"]
+        self.w_down = prepare_weight(tensors["down_proj.weight"], dtype)
         stacked = torch.cat([gate.to(common), up.to(common)], dim=0)
         # On the tensor-core path SiLU(gate)*up is the product's epilogue: rows are laid out
         # as blocks of 16 gate rows followed by their 16 up rows, so that both halves of an
@@ -44,7 +44,7 @@ class SwiGLU(FeedForward):
         if self.fused:
             h = stacked.shape[1]
             blocks = torch.stack([stacked[:self.inter].view(-1, 16, h), stacked[self.inter:].view(-1, 16, h)], dim=1)
-            self.w_gate_up = blocks.reshape(2 * self.inter, h).contiguous()
+            self.w_gate_up = prepare_weight(blocks.reshape(2 * self.inter, h).contiguous(), dtype)
         else:
             self.w_gate_up = stacked.contiguous()
 

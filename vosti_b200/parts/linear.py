@@ -7,16 +7,29 @@ The choice depends on types and on (N, K) only, never on the number of rows.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
 from .. import ops
 
+# VOSTI_PACK_WEIGHTS=0 keeps weights row-major (for comparisons; the results are the same bits).
+PACK_WEIGHTS = os.environ.get("VOSTI_PACK_WEIGHTS", "1") != "0"
 
-def uses_tensor_cores(x_dtype: torch.dtype, w: torch.Tensor) -> bool:
+
+def uses_tensor_cores(x_dtype: torch.dtype, w) -> bool:
     return (x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_cuda
             and ops.gemm_tc_supported(w.shape[0], w.shape[1]))
+
+
+def prepare_weight(w: torch.Tensor, serving_dtype: torch.dtype):
+    """What a part keeps of a [features, k] weight it only ever multiplies with: the
+    tile-packed copy if the tensor-core product will read it, else the tensor itself. A
+    weight that is also read by rows (a tied embedding table) must stay a tensor."""
+    if PACK_WEIGHTS and isinstance(w, torch.Tensor) and uses_tensor_cores(serving_dtype, w):
+        return ops.PackedWeight(w)
+    return w
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
@@ -25,6 +38,8 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, *, out_dtype: Optional[torch.d
     K splits not yet summed) for a consumer that adds them itself; the caller must hand it to
     such a consumer, or to `ops.materialize`, before any other product runs."""
     x = ops.materialize(x)
+    if isinstance(w, ops.PackedWeight) and x.dtype != torch.bfloat16:
+        raise ops.KernelError("a tile-packed weight serves bfloat16 activations only")
     if uses_tensor_cores(x.dtype, w):
         if row_index is not None:
             x = ops.gather_rows(x, row_index, ctx.status)
