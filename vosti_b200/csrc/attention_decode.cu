@@ -59,68 +59,76 @@ __device__ __forceinline__ void wait_or_abandon(uint32_t bar, uint32_t parity, u
 // A barrier among the consumer warps only (the producer never joins it).
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
 
-// Partial record of one (token, query head, segment): [0] max (base-2 scores), [1] sum,
-// [2 .. 2+d) accumulator.
-__host__ __device__ inline int record_floats(int d) { return d + 2; }
+// Partial record of one (token, query head, segment) in global memory: [0] max (base-2
+// scores), [1] sum, [2..3] unused, [4 .. 4+d) accumulator, so that the accumulator is read as
+// 16-byte words. (In shared memory a record is [max, sum, accumulator]: d + 2 floats.)
+__host__ __device__ inline int record_floats(int d) { return d + 4; }
 
 // One warp combines the segments first..last of one (token, query head): lane s holds
 // segment s's max and weight; the sums run over segments in segment order, whichever CTA
-// runs this. `base` points at the head's records, `dst` at its output row.
+// runs this. `base` points at the head's records, `dst` at its output row. A lane owns the
+// columns 4 * lane .. 4 * lane + 3 (and 128 further on for head sizes above 128); the loads of
+// up to BATCH segments are in flight together.
 __device__ __forceinline__ void merge_segments(const float* __restrict__ base, bf16* __restrict__ dst, int first,
                                                int last, int d) {
   const int lane = threadIdx.x & 31;
-  const int rec = d + 2;
-  // pass 1: the overall maximum
+  const int rec = record_floats(d);
+  constexpr int BATCH = 8;
+  // pass 1: every segment's (max, sum), the first 32 segments' kept for the second pass
+  float2 ml_first = make_float2(-INFINITY, 0.f);
   float m = -INFINITY;
   for (int s0 = first; s0 <= last; s0 += 32) {
     const int s = s0 + lane;
-    m = fmaxf(m, s <= last ? __ldcg(base + (int64_t)s * rec) : -INFINITY);
+    const float2 ml = s <= last ? __ldcg(reinterpret_cast<const float2*>(base + (int64_t)s * rec))   // other CTAs wrote these: read past L1
+                                : make_float2(-INFINITY, 0.f);
+    if (s0 == first) ml_first = ml;
+    m = fmaxf(m, ml.x);
   }
   m = warp_max(m);
   // pass 2: weights, sum and accumulator
   float l = 0.f;
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+  const bool second = 4 * lane + 128 < d;               // this lane also owns columns beyond 128
+  const bool owner = 4 * lane < d;
   for (int s0 = first; s0 <= last; s0 += 32) {
     const int mine = s0 + lane;
     float w_mine = 0.f, l_mine = 0.f;
     if (mine <= last) {
-      const float ms = __ldcg(base + (int64_t)mine * rec);
-      if (ms != -INFINITY) {
-        w_mine = fast_exp2(ms - m);
-        l_mine = __ldcg(base + (int64_t)mine * rec + 1) * w_mine;
+      const float2 ml = s0 == first ? ml_first : __ldcg(reinterpret_cast<const float2*>(base + (int64_t)mine * rec));
+      if (ml.x != -INFINITY) {
+        w_mine = fast_exp2(ml.x - m);
+        l_mine = ml.y * w_mine;
       }
     }
     const int n = min(32, last - s0 + 1);
-    // segments in batches of 4: their loads are issued together, then summed in segment order
-    for (int j0 = 0; j0 < n; j0 += 4) {
-      float v[4][8];
+    for (int j0 = 0; j0 < n; j0 += BATCH) {
+      float4 v[BATCH][2];
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int c = lane + 32 * i;
-          v[b][i] = (c < d) ? __ldcg(row + c) : 0.f;       // other CTAs wrote these: read past L1
-        }
+      for (int b = 0; b < BATCH; ++b) {
+        const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 4;
+        v[b][0] = owner ? __ldcg(reinterpret_cast<const float4*>(row + 4 * lane)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[b][1] = second ? __ldcg(reinterpret_cast<const float4*>(row + 4 * lane + 128)) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
+      for (int b = 0; b < BATCH; ++b) {
         const bool live = j0 + b < n;
         const float w = live ? __shfl_sync(0xffffffffu, w_mine, (j0 + b) & 31) : 0.f;
         l += live ? __shfl_sync(0xffffffffu, l_mine, (j0 + b) & 31) : 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[b][i], w, acc[i]);
+        for (int i = 0; i < 2; ++i) {
+          acc[i].x = fmaf(v[b][i].x, w, acc[i].x);
+          acc[i].y = fmaf(v[b][i].y, w, acc[i].y);
+          acc[i].z = fmaf(v[b][i].z, w, acc[i].z);
+          acc[i].w = fmaf(v[b][i].w, w, acc[i].w);
+        }
       }
     }
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int c = lane + 32 * i;
-    if (c < d) dst[c] = __float2bfloat16_rn(acc[i] * inv);
-  }
+  if (owner)
+    *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(pack_bf16(acc[0].x * inv, acc[0].y * inv), pack_bf16(acc[0].z * inv, acc[0].w * inv));
+  if (second)
+    *reinterpret_cast<uint2*>(dst + 4 * lane + 128) = make_uint2(pack_bf16(acc[1].x * inv, acc[1].y * inv), pack_bf16(acc[1].z * inv, acc[1].w * inv));
 }
 
 struct ItemMeta {
@@ -139,7 +147,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         int segment_keys, int max_segments, float scale_log2, int window, unsigned* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[CONSUMERS][RING];
-  __shared__ __align__(8) uint64_t q_full[Q_BUFFERS], q_empty[Q_BUFFERS];
+  __shared__ __align__(8) uint64_t q_full[Q_BUFFERS], q_empty[Q_BUFFERS], meta_bar[Q_BUFFERS];
   __shared__ ItemMeta item_meta[Q_BUFFERS];
   __shared__ ItemMeta consumer_meta;       // the consumers' common copy: they all take the same decisions
   __shared__ int tile_rows[Q_BUFFERS][MAX_SEGMENT_PAGES];   // cache row of each tile's first key (whole pages)
@@ -164,6 +172,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int b = 0; b < Q_BUFFERS; ++b) {
       mb_init(smem_addr(&q_full[b]), 1);
       mb_init(smem_addr(&q_empty[b]), CONSUMERS);
+      mb_init(smem_addr(&meta_bar[b]), 1);
     }
     mb_fence_init();
   }
@@ -174,13 +183,15 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int i = threadIdx.x; i < CONSUMERS * RING * slot_bytes / 16; i += THREADS)
       reinterpret_cast<uint4*>(ring_base)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
-  pdl_wait();
   pdl_launch_dependents();
+  // What the host wrote before the step (positions, requests, block tables, the token list) is
+  // read at once; q and the newest cache rows come from the kernel before this one: the producer
+  // waits for it before it fetches q, the consumers before they request their first tile.
 
   // items in segment-major order: the short last segments of the requests come last, which
   // evens out what the CTAs get
-  const int64_t pairs = (int64_t)count * nkv;
-  const int64_t total_items = pairs * max_segments;
+  const int pairs = count * nkv;                      // the launcher keeps pairs * max_segments below 2^31
+  const int total_items = pairs * max_segments;
   const int quarter = segment_keys / CONSUMERS;
 
   if (warp == 0) {
@@ -188,13 +199,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // It describes the items to the consumers one item ahead: token, position, the cache row
     // of every tile (block table resolved) and the query rows. The consumers fetch K and V.
     uint32_t q_issued = 0;
-    const int my_items = blockIdx.x < total_items ? (int)((total_items - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+    bool waited = false;
+    const int my_items = (int)blockIdx.x < total_items ? (total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     for (int base = 0; base < my_items; base += 32) {
       // token, position and request of 32 items at once: lane l holds item base + l
       int t_l = 0, pos_l = -1, req_l = 0;
       if (base + lane < my_items) {
-        const int64_t idx = blockIdx.x + (int64_t)(base + lane) * gridDim.x;
-        const int item = (int)((idx % pairs) / nkv);
+        const int idx = (int)blockIdx.x + (base + lane) * (int)gridDim.x;
+        const int item = (idx % pairs) / nkv;
         t_l = token_list ? token_list[item] : item;
         pos_l = positions[t_l];
         req_l = request_of[t_l];
@@ -204,8 +216,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       int next_pages[MAX_SEGMENT_PAGES / 32];
       auto fetch_pages = [&](int j) {
         const int pos = __shfl_sync(0xffffffffu, pos_l, j), req = __shfl_sync(0xffffffffu, req_l, j);
-        const int64_t idx = blockIdx.x + (int64_t)(base + j) * gridDim.x;
-        const int seg = (int)(idx / pairs);
+        const int idx = (int)blockIdx.x + (base + j) * (int)gridDim.x;
+        const int seg = idx / pairs;
         const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         const int seg_begin = seg * segment_keys;
         const int first_index = seg_begin / page_size;
@@ -221,10 +233,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       for (int j = 0; j < n; ++j) {
         const int t = __shfl_sync(0xffffffffu, t_l, j), pos = __shfl_sync(0xffffffffu, pos_l, j);
         const int req = __shfl_sync(0xffffffffu, req_l, j);
-        const int64_t idx = blockIdx.x + (int64_t)(base + j) * gridDim.x;
-        const int seg = (int)(idx / pairs);
-        const int g = (int)((idx % pairs) % nkv);
-        const int item = (int)((idx % pairs) / nkv);
+        const int idx = (int)blockIdx.x + (base + j) * (int)gridDim.x;
+        const int seg = idx / pairs;
+        const int g = (idx % pairs) % nkv;
+        const int item = (idx % pairs) / nkv;
         const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         const int seg_begin = seg * segment_keys, seg_end = min(seg_begin + segment_keys, pos + 1);
         if (whole_pages) {
@@ -248,8 +260,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
           }
           __syncwarp();
         }
+        if (!waited) {
+          pdl_wait();
+          waited = true;
+        }
         if (lane == 0) {
+          // the description first: the consumers request their tiles while the query rows travel
           item_meta[qb] = ItemMeta{t, pos, item, g, seg, kstart, req, 0};
+          mb_arrive(smem_addr(&meta_bar[qb]));
           mb_expect_tx(smem_addr(&q_full[qb]), (uint32_t)(group * d * 2));
           // the item's query rows are contiguous in q: the heads of one group
           for (int row = 0; row < group; ++row)
@@ -260,12 +278,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       }
     }
     // ---- no more items
+    if (!waited) pdl_wait();
     const uint32_t qb = q_issued % Q_BUFFERS;
     if (q_issued >= Q_BUFFERS)
       wait_or_abandon(smem_addr(&q_empty[qb]), ((q_issued / Q_BUFFERS) - 1) & 1, status, &abandoned);
     if (lane == 0) {
       item_meta[qb] = ItemMeta{-1, 0, 0, 0, 0, 0, 0, 0};
-      mb_arrive(smem_addr(&q_full[qb]));
+      mb_arrive(smem_addr(&meta_bar[qb]));
     }
     return;
   }
@@ -280,6 +299,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_half = lane >> 4;
   const uint32_t k_lane = k_row * 128, k_xor = (uint32_t)((k_half ^ (k_row & 7)) << 4);
   const uint32_t v_lane = v_row * 128, v_xor = (uint32_t)((v_half ^ (v_row & 7)) << 4);
+  pdl_wait();
   uint32_t seen = 0, n_issued = 0, q_seen = 0;       // tiles consumed and requested by this warp, items seen
   int ahead = 0;                                     // tiles of the next item already requested
   bool pending = false;                              // an item whose partials are written but not counted in
@@ -356,7 +376,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       __threadfence();
       for (int row = cw; row < group; row += CONSUMERS) {
         const int h = p_g * group + row;
-        merge_segments(partial + ((int64_t)p_item * nq + h) * max_segments * rec, out + ((int64_t)p_t * nq + h) * d,
+        merge_segments(partial + ((int64_t)p_item * nq + h) * max_segments * record_floats(d), out + ((int64_t)p_t * nq + h) * d,
                        p_first, p_last, d);
       }
     }
@@ -365,13 +385,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   while (true) {
     const uint32_t qb = q_seen % Q_BUFFERS;
     if (ctid == 0) {
-      wait_or_abandon(smem_addr(&q_full[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
+      wait_or_abandon(smem_addr(&meta_bar[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
       consumer_meta = item_meta[qb];
     }
     consumer_sync();                                 // also: everyone is done with the previous item's merge area
     const ItemMeta meta = consumer_meta;
     if (meta.t < 0) break;
-    wait_or_abandon(smem_addr(&q_full[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
+    wait_or_abandon(smem_addr(&meta_bar[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
     const int pos = meta.pos, kstart = meta.kstart, seg = meta.seg, g = meta.g;
     int first_tile, tiles;
     my_tiles(meta, first_tile, tiles);
@@ -386,6 +406,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     int next_first = 0, next_tiles = 0;
 
     // ---- Q fragments of this item into registers (up to head size 128)
+    wait_or_abandon(smem_addr(&q_full[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
     const uint8_t* q_s = q_base + qb * 16 * q_pitch;
     constexpr bool Q_IN_REGISTERS = DMAX <= 128;
     uint32_t qa[Q_IN_REGISTERS ? DMAX / 16 : 1][4];
@@ -492,7 +513,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         request_tile(meta, qb, first_tile + (requested++) * TILE);
       } else {
         // this item's tiles are all on their way: start on the next item's if it has been described
-        if (!next_known && !abandoned && mb_try_wait(smem_addr(&q_full[nqb]), ((q_seen + 1) / Q_BUFFERS) & 1)) {
+        if (!next_known && !abandoned && mb_try_wait(smem_addr(&meta_bar[nqb]), ((q_seen + 1) / Q_BUFFERS) & 1)) {
           next_known = true;
           next_meta = item_meta[nqb];
           if (next_meta.t >= 0) my_tiles(next_meta, next_first, next_tiles);
@@ -543,7 +564,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const float mw = merge[((int64_t)w * group + row) * rec];
         weight[w] = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
       }
-      float* dst = partial + (((int64_t)meta.item * nq + g * group + row) * max_segments + seg) * rec;
+      float* dst = partial + (((int64_t)meta.item * nq + g * group + row) * max_segments + seg) * record_floats(d);
       for (int c = ctid; c < rec; c += CONSUMERS * 32) {
         float value;
         if (c == 0) {
@@ -553,7 +574,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
           for (int w = 0; w < CONSUMERS; ++w) value += merge[((int64_t)w * group + row) * rec + c] * weight[w];
         }
-        dst[c] = value;
+        dst[c < 2 ? c : c + 2] = value;                  // the accumulator starts at float 4 of a global record
       }
     }
     if (pending) merge_if_last();
@@ -626,7 +647,7 @@ VOSTI_API int vosti_attention_decode_segment_keys(int count, int nq, int nkv, in
   return choose_segment_keys(count, nkv, d, nq / nkv, max_kv_len);
 }
 
-// float32 scratch elements needed: count * nq * segments * (d + 2).
+// float32 scratch elements needed: count * nq * segments * (d + 4).
 VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int nkv, int d, int max_kv_len) {
   const int keys = vosti_attention_decode_segment_keys(count, nq, nkv, d, max_kv_len);
   return (int64_t)count * nq * ((max_kv_len + keys - 1) / keys) * record_floats(d);
@@ -668,6 +689,7 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
                 "attention_decode: cuTensorMapEncodeTiled failed");
   const size_t smem = decode_smem_bytes(d, group);
   const int64_t items = (int64_t)count * nkv * segments;
+  VOSTI_REQUIRE(items < ((int64_t)1 << 30), "attention_decode: %lld work items are too many for one launch", (long long)items);
   const int64_t ctas = (int64_t)sm_count() * ctas_per_sm(d, group);
   dim3 grid((unsigned)(items < ctas ? items : ctas));
   int page_shift = -1;
