@@ -21,14 +21,14 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
                 const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
                 const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv, int d,
                 unsigned* status) {
-  pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int half = d >> 1;
   const int heads = nq + 2 * nkv;
   const int64_t in_base = (int64_t)t * heads * d;
 
+  // Positions, slots, rotation tables and norm weights were written before the step began:
+  // they are read while the projection before this kernel may still be running.
   int pos = positions ? positions[t] : 0;
   if (cos_table && (pos < 0 || pos >= max_positions)) {
     if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
@@ -42,6 +42,15 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
       slot = -1;
     }
   }
+  float cs[MAX_PAIRS_PER_LANE], sn[MAX_PAIRS_PER_LANE];
+#pragma unroll
+  for (int j = 0; j < MAX_PAIRS_PER_LANE; ++j) {
+    const int i = lane + 32 * j;
+    cs[j] = (cos_table && i < half) ? cos_table[(int64_t)pos * half + i] : 1.f;
+    sn[j] = (cos_table && i < half) ? sin_table[(int64_t)pos * half + i] : 0.f;
+  }
+  pdl_wait();
+  pdl_launch_dependents();
 
   for (int h = blockIdx.y * nwarps + warp; h < heads; h += gridDim.y * nwarps) {
     const T* src = qkv + in_base + (int64_t)h * d;
@@ -118,7 +127,7 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
         b = b * rrms * load_flex(w, norm_w_is_f32, i + half);
       }
       if (cos_table) {
-        const float c = cos_table[(int64_t)pos * half + i], s = sin_table[(int64_t)pos * half + i];
+        const float c = cs[j], s = sn[j];
         const float ra = a * c - b * s, rb = b * c + a * s;
         a = ra;
         b = rb;
@@ -143,8 +152,6 @@ qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf1
                      unsigned* status) {
   constexpr int HALF = 32 * VE, D = 2 * HALF;
   struct alignas(2 * VE) Word { bf16 v[VE]; };
-  pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int heads = nq + 2 * nkv;
@@ -174,6 +181,8 @@ qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf1
     wk1[e] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i) : 1.f;
     wk2[e] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i + HALF) : 1.f;
   }
+  pdl_wait();                      // everything above was written before the step began
+  pdl_launch_dependents();
   constexpr int UNROLL = 2;
   for (int h0 = warp; h0 < heads; h0 += 8 * UNROLL) {
     Word a[UNROLL], b[UNROLL];
