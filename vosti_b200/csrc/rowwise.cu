@@ -156,6 +156,14 @@ rmsnorm_partial_kernel(const float* __restrict__ partial, int splits, int64_t pl
                        T* __restrict__ residual_out, int width, float eps) {
   __shared__ float scratch[32];
   extern __shared__ float row_sum[];                       // the summed row, kept for the second pass
+  // the norm weights do not depend on the kernel before this one: read them while it still runs
+  constexpr int PRELOAD = 4;
+  float w_pre[PRELOAD];
+#pragma unroll
+  for (int j = 0; j < PRELOAD; ++j) {
+    const int i = threadIdx.x + j * BLOCK;
+    w_pre[j] = i < width ? load_flex(weight, weight_is_f32, i) : 0.f;
+  }
   pdl_wait();
   pdl_launch_dependents();
   const int64_t base = (int64_t)blockIdx.x * width;
@@ -211,7 +219,16 @@ rmsnorm_partial_kernel(const float* __restrict__ partial, int splits, int64_t pl
   __syncthreads();                                         // the second pass reads other threads' columns
   const float total = block_sum(ss, scratch);
   const float rrms = rsqrtf(total / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += BLOCK) {
+#pragma unroll
+  for (int j = 0; j < PRELOAD; ++j) {
+    const int i = threadIdx.x + j * BLOCK;
+    if (i < width) {
+      const float h = row_sum[i];
+      if (residual_out) residual_out[base + i] = from_f32<T>(h);
+      out[base + i] = from_f32<T>(h * rrms * w_pre[j]);
+    }
+  }
+  for (int i = threadIdx.x + PRELOAD * BLOCK; i < width; i += BLOCK) {
     const float h = row_sum[i];
     if (residual_out) residual_out[base + i] = from_f32<T>(h);
     out[base + i] = from_f32<T>(h * rrms * load_flex(weight, weight_is_f32, i));
