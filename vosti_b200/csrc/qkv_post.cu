@@ -139,7 +139,7 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
 }
 
 // The same pass for many tokens (prompts), bfloat16, head sizes 64, 128 and 256: one block per
-// token, a warp takes every eighth head and two heads at a time, so that the loads of both are
+// token, a warp takes every eighth head and six heads at a time, so that the loads of all are
 // in flight together; a lane holds VE consecutive elements of each half of the head and moves
 // them as one 2-, 4- or 8-byte word.
 template <int VE>
@@ -183,7 +183,7 @@ qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf1
   }
   pdl_wait();                      // everything above was written before the step began
   pdl_launch_dependents();
-  constexpr int UNROLL = 2;
+  constexpr int UNROLL = 6;
   for (int h0 = warp; h0 < heads; h0 += 8 * UNROLL) {
     Word a[UNROLL], b[UNROLL];
 #pragma unroll

@@ -125,12 +125,11 @@ def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], s
     if B == 0:
         raise ValueError("a step needs at least one entry")
     q_lens = [len(e.tokens) for e in entries]
-    handles = []
-    for e in entries:
-        h = cache._handles.get(e.request_id)
-        if h is None:
-            raise KeyError(f"request {e.request_id!r} is not live")
-        handles.append(h)
+    known = cache._handles
+    try:
+        handles = [known[e.request_id] for e in entries]
+    except KeyError as missing:
+        raise KeyError(f"request {missing.args[0]!r} is not live") from None
     G = len(cache.groups)
     ids = (ctypes.c_int64 * B)(*handles)
     counts = (ctypes.c_int32 * B)(*q_lens)
@@ -148,13 +147,17 @@ def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], s
         offsets.append(total)
         total += _round_up(max(s, 1), 4)
     extras = dict(extras or {})
+    single = T == B                    # a decode-only step: one token per request
     short_tokens, long_rows, cursor = [], [], 0
-    for i, n in enumerate(q_lens):
-        if n <= SHORT_ROW:
-            short_tokens.extend(range(cursor, cursor + n))
-        else:
-            long_rows.append(i)
-        cursor += n
+    if single:
+        short_tokens = range(B)
+    else:
+        for i, n in enumerate(q_lens):
+            if n <= SHORT_ROW:
+                short_tokens.extend(range(cursor, cursor + n))
+            else:
+                long_rows.append(i)
+            cursor += n
     if short_tokens and long_rows:
         extras["_short_tokens"] = np.asarray(short_tokens, dtype=np.int32)
         extras["_long_rows"] = np.asarray(long_rows, dtype=np.int32)
@@ -166,16 +169,20 @@ def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], s
     staging.reserve(total)
     buf = staging.host_np
     o_tok, o_pos, o_req, o_cu, o_kv, o_slot, o_want = offsets[:7]
-    cursor, wcursor = 0, 0
-    for i, e in enumerate(entries):
-        n = q_lens[i]
-        buf[o_tok + cursor:o_tok + cursor + n] = e.tokens
-        for w in e.want:
-            if not 0 <= w < n:
-                raise ValueError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
-            buf[o_want + wcursor] = cursor + w
-            wcursor += 1
-        cursor += n
+    if single and W == B and all(len(e.want) == 1 and e.want[0] == 0 for e in entries):
+        buf[o_tok:o_tok + B] = [e.tokens[0] for e in entries]
+        buf[o_want:o_want + B] = np.arange(B, dtype=np.int32)
+    else:
+        cursor, wcursor = 0, 0
+        for i, e in enumerate(entries):
+            n = q_lens[i]
+            buf[o_tok + cursor:o_tok + cursor + n] = e.tokens
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
+                buf[o_want + wcursor] = cursor + w
+                wcursor += 1
+            cursor += n
     base = staging.host.data_ptr()
     at = lambda offset: ctypes.cast(base + 4 * offset, host.i32p)
     slot_ptrs = (host.i32p * max(G, 1))(*[at(offsets[7 + 2 * g]) for g in range(G)])
@@ -194,7 +201,7 @@ def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], s
     groups = [GroupView(block_table=dev[offsets[8 + 2 * g]:offsets[8 + 2 * g] + B * max_pages[g]].view(B, max_pages[g]),
                         slot_mapping=dev[offsets[7 + 2 * g]:offsets[7 + 2 * g] + T], page_size=cache.page_size,
                         max_pages=max_pages[g]) for g in range(G)]
-    kv_lens = [starts[i] + q_lens[i] for i in range(B)]
+    kv_lens = (np.frombuffer(starts, dtype=np.int32, count=B) + np.asarray(q_lens, dtype=np.int32)).tolist()
     state_slots = buf[o_slot:o_slot + B].tolist()
     return StepContext(
         num_tokens=T, num_requests=B, tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T],
