@@ -415,6 +415,26 @@ def test_prefill_attention_on_tcgen05(dev, status, nq, nkv, d, page, window):
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("step", [0.02, 0.2, 2.0])
+def test_prefill_attention_on_tcgen05_with_a_rising_maximum(dev, status, step):
+    """Scores that grow with the key index: the kernel's reference maximum is raised (and the
+    running product in tensor memory scaled down) at every tile for the steep ramp, only now
+    and then for the gentle ones, where exponentials above one are accumulated in between."""
+    nq, nkv, d, page, L = 8, 2, 128, 16, 900
+    case = paged_case(dev, torch.bfloat16, [L], [L], nq, nkv, d, page, seed=3)
+    direction = torch.nn.functional.normalize(torch.randn(d), dim=0)
+    case["q"][:, :, :] = (8.0 * direction + 0.1 * torch.randn(L, nq, d)).bfloat16().float()
+    case["qs"][0][:] = case["q"]
+    for pos in range(L):
+        slot = int(case["table"][0, pos // page]) * page + pos % page
+        case["ks"][0][pos] = (step * pos * direction + 0.05 * torch.randn(nkv, d)).bfloat16().float()
+        case["k_cache"][slot, :] = case["ks"][0][pos]
+    out = _run_tc_attention(dev, status, case, [L], [L], nq, nkv, d, page, 1.0, 0, "prefill", kernel="tc")
+    want = reference_attention(case, 1.0, 0)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.float().cpu(), want, atol=3e-2, rtol=3e-2), (out.float().cpu() - want).abs().max()
+
+
 def test_prefill_attention_on_tcgen05_rows_do_not_depend_on_companions(dev, status):
     """A request's rows are the same bits whether it runs alone or beside others."""
     nq, nkv, d, page = 8, 2, 128, 16

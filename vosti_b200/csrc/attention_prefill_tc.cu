@@ -7,17 +7,19 @@
 //   the absolute key index. Roles, one warpgroup each:
 //     * two softmax warpgroups, one thread per row; the first takes the even tiles, the second
 //       the odd ones. A thread reads its row's scores from tensor memory, does the online
-//       softmax (base 2, float32), writes P (rounded to bfloat16) to shared memory for the
-//       second MMA, and adds the product tile to the row's accumulator in registers, scaled by
-//       the factor of the running maximum. At the end the two groups' (max, sum, accumulator)
-//       are merged, normalised and stored.
+//       softmax (base 2, float32) and writes P (rounded to bfloat16) to shared memory for the
+//       second MMA, which adds to the group's running product in tensor memory. The maximum
+//       the exponentials are taken against follows the true maximum lazily: only when it
+//       falls behind by more than 8 (P would pass 2^8) is it raised and the running product
+//       scaled down in tensor memory. At the end the two groups' (max, sum, product) are
+//       merged, normalised and stored.
 //     * four loader warps: each brings 16 keys of a tile, one TMA box per 64 features of K
 //       and of V straight from the page, into the tensor cores' 128-byte-swizzled layout
 //       (four stages). The query rows come as one 4-D box per 64 features.
 //     * four threads (one per warp) issue the MMAs: S = Q K^T (M 128, N 64) into the score
 //       buffer of the tile's group in tensor memory, and P V (M 128, N = head size, V read as
-//       an MN-major operand straight from its [key][feature] rows) into the group's product
-//       buffer; scores and products, even and odd tiles have a thread each. The scores of a
+//       an MN-major operand straight from its [key][feature] rows) accumulating in the group's
+//       product buffer; scores and products, even and odd tiles have a thread each. The scores of a
 //       group's next tile are issued as soon as it has read the last ones.
 //   Registers move from the loader and MMA warpgroups to the softmax ones (setmaxnreg).
 //
@@ -55,7 +57,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             int page_size, int page_shift, int num_pages, int nq, int nkv, float scale_log2,
                             int window, unsigned* status) {
   constexpr int NB = D / 64;                          // 64-element blocks of the head size
-  constexpr int CHUNKS = D / 8;                       // 16-byte chunks per row
   constexpr int Q_BYTES = NB * ROWS * 128;
   constexpr int K_BYTES = NB * KT * 128;              // one tile of K; V the same
   constexpr int STAGE_BYTES = 2 * K_BYTES;
@@ -69,7 +70,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* kv_s = q_s + Q_BYTES;
   uint8_t* p_s = kv_s + STAGES * STAGE_BYTES;
   __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], edge_bar[KT / GROUP_KEYS];
-  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], pv_full[2], pv_empty[2];
+  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], pv_full[2];
   __shared__ uint32_t tmem_base_holder;
   __shared__ volatile int abort_flag;
 
@@ -103,7 +104,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(smem_u32(&p_full[i]), 4);
       mbar_init(smem_u32(&p_empty[i]), 1);
       mbar_init(smem_u32(&pv_full[i]), 1);
-      mbar_init(smem_u32(&pv_empty[i]), 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -124,30 +124,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int pos = valid ? shift + token : -1;                  // -1: no key is visible, nothing is written
     const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    // m_run is the maximum the exponentials are taken against. It follows the true running
+    // maximum lazily: only when a tile's maximum exceeds it by more than RESCALE (P would pass
+    // 2^RESCALE) is it raised and the running product, which stays in tensor memory, scaled down.
+    constexpr float RESCALE = 8.f;
+    float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     uint8_t* p_dst = p_s + wg * P_BYTES;
-
-    // O = O * alpha + (P V) of this group's k-th tile
-    auto accumulate = [&](int k, float alpha) {
-      ok = ok && mbar_wait(smem_u32(&pv_full[wg]), k & 1, &abort_flag, status);
-      tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 64) {
-        uint32_t v[2][32];                              // two loads in flight
-        tmem_load32_async(lane_base + PV_COL + wg * D + c0, v[0]);
-        tmem_load32_async(lane_base + PV_COL + wg * D + c0 + 32, v[1]);
-        tmem_wait_loads();
-#pragma unroll
-        for (int j = 0; j < 64; ++j) o[c0 + j] = fmaf(o[c0 + j], alpha, __uint_as_float(v[j >> 5][j & 31]));
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&pv_empty[wg]));
-    };
+    const uint32_t o_tmem = lane_base + PV_COL + wg * D;
 
     int k = 0;
     for (int j = wg; j < tiles && ok; j += 2, ++k) {
@@ -175,12 +159,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int i = 0; i < KT; ++i) part_max[i & 3] = fmaxf(part_max[i & 3], __uint_as_float(raw[i >> 5][i & 31]));
       }
       const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * scale_log2;
-      const float m_new = fmaxf(m_run, tile_max);
-      const float safe = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = fast_exp2(m_run - safe);
-      m_run = m_new;
+      // raise the reference maximum? (always at the first visible key: m_run = -inf)
+      const bool raise = tile_max > m_run + RESCALE || (m_run == -INFINITY && tile_max > -INFINITY);
+      float alpha = 1.f;
+      if (raise) {
+        alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run - tile_max);
+        m_run = tile_max;
+        l_run *= alpha;
+      }
+      const float safe = m_run == -INFINITY ? 0.f : m_run;
+      // ---- the product of the tile before this one is complete by now (it was issued a softmax
+      // ago); the wait also keeps this thread in step with the barrier's phases. If any row of the
+      // warp raised its maximum, the warp scales its rows of the running product.
+      if (k >= 1) {
+        ok = mbar_wait(smem_u32(&pv_full[wg]), (k - 1) & 1, &abort_flag, status);
+        if (__any_sync(0xffffffffu, raise)) {
+          tc_fence_after();
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t v[32];
+            tmem_load32(o_tmem + c0, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_store32(o_tmem + c0, v);
+          }
+          tmem_wait_stores();
+          tc_fence_before();
+        }
+        ok = ok && mbar_wait(smem_u32(&p_empty[wg]), (k - 1) & 1, &abort_flag, status);
+      }
       // ---- P (rounded to bfloat16) into shared memory as the A operand of the second MMA
-      if (k >= 1) ok = mbar_wait(smem_u32(&p_empty[wg]), (k - 1) & 1, &abort_flag, status);
       float part_sum[4] = {0.f, 0.f, 0.f, 0.f};         // four chains, combined in a fixed order
       if (masked) {
 #pragma unroll
@@ -210,45 +218,63 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
               make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
         }
       }
-      l_run = l_run * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
+      l_run += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&p_full[wg]));
-      // ---- the product of this group's tile before this one has had the time of this softmax
-      if (k > 0) accumulate(k - 1, alpha_prev);
-      alpha_prev = alpha;
     }
-    if (ok && k > 0) accumulate(k - 1, alpha_prev);
+    if (ok && k > 0) ok = mbar_wait(smem_u32(&pv_full[wg]), (k - 1) & 1, &abort_flag, status);
+    tc_fence_after();
 
-    // ---- merge the two groups (every MMA is complete once both have their last products)
+    // ---- merge the two groups (every MMA is complete once both have their last products),
+    // 32 columns at a time: the second group's rows go through shared memory
     float* merge = reinterpret_cast<float*>(kv_s);                    // [128 rows][D + 2]
     softmax_sync();
     if (wg == 1) {
       float* mine = merge + r * (D + 2);
       mine[0] = m_run;
       mine[1] = l_run;
+      if (k > 0) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t v[32];
+          tmem_load32(o_tmem + c0, v);
 #pragma unroll
-      for (int i = 0; i < D; ++i) mine[2 + i] = o[i];
+          for (int i = 0; i < 32; ++i) mine[2 + c0 + i] = __uint_as_float(v[i]);
+        }
+      }
     }
     softmax_sync();
-    if (wg == 0 && ok && valid) {
+    if (wg == 0) {
       const float* other = merge + r * (D + 2);
       const float m_other = other[0];
+      const bool has_other = m_other != -INFINITY;                   // the second group saw a visible key
       const float m = fmaxf(m_run, m_other);
       const float w_mine = m_run == -INFINITY ? 0.f : fast_exp2(m_run - m);
-      const float w_other = m_other == -INFINITY ? 0.f : fast_exp2(m_other - m);
+      const float w_other = has_other ? fast_exp2(m_other - m) : 0.f;
       const float l = l_run * w_mine + other[1] * w_other;
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + ((int64_t)(q_start + token) * nq + g * group + r % group) * D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t v[32];
+        tmem_load32(o_tmem + c0, v);                                  // the first group always has a tile
+        if (ok && valid) {
 #pragma unroll
-      for (int c = 0; c < CHUNKS; ++c) {
-        float y[8];
+          for (int c = 0; c < 4; ++c) {
+            float y[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = (o[8 * c + e] * w_mine + other[2 + 8 * c + e] * w_other) * inv;
-        *reinterpret_cast<uint4*>(dst + 8 * c) =
-            make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+            for (int e = 0; e < 8; ++e) {
+              const float mine_v = __uint_as_float(v[8 * c + e]) * w_mine;
+              y[e] = (has_other ? mine_v + other[2 + c0 + 8 * c + e] * w_other : mine_v) * inv;
+            }
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * c) =
+                make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+          }
+        }
       }
     }
+    tc_fence_before();
   } else if (warp < MMA_WARP) {
     // ------------------------------------------------------------ loaders
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -345,14 +371,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           const int stage = t % STAGES;
           ok = mbar_wait(smem_u32(&kv_full[stage]), (t / STAGES) & 1, &abort_flag, status);
           if (ok) ok = mbar_wait(smem_u32(&p_full[wg]), k & 1, &abort_flag, status);
-          if (ok && k >= 1) ok = mbar_wait(smem_u32(&pv_empty[wg]), (k - 1) & 1, &abort_flag, status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t vd = v_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
           for (int ks = 0; ks < KT / 16; ++ks)
             umma_bf16(tmem_base + PV_COL + wg * D, p_desc + (uint64_t)((ks * 32) >> 4),
-                      vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, ks ? 1u : 0u);
+                      vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, (k | ks) ? 1u : 0u);
           umma_commit(smem_u32(&pv_full[wg]));
           umma_commit(smem_u32(&p_empty[wg]));
           umma_commit(smem_u32(&kv_empty[stage]));
