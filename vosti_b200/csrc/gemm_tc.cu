@@ -46,7 +46,10 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ out, int tokens, int features, int k_blocks, int ld_out, int epilogue,
-               int w_tiles, unsigned* status) {
+               int w_tiles, int x_rows, unsigned* status) {
+  // x_rows: rows of the token box map_x brings per stage (the tokens rounded up to 8, at most BN):
+  // with few tokens the rest of the tile is never fetched; what those rows of shared memory
+  // hold only reaches output columns that are not stored.
   // w_tiles > 0: the weight is stored tile by tile ([k block][feature tile][128][64], w_tiles
   // feature tiles) and map_w sees it as a matrix of 64 columns; 0: row-major [features, k]
   constexpr int B_BYTES = BN * BK * 2;
@@ -90,7 +93,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int ahead = my_blocks < STAGES ? my_blocks : STAGES;
       for (int i = 0; i < ahead; ++i) {
         const uint32_t bar = smem_u32(&full_bar[i]);
-        mbar_expect_tx(bar, STAGE_BYTES);
+        mbar_expect_tx(bar, (uint32_t)(A_BYTES + x_rows * BK * 2));
         if (w_tiles) tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, 0, ((kb_begin + i) * w_tiles + (int)blockIdx.x) * BM, bar);
         else tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb_begin + i) * BK, m0, bar);
       }
@@ -102,7 +105,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t round = i / STAGES;
         if (!mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, &abort_flag, status)) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
-        mbar_expect_tx(bar, STAGE_BYTES);
+        mbar_expect_tx(bar, (uint32_t)(A_BYTES + x_rows * BK * 2));
         const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
         const int k0 = (kb_begin + i) * BK;          // multiple of 64 elements: 16-byte aligned
         if (w_tiles) tma_load_2d(a_dst, &map_w, 0, ((kb_begin + i) * w_tiles + (int)blockIdx.x) * BM, bar);
@@ -448,7 +451,7 @@ int token_tile(int tokens) { return tokens <= 32 ? 32 : tokens <= 64 ? 64 : toke
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int k_blocks, int ld_out,
-           int epilogue, int splits, int w_tiles, unsigned* status, cudaStream_t stream) {
+           int epilogue, int splits, int w_tiles, int x_rows, unsigned* status, cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -461,7 +464,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
   }
   dim3 grid((features + BM - 1) / BM, (tokens + BN - 1) / BN, splits);
   vosti_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, mw, mx, out, tokens, features, k_blocks, ld_out,
-               epilogue, w_tiles, status);
+               epilogue, w_tiles, x_rows, status);
   return 0;
 }
 
@@ -538,17 +541,18 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
     VOSTI_LAUNCH_CHECK();
   }
   const int bn = token_tile(tokens);
-  VOSTI_REQUIRE(weight_map(w, w_rows, w_cols, BM, &mw_storage) && make_map(&mx, x, tokens, k, bn),
+  const int x_rows = (tokens + 7) / 8 * 8 < bn ? (tokens + 7) / 8 * 8 : bn;   // the token box: no more rows than needed
+  VOSTI_REQUIRE(weight_map(w, w_rows, w_cols, BM, &mw_storage) && make_map(&mx, x, tokens, k, x_rows),
                 "gemm_tc: cuTensorMapEncodeTiled failed");
   void* dst = splits > 1 ? (void*)workspace : y;
   const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
   const int ld = splits > 1 ? features : ld_out;
   int rc;
   switch (bn) {
-    case 32: rc = launch<32, 5>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
-    case 64: rc = launch<64, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
-    case 128: rc = launch<128, 6>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
-    default: rc = launch<256, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, status, stream); break;
+    case 32: rc = launch<32, 5>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
+    case 64: rc = launch<64, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
+    case 128: rc = launch<128, 6>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
+    default: rc = launch<256, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
   }
   if (rc != 0) return rc;
   if (splits > 1 && !defer_reduce) {
@@ -630,9 +634,9 @@ VOSTI_API int vosti_gemm_tc_split_static(const void* x, const void* w, void* y, 
   const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
   int rc;
   switch (bn) {
-    case 32: rc = launch<32, 5>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, status, stream); break;
-    case 64: rc = launch<64, 4>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, status, stream); break;
-    default: rc = launch<128, 6>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, status, stream); break;
+    case 32: rc = launch<32, 5>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, bn, status, stream); break;
+    case 64: rc = launch<64, 4>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, bn, status, stream); break;
+    default: rc = launch<128, 6>(mw, mx, dst, tokens, features, k_blocks, features, epi, splits, 0, bn, status, stream); break;
   }
   if (rc != 0) return rc;
   if (splits > 1) {
