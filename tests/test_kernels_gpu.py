@@ -453,6 +453,32 @@ def test_prefill_attention_on_tcgen05_rows_do_not_depend_on_companions(dev, stat
     assert torch.equal(out[300:500], full[300:500]) and out[:300].abs().max() == 0 and out[500:].abs().max() == 0
 
 
+@pytest.mark.parametrize("seed", [11, 12])
+def test_attention_tensor_cores_random_shapes(dev, status, seed):
+    """Head counts, groups, head sizes, page sizes, windows and lengths drawn at random (twenty
+    launches per seed): whatever path the dispatcher picks must agree with the plain formula."""
+    import random
+    rng = random.Random(seed)
+    edge_lengths = [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 256, 257, 500, 1000, 2100]
+    for it in range(20):
+        nkv, group = rng.choice([1, 2, 3, 4, 8]), rng.choice([1, 2, 3, 4, 5, 7, 8, 16])
+        nq, d = nkv * group, rng.choice([16, 32, 48, 64, 80, 96, 128, 160, 256])
+        page, window = rng.choice([1, 4, 8, 16, 16, 16, 32, 48, 64]), rng.choice([0, 0, 0, 5, 33, 100, 700])
+        which = rng.choice(["decode", "prefill"])
+        lens_k = [rng.choice(edge_lengths) for _ in range(rng.randint(1, 5))]
+        longest_q = 4 if which == "decode" else rng.choice([1, 5, 17, 64, 100, 129, 300])
+        lens_q = [min(k, rng.randint(1, longest_q)) for k in lens_k]
+        if d * nq * sum(lens_k) > 1.5e8:
+            continue
+        case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page, seed=100 * seed + it)
+        scale = 0.5 * d ** -0.5
+        out = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, which)
+        want = reference_attention(case, scale, window)
+        what = dict(which=which, nq=nq, nkv=nkv, d=d, page=page, window=window, lens_q=lens_q, lens_k=lens_k)
+        assert torch.isfinite(out).all() and status.item() == 0, what
+        assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), (what, (out.float().cpu() - want).abs().max())
+
+
 @pytest.mark.parametrize("which", ["decode", "prefill"])
 def test_attention_tensor_cores_find_one_far_key(dev, status, which):
     nq, nkv, d, page = 8, 2, 64, 16
