@@ -115,11 +115,12 @@ def number(steps, start=0):
     return [dict(step=start + i, **s) for i, s in enumerate(steps)]
 
 
-def run_in_process(model_dir, dtype, steps, max_tokens, page_size, out_dir):
+def run_in_process(model_dir, dtype, steps, max_tokens, page_size, out_dir, batch_invariant=False):
     """Replay through the package's TraceReplayer (what bin/trace_run wraps)."""
     from vosti_b200.engine.trace import TraceReplayer
 
-    replayer = TraceReplayer(model_dir, dtype=dtype, out_dir=out_dir, max_tokens=max_tokens, page_size=page_size)
+    replayer = TraceReplayer(model_dir, dtype=dtype, out_dir=out_dir, max_tokens=max_tokens, page_size=page_size,
+                             batch_invariant=batch_invariant)
     for record in steps:
         replayer.run_line(record)
     replayer.runner.cache.check()

@@ -50,3 +50,44 @@ def test_benchmark_layer_sizes(wide_model, dtype, tmp_path):
     assert len(rows) == 4 * sum(len(t) for t in requests.values())
     worst = R.compare_with_plain(rows, requests, plain_model, dtype, alias=lambda rid: alias[rid])
     print(f"benchmark layer sizes, {dtype}: worst error {worst:.3e} of the largest logit")
+
+
+def _decode_trace(requests, prompt_len, alone=None):
+    """Prompts one by one (each whole, nothing wanted), then every request's remaining tokens
+    one per step, all requests side by side; with `alone` only that request takes part."""
+    names = [alone] if alone else list(requests)
+    steps = [{"entries": [{"id": rid, "tokens": requests[rid][:prompt_len[rid]], "want": []}], "end": []} for rid in names]
+    longest = max(len(requests[rid]) - prompt_len[rid] for rid in names)
+    for i in range(longest):
+        entries, ended = [], []
+        for rid in names:
+            at = prompt_len[rid] + i
+            if at < len(requests[rid]):
+                entries.append({"id": rid, "tokens": [requests[rid][at]], "want": [0]})
+                if at == len(requests[rid]) - 1:
+                    ended.append(rid)
+        steps.append({"entries": entries, "end": ended})
+    return R.number(steps)
+
+
+def test_decode_bits_do_not_depend_on_the_batch_when_the_segment_length_is_pinned(wide_model, tmp_path):
+    """With the decode attention's segment length fixed, a request decoded alone and decoded
+    beside seven others (other lengths, another batch size, another table width) gives the same
+    logits bit for bit: every other reduction order of a decode step depends on the weight's
+    shape only."""
+    import numpy as np
+    path, _, config = wide_model
+    vocab = config["vocab_size"]
+    lengths = {"a": (300, 24), "b": (17, 30), "c": (129, 12), "d": (64, 24), "e": (500, 24), "f": (33, 8), "g": (260, 24),
+               "h": (2, 20)}
+    requests = {rid: R.random_tokens(vocab, p + n, seed=40 + i) for i, (rid, (p, n)) in enumerate(lengths.items())}
+    prompt_len = {rid: p for rid, (p, n) in lengths.items()}
+    together = _decode_trace(requests, prompt_len)
+    alone = _decode_trace(requests, prompt_len, alone="a")
+    R.run_in_process(path, "bfloat16", together, R.max_live_tokens(together), 16, tmp_path / "together", batch_invariant=True)
+    R.run_in_process(path, "bfloat16", alone, R.max_live_tokens(alone), 16, tmp_path / "alone", batch_invariant=True)
+    rows_together = R.collect(together, tmp_path / "together", vocab)
+    rows_alone = R.collect(alone, tmp_path / "alone", vocab)
+    assert len(rows_alone) == lengths["a"][1]
+    for key, row in rows_alone.items():
+        assert np.array_equal(row, rows_together[key]), f"position {key[1]} differs between the two batches"

@@ -616,7 +616,10 @@ int ctas_per_sm(int d, int group) {
 
 // Keys per segment for a launch: items are spread over the persistent CTAs in rounds; a round
 // costs the segment's length plus a fixed share for starting and finishing an item.
+int g_pinned_segment = 0;           // vosti_set_decode_segment: 0 lets every launch choose
+
 int choose_segment_keys(int count, int nkv, int d, int group, int max_kv_len) {
+  if (g_pinned_segment > 0) return g_pinned_segment;
   if (const char* forced = getenv("VOSTI_DECODE_SEGMENT")) {
     const int keys = atoi(forced);
     if (keys >= SEGMENT_STEP && keys <= MAX_SEGMENT && keys % SEGMENT_STEP == 0) return keys;
@@ -640,6 +643,16 @@ int choose_segment_keys(int count, int nkv, int d, int group, int max_kv_len) {
 }
 
 }  // namespace
+
+// Pin the segment length for every later launch of this process (a multiple of 64 between 64
+// and 4096), or give the choice back to the launches with 0. With a pinned length a token's
+// attention is the same bits whatever else the launch holds.
+VOSTI_API int vosti_set_decode_segment(int keys) {
+  VOSTI_REQUIRE(keys == 0 || (keys >= SEGMENT_STEP && keys <= MAX_SEGMENT && keys % SEGMENT_STEP == 0),
+                "set_decode_segment: %d is not 0 or a multiple of %d up to %d", keys, SEGMENT_STEP, MAX_SEGMENT);
+  g_pinned_segment = keys;
+  return VOSTI_OK;
+}
 
 // Keys per segment, and so (max_kv_len + keys - 1) / keys partial records per token and
 // head, of a launch with `count` tokens and keys up to `max_kv_len`.

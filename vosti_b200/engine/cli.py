@@ -144,6 +144,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     parser.add_argument("--step-trace", default=_env("VOSTI_ENGINE_STEP_TRACE"))
     parser.add_argument("--no-prefix-caching", action="store_true")
     parser.add_argument("--cuda-graph", type=int, choices=[0, 1], default=int(_env("VOSTI_CUDA_GRAPH", 1)))
+    parser.add_argument("--batch-invariant", action="store_true", default=_env("VOSTI_BATCH_INVARIANT", "0") == "1",
+                        help="pin the decode attention's segment length: a row's bits do not depend on its batch")
     parser.add_argument("--random-config", help="config.json to draw a random-weights model from")
     parser.add_argument("--random-seed", type=int, default=0)
     args = parser.parse_args(argv)
@@ -168,7 +170,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                     block_size=args.block_size, max_num_seqs=max_seqs,
                     max_num_batched_tokens=args.max_batched_tokens, prefill_chunk_size=args.chunk_size,
                     enable_prefix_caching=not args.no_prefix_caching, step_trace=args.step_trace,
-                    cuda_graphs=bool(args.cuda_graph))
+                    cuda_graphs=bool(args.cuda_graph), batch_invariant=args.batch_invariant)
     print(f"MODEL_RUNTIME architecture={engine.runner.spec.architecture} dtype={args.dtype} "
           f"device={args.device}", flush=True)
 

@@ -367,6 +367,16 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, status: torch.Tensor) -> to
     return embedding(rows, x, status)
 
 
+BATCH_INVARIANT_SEGMENT = 576    # keys per decode-attention segment when the length is pinned
+
+
+def set_decode_segment(keys: int) -> None:
+    """Pin the decode attention's segment length for this process (0: every launch chooses by
+    its shape). Pinned, a token's attention does not depend on the size of its batch or on its
+    companions' lengths, at some cost in speed for large batches."""
+    _check(library().vosti_set_decode_segment(int(keys)), "set_decode_segment", kernels=0)
+
+
 def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, request_of, block_table,
                      page_size, nq, nkv, head_dim, max_kv_len, scale, window, status) -> None:
     """Single-query attention with split keys for `count` tokens (bfloat16)."""
