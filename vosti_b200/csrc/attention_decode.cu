@@ -4,27 +4,28 @@
 //
 //   A work item is one token, one kv head with the whole group of query heads that share it
 //   (they fill the MMA's 16 rows), and one segment of `segment_keys` keys counted from key 0
-//   of the request. CTA c walks over the items c, c + grid, ... Warp 0 is the producer: it
-//   resolves the block table (page ids of the next item are fetched while the current one
-//   streams) and feeds each consumer warp's ring of tile buffers by TMA, one box per 16 keys
-//   and 64 columns straight from the page (128-byte swizzle), across item boundaries. Warps
-//   1..4 are the consumers: each takes a quarter of the segment, runs the online softmax
-//   (base 2, float32) with mma.sync m16n8k16 for Q.K^T and P.V, and they are merged in warp
-//   order into an unnormalised partial (max, sum, accumulator) per query head. The CTA that
-//   finishes last for a (token, kv head) merges the segments in segment order and normalises;
-//   a CTA counts itself in one item late, so that the wait for its own stores overlaps the
-//   next item.
+//   of the request. CTA c walks over the items c, c + grid, ... Warp 0 is the producer: one
+//   item ahead of the consumers it describes the next item (token, position, segment), resolves
+//   the block table into the cache row of every 16-key tile, and fetches the query rows; what
+//   the host wrote before the step is read before the kernel waits for its predecessor. Warps
+//   1..4 are the consumers: each takes a quarter of the segment and requests its own tiles by
+//   TMA (one box per 16 keys of K and one of V straight from the page, 128-byte swizzle) into
+//   a ring of two buffers, across item boundaries; it runs the online softmax (base 2,
+//   float32) with mma.sync m16n8k16 for Q.K^T and P.V. The four are merged in warp order into
+//   an unnormalised partial (max, sum, accumulator) per query head. The CTA that finishes
+//   last for a (token, kv head) merges the segments in segment order and normalises; a CTA
+//   counts itself in one item late, so that the wait for its own stores overlaps the next item.
 //
 // The segmentation depends on the key index and on the launch (its length is chosen from the
-// number of tokens and the longest context), never on the companions' contents. Formulas as
-// in kernels/triton_kernels/fattn_paged.py:176-252: kv head = query head * nkv / nq,
+// number of tokens and the longest context, or pinned), never on the companions' contents.
+// Formulas as in kernels/triton_kernels/fattn_paged.py:176-252: kv head = query head * nkv / nq,
 // scale * log2(e), causal up to the token's own position, optional window, P rounded to
 // bfloat16 before P.V (:246), out = acc / l (0 if l = 0).
 //
-// A box of 16 keys is read whole when pages hold a multiple of 16 tokens: keys of the page
-// beyond the token's position (or before its window) are read and masked, so the cache must
-// hold finite values in every slot of a held page. Other page sizes read row by row, masked
-// keys not at all.
+// A box of 16 keys is read whole when pages hold a multiple of 16 tokens; the V rows of keys
+// beyond the token's position (or before its window) are overwritten with zeros in shared
+// memory and their scores masked, so what unused cache slots hold never reaches the
+// arithmetic. Other page sizes read row by row, masked keys not at all.
 #include <cstdlib>
 
 #include "common.cuh"
