@@ -91,3 +91,21 @@ def test_decode_bits_do_not_depend_on_the_batch_when_the_segment_length_is_pinne
     assert len(rows_alone) == lengths["a"][1]
     for key, row in rows_alone.items():
         assert np.array_equal(row, rows_together[key]), f"position {key[1]} differs between the two batches"
+
+
+def test_generation_does_not_depend_on_the_batch_with_batch_invariant(wide_model):
+    """Through the entry point: the same prompt gives the same tokens, greedy and sampled,
+    alone and among seven others, when decode is batch-invariant (CUDA graphs on). The mode
+    turns prefix reuse off: a reused prefix would turn the second prefill into a short portion,
+    and a prompt cut differently is not covered by this guarantee."""
+    from vosti_b200 import Engine
+    path, _, config = wide_model
+    vocab = config["vocab_size"]
+    prompts = [R.random_tokens(vocab, n, seed=70 + n) for n in (200, 3, 77, 130, 16, 301, 64, 9)]
+    seeds = list(range(8))
+    engine = Engine(path, dtype="bfloat16", num_blocks=400, block_size=16, max_num_seqs=8, batch_invariant=True)
+    for temperature in (0.0, 0.8):
+        together = engine.generate(prompts, max_tokens=40, temperature=temperature, seeds=seeds)
+        alone = engine.generate(prompts[:1], max_tokens=40, temperature=temperature, seeds=seeds[:1])
+        assert alone[0] == together[0], temperature
+    engine.runner.cache.check()

@@ -44,8 +44,12 @@ class Engine:
         VOSTI_MAX_SEQS, VOSTI_MAX_BATCHED_TOKENS; its page size is fixed at 64).
         `batch_invariant` pins the decode attention's segment length (a setting of the whole
         process): decode steps of up to 64 rows then give a row the same bits whatever the
-        batch around it is; the default lets every launch cut the keys to fit its shape."""
+        batch around it is; the default lets every launch cut the keys to fit its shape. It also
+        turns prompt-prefix reuse off: a reused prefix makes the rest of the prompt a short
+        portion, and a prompt cut differently is the same only up to rounding."""
         from .. import ops
+        if batch_invariant:
+            enable_prefix_caching = False
         if _is_bfloat16(dtype):
             ops.set_decode_segment(ops.BATCH_INVARIANT_SEGMENT if batch_invariant else 0)
         self.runner = ModelRunner(model, dtype=dtype, device=device, num_pages=num_blocks, page_size=block_size,
