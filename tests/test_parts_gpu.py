@@ -1,7 +1,8 @@
 """Each part alone against the plain implementation, and the framework's generality: a toy
-mixer with state of its own (defined here) is registered, built and stepped; a run order
-that names a layer twice; a layer that reads another layer's cache; a windowed layer beside
-a full one, with pages of their own."""
+mixer with state of its own, a toy feed-forward with routing and a toy position encoding
+(all defined here) are registered, built and stepped; a run order that names a layer twice;
+a layer that reads another layer's cache; a windowed layer beside a full one, with pages of
+their own."""
 import pytest
 import torch
 
@@ -9,7 +10,8 @@ import plain_qwen3 as plain
 from gpu_util import Harness
 from vosti_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
 from vosti_b200.engine.batch import StepEntry
-from vosti_b200.parts import Mixer, StateSpec, build_block, build_norm, register_part, unregister_part
+from vosti_b200.parts import (FeedForward, Mixer, PositionEncoding, StateSpec, build_block, build_norm, register_part,
+                              unregister_part)
 from vosti_b200.parts.base import build_feed_forward, build_mixer
 from vosti_b200.weights import WeightSpec, draw_tensors
 
@@ -203,6 +205,96 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
         assert (other[-1] - whole[-1]).abs().max() > 1e-4
     finally:
         unregister_part("mixer", "decay")
+
+
+# ------------------------------------------------- a toy feed-forward that routes its tokens
+class RoutedToy(FeedForward):
+    """Every token goes to the one expert its router row scores highest (scores in 32-bit);
+    an expert is one square matrix."""
+
+    def __init__(self, spec, hidden_size):
+        super().__init__(spec, hidden_size)
+        self.experts = int(spec["experts"])
+        self.router = self.w = None
+
+    def weight_specs(self):
+        specs = {"router.weight": WeightSpec((self.experts, self.hidden_size), std=1.0)}
+        for e in range(self.experts):
+            specs[f"experts.{e}.weight"] = WeightSpec((self.hidden_size, self.hidden_size), std=0.2)
+        return specs
+
+    def load(self, tensors, dtype):
+        self.router = tensors["router.weight"].float()
+        self.w = torch.stack([tensors[f"experts.{e}.weight"] for e in range(self.experts)])
+
+    def forward(self, ctx, x):
+        choice = (x.float() @ self.router.T).argmax(-1)
+        return torch.bmm(x[:, None, :], self.w[choice].transpose(1, 2))[:, 0, :]
+
+
+def test_toy_feed_forward_with_routing_registers_builds_and_steps():
+    register_part("feed_forward", "routed_toy", RoutedToy, replace=True)
+    try:
+        base = attention_layer()
+        routed = LayerSpec(mixer=base.mixer, feed_forward=PartSpec.make("routed_toy", experts=3), norm=base.norm,
+                           position=base.position)
+        spec = toy_spec([routed, attention_layer()], [RunEntry(0), RunEntry(1)])
+        tokens = torch.randint(0, 50, (40,), generator=torch.Generator().manual_seed(4)).tolist()
+        (whole, runner), (cut, _) = run_whole_and_cut(spec, tokens)
+        names = runner.model.expected_weights()
+        assert "model.layers.0.feed_forward.router.weight" in names and "model.layers.0.feed_forward.experts.2.weight" in names
+        assert torch.allclose(whole, cut, atol=1e-4, rtol=1e-4)
+        # the routing is per token: every expert gets some of these tokens
+        ffn = runner.model.blocks[0].feed_forward
+        hidden = torch.randn(64, 32, device=DEV)
+        assert len(set((hidden @ ffn.router.T).argmax(-1).tolist())) == 3
+    finally:
+        unregister_part("feed_forward", "routed_toy")
+
+
+# --------------------------------------------------------- a toy position encoding
+class SlowRotation(PositionEncoding):
+    """A rotation whose angle grows `slowdown` times slower than the position."""
+
+    def __init__(self, spec, hidden_size, head_dim):
+        super().__init__(spec, hidden_size, head_dim)
+        self.cos = self.sin = None
+
+    def setup(self, device, dtype):
+        positions = torch.arange(int(self.spec["max_positions"]), dtype=torch.float32) / float(self.spec["slowdown"])
+        self.cos, self.sin = (t.to(device).contiguous()
+                              for t in plain.rope_tables(positions, self.head_dim, self.spec["theta"]))
+
+    def rotation_tables(self):
+        return self.cos, self.sin
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_position_encoding_registers_and_reaches_the_kernels(dtype):
+    register_part("position", "slow_rotation", SlowRotation, replace=True)
+    try:
+        cfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=500.0)
+        spec = PartSpec.make("attention", num_heads=4, num_kv_heads=2, head_dim=16, head_norm_eps=1e-5, window=0,
+                             scale=0.25)
+        mixer = build_mixer(spec, 48, PartSpec.make("slow_rotation", theta=500.0, slowdown=4.0, max_positions=64))
+        assert isinstance(mixer.position, SlowRotation)
+        W = load(mixer, 6, dtype, scale=4.0)
+        harness = Harness([mixer.cache_spec()], [None], dtype, num_pages=8, page_size=8)
+        x = torch.randn(50, 48).to(dtype)
+        outs, at = [], 0
+        for size in (7, 1, 40, 2):
+            ctx = harness.context([StepEntry("s", [0] * size)])
+            outs.append(mixer.forward(ctx, x[at:at + size].to(DEV), harness.cache.layer_caches[0]).float().cpu())
+            harness.cache.trim("s")
+            at += size
+        weights = {("p." + k): v for k, v in W.items()}
+        want = plain.attention_block(x.float(), torch.arange(50) / 4.0, weights, "p.", cfg)
+        assert torch.allclose(torch.cat(outs), want, **tol(dtype))
+        plain_rope = plain.attention_block(x.float(), torch.arange(50), weights, "p.", cfg)
+        assert (plain_rope - want).abs().max() > 0.05       # the slowdown is not a no-op
+        assert harness.status.item() == 0
+    finally:
+        unregister_part("position", "slow_rotation")
 
 
 def test_run_order_may_name_a_layer_twice_and_share_a_cache():
