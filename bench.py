@@ -178,6 +178,8 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
     parser.add_argument("--no-cuda-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
+    parser.add_argument("--batch-invariant", default="off", choices=["off", "decode", "full"],
+                        help="measure with the engine's bitwise-invariance modes (the default run has them off)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -212,7 +214,8 @@ def main() -> int:
     num_blocks = max_batch * ((tokens_per_request + PAGE - 1) // PAGE) + 8
     engine = Engine(spec=spec, tensors=tensors, dtype="bfloat16", device="cuda:0", num_blocks=num_blocks,
                     block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=2 * CONTEXT,
-                    enable_prefix_caching=False, cuda_graphs=not args.no_cuda_graphs)
+                    enable_prefix_caching=False, cuda_graphs=not args.no_cuda_graphs,
+                    batch_invariant=args.batch_invariant)
     del tensors
     torch.cuda.empty_cache()
     weight_bytes = engine.runner.model.weight_bytes() - spec.vocab_size * spec.hidden_size * 2  # embedding rows: not read whole
@@ -245,7 +248,7 @@ def main() -> int:
         "impl": "ours",
         "config": {"model": "Qwen3-8B size", "layers": L, "layers_full": layers_full, "hidden": H, "heads": nq,
                    "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "page_size": PAGE, "parallelism": "1 GPU",
+                   "seq_len": CONTEXT, "page_size": PAGE, "parallelism": "1 GPU", "invariance": args.batch_invariant,
                    "l2": "inputs larger than L2 (weights read every step)", "peaks": peak_kind},
         "e2e": {"value": round(args.batch * 1e3 / main_run["wall_ms"], 1), "unit": "tok/s",
                 "h2d_bytes_per_step": main_run["h2d"], "d2h_bytes_per_step": main_run["d2h"]},

@@ -52,6 +52,43 @@ def test_benchmark_layer_sizes(wide_model, dtype, tmp_path):
     print(f"benchmark layer sizes, {dtype}: worst error {worst:.3e} of the largest logit")
 
 
+def test_bfloat16_bits_do_not_depend_on_the_cut_in_fixed_order(wide_model, tmp_path):
+    """At the benchmark layer sizes: with batch_invariant="full" a position's logits are the
+    same bits for a whole prompt (the wide product kernel, 128-row attention tiles), a decoded
+    tail (one-token steps), portions and a mixed batch."""
+    import numpy as np
+    from vosti_b200 import ops
+    path, _, config = wide_model
+    vocab = config["vocab_size"]
+    requests = {"p": R.random_tokens(vocab, 333, seed=9), "q": R.random_tokens(vocab, 150, seed=10),
+                "r": R.random_tokens(vocab, 70, seed=11)}
+    kinds = {"whole": R.whole_steps, "tail": R.tail_steps,
+             "portion": lambda reqs: R.portion_steps(reqs, sizes=(130, 2, 64, 7, 200)),
+             "mixed": lambda reqs: R.mixed_steps(reqs, seed=5)}
+    steps = []
+    for kind, make in kinds.items():
+        steps.extend(make({f"{kind}-{rid}": tokens for rid, tokens in requests.items()}))
+    steps = R.number(steps)
+    try:
+        R.run_in_process(path, "bfloat16", steps, R.max_live_tokens(steps), 16, tmp_path, batch_invariant="full")
+    finally:
+        ops.set_invariance("off")
+    rows = R.collect(steps, tmp_path, vocab)
+    for rid, tokens in requests.items():
+        for position in range(len(tokens)):
+            whole = rows[(f"whole-{rid}", position)]
+            for kind in ("tail", "portion", "mixed"):
+                assert np.array_equal(whole, rows[(f"{kind}-{rid}", position)]), \
+                    f"{rid} position {position}: {kind} differs from whole"
+    # the comparison can fail: the default mode, which cuts every launch to fit its shape, agrees
+    # across these cuts up to rounding only
+    default_steps = [s for s in steps if s["entries"][0]["id"].startswith(("whole-", "tail-"))]
+    R.run_in_process(path, "bfloat16", default_steps, R.max_live_tokens(default_steps), 16, tmp_path / "default")
+    default_rows = R.collect(default_steps, tmp_path / "default", vocab)
+    last = len(requests["p"]) - 1
+    assert not np.array_equal(default_rows[("whole-p", last)], default_rows[("tail-p", last)])
+
+
 def _decode_trace(requests, prompt_len, alone=None):
     """Prompts one by one (each whole, nothing wanted), then every request's remaining tokens
     one per step, all requests side by side; with `alone` only that request takes part."""
@@ -84,8 +121,10 @@ def test_decode_bits_do_not_depend_on_the_batch_when_the_segment_length_is_pinne
     prompt_len = {rid: p for rid, (p, n) in lengths.items()}
     together = _decode_trace(requests, prompt_len)
     alone = _decode_trace(requests, prompt_len, alone="a")
-    R.run_in_process(path, "bfloat16", together, R.max_live_tokens(together), 16, tmp_path / "together", batch_invariant=True)
-    R.run_in_process(path, "bfloat16", alone, R.max_live_tokens(alone), 16, tmp_path / "alone", batch_invariant=True)
+    R.run_in_process(path, "bfloat16", together, R.max_live_tokens(together), 16, tmp_path / "together", batch_invariant="decode")
+    R.run_in_process(path, "bfloat16", alone, R.max_live_tokens(alone), 16, tmp_path / "alone", batch_invariant="decode")
+    from vosti_b200 import ops
+    ops.set_invariance("off")
     rows_together = R.collect(together, tmp_path / "together", vocab)
     rows_alone = R.collect(alone, tmp_path / "alone", vocab)
     assert len(rows_alone) == lengths["a"][1]
@@ -95,17 +134,26 @@ def test_decode_bits_do_not_depend_on_the_batch_when_the_segment_length_is_pinne
 
 def test_generation_does_not_depend_on_the_batch_with_batch_invariant(wide_model):
     """Through the entry point: the same prompt gives the same tokens, greedy and sampled,
-    alone and among seven others, when decode is batch-invariant (CUDA graphs on). The mode
-    turns prefix reuse off: a reused prefix would turn the second prefill into a short portion,
-    and a prompt cut differently is not covered by this guarantee."""
-    from vosti_b200 import Engine
+    alone and among seven others (CUDA graphs on), with one order of arithmetic everywhere. The
+    second run finds its prompt's pages in the prefix cache and computes only the last portion:
+    in this mode that changes nothing either. The "decode" mode promises the same for decode
+    steps only, so it is run with prefix reuse off."""
+    from vosti_b200 import Engine, ops
     path, _, config = wide_model
     vocab = config["vocab_size"]
     prompts = [R.random_tokens(vocab, n, seed=70 + n) for n in (200, 3, 77, 130, 16, 301, 64, 9)]
     seeds = list(range(8))
-    engine = Engine(path, dtype="bfloat16", num_blocks=400, block_size=16, max_num_seqs=8, batch_invariant=True)
-    for temperature in (0.0, 0.8):
-        together = engine.generate(prompts, max_tokens=40, temperature=temperature, seeds=seeds)
-        alone = engine.generate(prompts[:1], max_tokens=40, temperature=temperature, seeds=seeds[:1])
-        assert alone[0] == together[0], temperature
-    engine.runner.cache.check()
+    try:
+        for mode, reuse in (("full", True), ("decode", False)):
+            engine = Engine(path, dtype="bfloat16", num_blocks=400, block_size=16, max_num_seqs=8,
+                            batch_invariant=mode, enable_prefix_caching=reuse)
+            for temperature in (0.0, 0.8):
+                together = engine.generate(prompts, max_tokens=40, temperature=temperature, seeds=seeds)
+                alone = engine.generate(prompts[:1], max_tokens=40, temperature=temperature, seeds=seeds[:1])
+                assert alone[0] == together[0], (mode, temperature)
+            if reuse:
+                assert engine.cache_stats()["requests_with_reuse"] >= 1
+            engine.runner.cache.check()
+            del engine
+    finally:
+        ops.set_invariance("off")

@@ -42,3 +42,14 @@ def test_decode_segment_length(lib):
     assert lib.vosti_attention_decode_segment_keys(1, nq, nkv, d, 2560) == 128
     # the choice is a function of the launch's shape, never of a request's place in it
     assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 2560) == lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 2560)
+
+
+def test_no_product_is_split_when_one_order_of_arithmetic_is_asked_for(lib):
+    assert lib.vosti_fixed_order() == 0
+    lib.vosti_set_fixed_order(1)
+    try:
+        for features, k in [(4096, 4096), (4096, 12288), (151936, 4096), (1000, 1000)]:
+            assert {lib.vosti_gemm_tc_splits(t, features, k) for t in (1, 8, 64, 65, 128, 129, 4096)} == {1}
+    finally:
+        lib.vosti_set_fixed_order(0)
+    assert lib.vosti_gemm_tc_splits(8, 4096, 12288) > 1

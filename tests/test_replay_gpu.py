@@ -45,6 +45,35 @@ def test_replay_all_cuts(name, dtype, model_dirs, plain_models, tmp_path):
     print(f"{name} {dtype}: worst error {worst:.3e} of the largest logit")
 
 
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_bfloat16_bits_do_not_depend_on_the_cut_in_fixed_order(name, model_dirs, tmp_path):
+    """With one order of arithmetic everywhere (batch_invariant="full") the bfloat16 logits at a
+    position are the same bits whether its request came whole, with a decoded tail, in portions
+    of changing size or mixed with other requests on reused pages."""
+    import numpy as np
+    from vosti_b200 import ops
+    path, config, page = model_dirs[name]
+    requests = _requests(name, config)
+    kinds = {"whole": R.whole_steps, "tail": R.tail_steps, "portion": R.portion_steps,
+             "mixed": lambda reqs: R.mixed_steps(reqs, seed=3)}
+    steps = []
+    for kind, make in kinds.items():
+        steps.extend(make({f"{kind}-{rid}": tokens for rid, tokens in requests.items()}))
+    steps = R.number(steps)
+    try:
+        R.run_in_process(path, "bfloat16", steps, R.max_live_tokens(steps), page, tmp_path, batch_invariant="full")
+    finally:
+        ops.set_invariance("off")
+    rows = R.collect(steps, tmp_path, config["vocab_size"])
+    assert len(rows) == 4 * sum(len(t) for t in requests.values())
+    for rid, tokens in requests.items():
+        for position in range(len(tokens)):
+            whole = rows[(f"whole-{rid}", position)]
+            for kind in ("tail", "portion", "mixed"):
+                assert np.array_equal(whole, rows[(f"{kind}-{rid}", position)]), \
+                    f"{rid} position {position}: {kind} differs from whole"
+
+
 def test_trace_run_binary(model_dirs, plain_models, tmp_path):
     """The program itself: line protocol, files, exit code; pages used again."""
     path, config, page = model_dirs["b"]

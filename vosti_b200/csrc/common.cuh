@@ -30,6 +30,7 @@ enum VostiDeviceFault : unsigned {
 };
 
 void vosti_set_error(const char* fmt, ...);
+extern int g_vosti_fixed_order;   // errors.cu: one order of arithmetic however the work is cut
 
 #define VOSTI_REQUIRE(cond, ...)            \
   do {                                      \

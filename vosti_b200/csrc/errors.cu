@@ -39,3 +39,11 @@ int vosti_pdl_enabled() {
 }
 
 VOSTI_API void vosti_set_pdl(int enabled) { g_pdl = enabled ? 1 : 0; }
+
+// One order of arithmetic for every way of cutting the work (vosti_set_fixed_order): a product
+// never splits its K range, and no kernel is chosen by the number of tokens in the launch, so a
+// token's values are the same bits whether it comes alone, in a batch or inside a long portion.
+int g_vosti_fixed_order = 0;
+
+VOSTI_API void vosti_set_fixed_order(int enabled) { g_vosti_fixed_order = enabled ? 1 : 0; }
+VOSTI_API int vosti_fixed_order() { return g_vosti_fixed_order; }

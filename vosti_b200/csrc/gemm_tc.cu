@@ -474,12 +474,14 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
 VOSTI_API int vosti_gemm_tc_supported(int features, int k) { return features >= 1 && k >= BK && k % 8 == 0; }
 
 // How many K splits a product of these sizes uses (a function of the sizes only; the
-// sum over splits is taken in split order). More than one split needs a float32 workspace
+// sum over splits is taken in split order). With one order of arithmetic asked for
+// (vosti_set_fixed_order) no product is split: the unsplit kernels give a token the same bits
+// whichever of them runs, the split ones do not. More than one split needs a float32 workspace
 // of splits * tokens * features elements.
 VOSTI_API int vosti_gemm_tc_splits(int tokens, int features, int k) {
   const int k_blocks = (k + BK - 1) / BK;
   const int tiles = ((features + BM - 1) / BM) * ((tokens + token_tile(tokens) - 1) / token_tile(tokens));
-  if (tokens > 128) return 1;
+  if (tokens > 128 || g_vosti_fixed_order) return 1;
   int splits;
   if (token_tile(tokens) <= 64) {
     // two CTAs of this tile size fit an SM: fill both slots of every SM, never a second round

@@ -263,7 +263,7 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
   VOSTI_REQUIRE(cos_table == nullptr || positions != nullptr, "qkv_post: rotation needs positions");
   if (tokens == 0) return VOSTI_OK;
   const int heads = nq + 2 * nkv;
-  if (!is_f32 && partial == nullptr && tokens >= 64 && (d == 64 || d == 128 || d == 256)) {
+  if (!is_f32 && partial == nullptr && tokens >= 64 && !g_vosti_fixed_order && (d == 64 || d == 128 || d == 256)) {
     // many tokens: a block per token, vector accesses
 #define LAUNCH_QKV_POST_WIDE(VE)                                                                                   \
     vosti_launch(qkv_post_wide_kernel<VE>, dim3(tokens), dim3(256), 0, stream, (const bf16*)qkv, (bf16*)q_out,     \

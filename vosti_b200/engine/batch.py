@@ -17,7 +17,7 @@ import ctypes
 import numpy as np
 import torch
 
-from .. import host
+from .. import host, ops
 
 
 @dataclass
@@ -149,7 +149,9 @@ def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], s
     extras = dict(extras or {})
     single = T == B                    # a decode-only step: one token per request
     short_tokens, long_rows, cursor = [], [], 0
-    if single:
+    if ops.FIXED_ORDER:
+        long_rows = range(B)           # every token's attention on the portion kernel
+    elif single:
         short_tokens = range(B)
     else:
         for i, n in enumerate(q_lens):

@@ -144,8 +144,11 @@ def main(argv: Optional[List[str]] = None) -> int:
     parser.add_argument("--step-trace", default=_env("VOSTI_ENGINE_STEP_TRACE"))
     parser.add_argument("--no-prefix-caching", action="store_true")
     parser.add_argument("--cuda-graph", type=int, choices=[0, 1], default=int(_env("VOSTI_CUDA_GRAPH", 1)))
-    parser.add_argument("--batch-invariant", action="store_true", default=_env("VOSTI_BATCH_INVARIANT", "0") == "1",
-                        help="pin the decode attention's segment length: a row's bits do not depend on its batch")
+    parser.add_argument("--batch-invariant", nargs="?", const="full", choices=["off", "decode", "full"],
+                        default={"0": "off", "1": "full"}.get(_env("VOSTI_BATCH_INVARIANT", "off"),
+                                                              _env("VOSTI_BATCH_INVARIANT", "off")),
+                        help="full: a token's bits do not depend on how the work is cut into steps and batches "
+                             "(slower decoding); decode: decode steps of up to 64 rows do not depend on the batch")
     parser.add_argument("--random-config", help="config.json to draw a random-weights model from")
     parser.add_argument("--random-seed", type=int, default=0)
     args = parser.parse_args(argv)

@@ -38,20 +38,19 @@ class Engine:
                  num_blocks: int = 32, block_size: int = 16, max_num_seqs: int = 1,
                  max_num_batched_tokens: int = 4096, prefill_chunk_size: int = 0,
                  enable_prefix_caching: bool = True, step_trace: Optional[str] = None,
-                 cuda_graphs: bool = True, batch_invariant: bool = False, spec=None, tensors=None):
+                 cuda_graphs: bool = True, batch_invariant=False, spec=None, tensors=None):
         """`num_blocks` pages of `block_size` tokens; `max_num_seqs` rows and
         `max_num_batched_tokens` tokens per step at most (the reference's VOSTI_NUM_BLOCKS,
         VOSTI_MAX_SEQS, VOSTI_MAX_BATCHED_TOKENS; its page size is fixed at 64).
-        `batch_invariant` pins the decode attention's segment length (a setting of the whole
-        process): decode steps of up to 64 rows then give a row the same bits whatever the
-        batch around it is; the default lets every launch cut the keys to fit its shape. It also
-        turns prompt-prefix reuse off: a reused prefix makes the rest of the prompt a short
-        portion, and a prompt cut differently is the same only up to rounding."""
+        `batch_invariant` (a setting of the whole process, bfloat16 only; ops.set_invariance):
+        True or "full" computes every token in one order of arithmetic, so that its bits do not
+        depend on how prompts are cut into portions, on reused prefixes or on the batch around
+        it, at the price of slower decoding; "decode" only pins the decode attention's segment
+        length, which makes decode steps of up to 64 rows independent of the batch and costs
+        little; the default lets every launch cut its work to fit its shape."""
         from .. import ops
-        if batch_invariant:
-            enable_prefix_caching = False
         if _is_bfloat16(dtype):
-            ops.set_decode_segment(ops.BATCH_INVARIANT_SEGMENT if batch_invariant else 0)
+            ops.set_invariance(batch_invariant)
         self.runner = ModelRunner(model, dtype=dtype, device=device, num_pages=num_blocks, page_size=block_size,
                                   max_requests=max_num_seqs, prefix_reuse=enable_prefix_caching, spec=spec,
                                   tensors=tensors)

@@ -22,10 +22,10 @@ MAX_LIVE = 8
 
 class TraceReplayer:
     def __init__(self, model_dir, *, dtype: str, out_dir, max_tokens: int, page_size: int = 16,
-                 device: str = "cuda:0", batch_invariant: bool = False):
+                 device: str = "cuda:0", batch_invariant=False):
         if dtype == "bfloat16":
             from .. import ops
-            ops.set_decode_segment(ops.BATCH_INVARIANT_SEGMENT if batch_invariant else 0)
+            ops.set_invariance(batch_invariant)
         self.out_dir = Path(out_dir)
         self.out_dir.mkdir(parents=True, exist_ok=True)
         num_pages = (max_tokens + page_size - 1) // page_size

@@ -367,6 +367,20 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, status: torch.Tensor) -> to
     return embedding(rows, x, status)
 
 
+FIXED_ORDER = False              # set_fixed_order: one order of arithmetic however the work is cut
+
+
+def set_fixed_order(enabled: bool) -> None:
+    """Make a token's bfloat16 values the same bits however the work is cut into steps and
+    batches, for this process: products never split their K range, no kernel is chosen by the
+    number of tokens in the launch, and every token's attention runs on the portion kernel
+    (whose rows are independent of one another and whose key tiles start at key 0). Decoding
+    is slower for it: fewer CTAs stream the weights, and a lone token fills one row of a tile."""
+    global FIXED_ORDER
+    library().vosti_set_fixed_order(1 if enabled else 0)
+    FIXED_ORDER = bool(enabled)
+
+
 BATCH_INVARIANT_SEGMENT = 576    # keys per decode-attention segment when the length is pinned
 
 
@@ -375,6 +389,22 @@ def set_decode_segment(keys: int) -> None:
     its shape). Pinned, a token's attention does not depend on the size of its batch or on its
     companions' lengths, at some cost in speed for large batches."""
     _check(library().vosti_set_decode_segment(int(keys)), "set_decode_segment", kernels=0)
+
+
+def set_invariance(mode) -> str:
+    """Choose what a token's bfloat16 bits may depend on, for this process.
+    False, None, "off": every launch picks the fastest cut for its shape.
+    "decode": the decode attention's segment length is pinned, so a decode step of up to 64
+    rows gives a row the same bits whatever the batch around it is; prompts cut differently
+    agree up to rounding only.
+    True, "full": one order of arithmetic everywhere (set_fixed_order): the same bits however
+    the tokens are cut into steps and whatever else is in the batch."""
+    name = {False: "off", None: "off", True: "full", "0": "off", "1": "full", "": "off"}.get(mode, mode)
+    if name not in ("off", "decode", "full"):
+        raise ValueError(f"batch invariance is 'off', 'decode' or 'full', not {mode!r}")
+    set_fixed_order(name == "full")
+    set_decode_segment(BATCH_INVARIANT_SEGMENT if name == "decode" else 0)
+    return name
 
 
 def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, request_of, block_table,
