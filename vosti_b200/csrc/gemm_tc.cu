@@ -137,7 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // epilogue: this warp may read the 32 accumulator lanes of its quarter only
     const int quarter = warp & 3;
     pdl_wait();                                       // the output may still be read by the kernel before
-    bool ok = my_blocks > 0 ? mbar_wait(smem_u32(&accum_bar), 0, &abort_flag, status) : true;
+    bool ok = my_blocks > 0 ? mbar_wait_warp(smem_u32(&accum_bar), 0, &abort_flag, status) : true;
     tc_fence_after();
     const int feature = m0 + quarter * 32 + lane;
     if (ok) {
@@ -301,7 +301,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * WIDE_BN;
       const uint32_t as = local & 1;
-      ok = mbar_wait(smem_u32(&acc_full[as]), (local >> 1) & 1, &abort_flag, status);
+      ok = mbar_wait_warp(smem_u32(&acc_full[as]), (local >> 1) & 1, &abort_flag, status);
       if (!ok) break;
       tc_fence_after();
       const int token = m0 + quarter * 32 + lane;

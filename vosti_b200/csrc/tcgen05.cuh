@@ -36,6 +36,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return true;
 }
+// The same wait for a whole warp (all 32 lanes must call it): lane 0 polls, the others sleep at
+// the shuffle, and every lane then observes the completed phase itself. Thirty-two lanes that
+// poll one barrier for a long time (an epilogue warp during the main loop) keep the
+// shared-memory pipe busy and slow the barrier traffic of the threads that feed the tensor core.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned* status) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  return ok && mbar_wait(bar, parity, abort_flag, status);
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols));
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
