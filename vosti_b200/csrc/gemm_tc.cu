@@ -42,18 +42,24 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
 __device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
 
 // ------------------------------------------------------------------ the kernel
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KPS>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ out, int tokens, int features, int k_blocks, int ld_out, int epilogue,
                int w_tiles, int x_rows, unsigned* status) {
-  // x_rows: rows of the token box map_x brings per stage (the tokens rounded up to 8, at most BN):
+  // x_rows: rows of the token box map_x brings per k-block (the tokens rounded up to 8, at most BN):
   // with few tokens the rest of the tile is never fetched; what those rows of shared memory
   // hold only reaches output columns that are not stored.
   // w_tiles > 0: the weight is stored tile by tile ([k block][feature tile][128][64], w_tiles
   // feature tiles) and map_w sees it as a matrix of 64 columns; 0: row-major [features, k]
+  // KPS: k-blocks per stage of the ring. The lane that issues the MMAs pays about 200 cycles for
+  // the barrier wait that follows its own commit (even when the stage landed long before), 85
+  // for the commit and 95 for the loop, beside 56 per MMA: with one k-block per stage that is
+  // 610 cycles per k-block, with two 416. Launches with so few CTAs that each has an SM (and its
+  // shared memory) to itself, whose time is k-blocks x that cost, take two k-blocks per stage.
   constexpr int B_BYTES = BN * BK * 2;
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int BLOCK_BYTES = A_BYTES + B_BYTES;
+  constexpr int STAGE_BYTES = KPS * BLOCK_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle pattern
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -69,6 +75,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kb_begin = (int)((long long)k_blocks * split / splits);
   const int kb_end = (int)((long long)k_blocks * (split + 1) / splits);
   const int my_blocks = kb_end - kb_begin;
+  const int my_stages = (my_blocks + KPS - 1) / KPS;       // the last one may hold fewer k-blocks
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -88,46 +95,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
+      // k-blocks of stage i: i * KPS .. i * KPS + held(i) - 1 (counted from kb_begin)
+      auto held = [&](int i) { return my_blocks - i * KPS < KPS ? my_blocks - i * KPS : KPS; };
+      auto load_w = [&](int i, int s) {
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        mbar_expect_tx(bar, (uint32_t)(held(i) * (A_BYTES + x_rows * BK * 2)));
+        for (int q = 0; q < held(i); ++q) {
+          const int kb = kb_begin + i * KPS + q;           // k offsets are multiples of 64 elements: 16-byte aligned
+          const uint32_t dst = smem_u32(smem + s * STAGE_BYTES + q * BLOCK_BYTES);
+          if (w_tiles) tma_load_2d(dst, &map_w, 0, (kb * w_tiles + (int)blockIdx.x) * BM, bar);
+          else tma_load_2d(dst, &map_w, kb * BK, m0, bar);
+        }
+      };
+      auto load_x = [&](int i, int s) {
+        for (int q = 0; q < held(i); ++q)
+          tma_load_2d(smem_u32(smem + s * STAGE_BYTES + q * BLOCK_BYTES) + A_BYTES, &map_x, (kb_begin + i * KPS + q) * BK, n0,
+                      smem_u32(&full_bar[s]));
+      };
       // The weight tiles of the first stages do not depend on the kernel before this one:
       // they are requested at once, the token tiles after that kernel has completed.
-      const int ahead = my_blocks < STAGES ? my_blocks : STAGES;
-      for (int i = 0; i < ahead; ++i) {
-        const uint32_t bar = smem_u32(&full_bar[i]);
-        mbar_expect_tx(bar, (uint32_t)(A_BYTES + x_rows * BK * 2));
-        if (w_tiles) tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, 0, ((kb_begin + i) * w_tiles + (int)blockIdx.x) * BM, bar);
-        else tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb_begin + i) * BK, m0, bar);
-      }
+      const int ahead = my_stages < STAGES ? my_stages : STAGES;
+      for (int i = 0; i < ahead; ++i) load_w(i, i);
       pdl_wait();
-      for (int i = 0; i < ahead; ++i)
-        tma_load_2d(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, &map_x, (kb_begin + i) * BK, n0, smem_u32(&full_bar[i]));
-      for (int i = ahead; i < my_blocks; ++i) {
+      for (int i = 0; i < ahead; ++i) load_x(i, i);
+      for (int i = ahead; i < my_stages; ++i) {
         const int s = i % STAGES;
         const uint32_t round = i / STAGES;
         if (!mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, &abort_flag, status)) break;
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        mbar_expect_tx(bar, (uint32_t)(A_BYTES + x_rows * BK * 2));
-        const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
-        const int k0 = (kb_begin + i) * BK;          // multiple of 64 elements: 16-byte aligned
-        if (w_tiles) tma_load_2d(a_dst, &map_w, 0, ((kb_begin + i) * w_tiles + (int)blockIdx.x) * BM, bar);
-        else tma_load_2d(a_dst, &map_w, k0, m0, bar);
-        tma_load_2d(a_dst + A_BYTES, &map_x, k0, n0, bar);
+        load_w(i, s);
+        load_x(i, s);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
-      for (int i = 0; i < my_blocks && ok; ++i) {
+      for (int i = 0; i < my_stages && ok; ++i) {
         const int s = i % STAGES;
         ok = mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1, &abort_flag, status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+        const int held = my_blocks - i * KPS < KPS ? my_blocks - i * KPS : KPS;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // 16 elements further along K: 32 bytes, 2 in the descriptor's 16-byte units
-          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        for (int q = 0; q < KPS; ++q) {
+          if (q < held) {
+            const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES + q * BLOCK_BYTES);
+            const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // 16 elements further along K: 32 bytes, 2 in the descriptor's 16-byte units
+              umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || q > 0 || k > 0) ? 1u : 0u);
+            }
+          }
         }
         umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these MMAs have read it
       }
@@ -449,13 +468,14 @@ bool weight_map(const void* w, int rows, int k, int box_rows, CUtensorMap* out) 
 
 int token_tile(int tokens) { return tokens <= 32 ? 32 : tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256; }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KPS = 1>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int k_blocks, int ld_out,
            int epilogue, int splits, int w_tiles, int x_rows, unsigned* status, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024;
+  constexpr size_t smem = (size_t)STAGES * KPS * (A_BYTES + BN * BK * 2) + 1024;
+  static_assert(smem <= 232448, "the ring does not fit an SM's shared memory");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, KPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       vosti_set_error("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return (int)e;
@@ -463,7 +483,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
     configured = true;
   }
   dim3 grid((features + BM - 1) / BM, (tokens + BN - 1) / BN, splits);
-  vosti_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), smem, stream, mw, mx, out, tokens, features, k_blocks, ld_out,
+  vosti_launch(gemm_tc_kernel<BN, STAGES, KPS>, grid, dim3(THREADS), smem, stream, mw, mx, out, tokens, features, k_blocks, ld_out,
                epilogue, w_tiles, x_rows, status);
   return 0;
 }
@@ -549,13 +569,18 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
   void* dst = splits > 1 ? (void*)workspace : y;
   const int epi = splits > 1 ? EPI_PARTIAL : epilogue;
   const int ld = splits > 1 ? features : ld_out;
+  // no more CTAs than SMs: each has an SM's shared memory to itself and takes two k-blocks per stage
+  const int64_t ctas = (int64_t)((features + BM - 1) / BM) * ((tokens + bn - 1) / bn) * splits;
+  const bool lone = ctas <= 148;
+#define VOSTI_GEMM_ARGS *mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream
   int rc;
   switch (bn) {
-    case 32: rc = launch<32, 5>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
-    case 64: rc = launch<64, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
-    case 128: rc = launch<128, 6>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
-    default: rc = launch<256, 4>(*mw, mx, dst, tokens, features, k_blocks, ld, epi, splits, w_tiles, x_rows, status, stream); break;
+    case 32: rc = lone ? launch<32, 5, 2>(VOSTI_GEMM_ARGS) : launch<32, 5>(VOSTI_GEMM_ARGS); break;
+    case 64: rc = lone ? launch<64, 4, 2>(VOSTI_GEMM_ARGS) : launch<64, 4>(VOSTI_GEMM_ARGS); break;
+    case 128: rc = lone ? launch<128, 3, 2>(VOSTI_GEMM_ARGS) : launch<128, 6>(VOSTI_GEMM_ARGS); break;
+    default: rc = launch<256, 4>(VOSTI_GEMM_ARGS); break;
   }
+#undef VOSTI_GEMM_ARGS
   if (rc != 0) return rc;
   if (splits > 1 && !defer_reduce) {
     const int64_t n = (int64_t)tokens * features;
