@@ -149,8 +149,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const bool masked = key0 + KT - 1 > pos || key0 < kstart;
       // the maximum is exact in any order: four independent chains, scaled once at the end
       // (scale_log2 > 0, so max(s * scale) = max(s) * scale bit for bit)
+      // A row of the tile that holds no token (a lone decode token fills 1 to 16 of the 128 rows)
+      // takes no part in the arithmetic: its maximum stays -inf, nothing is written to its row of
+      // P, and what the product makes of that row's stale bytes is never stored.
       float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (masked) {
+      if (!valid) {
+      } else if (masked) {
 #pragma unroll
         for (int i = 0; i < KT; ++i)
           if (key0 + i <= pos && key0 + i >= kstart) part_max[i & 3] = fmaxf(part_max[i & 3], __uint_as_float(raw[i >> 5][i & 31]));
@@ -190,7 +194,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       // ---- P (rounded to bfloat16) into shared memory as the A operand of the second MMA
       float part_sum[4] = {0.f, 0.f, 0.f, 0.f};         // four chains, combined in a fixed order
-      if (masked) {
+      if (!valid) {
+      } else if (masked) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float p[8];
