@@ -283,7 +283,8 @@ def test_sampling(dev):
 
 # ---------------------------------------------------------------- tensor-core product
 @pytest.mark.parametrize("tokens", [1, 7, 33, 64, 100, 129, 300, 1100])
-@pytest.mark.parametrize("features,k", [(64, 64), (200, 80), (331, 96), (4096, 1000), (1536, 4096), (152, 12288)])
+@pytest.mark.parametrize("features,k", [(64, 64), (200, 80), (331, 96), (200, 320), (72, 448), (4096, 1000), (1536, 4096),
+                                        (152, 12288)])
 def test_gemm_tc(dev, status, tokens, features, k):
     from vosti_b200 import ops
     assert ops.gemm_tc_supported(features, k)
@@ -322,7 +323,7 @@ def test_gemm_tc_fused_silu_mul(dev, status, tokens, inter, k):
 
 
 @pytest.mark.parametrize("tokens", [5, 70, 300])
-@pytest.mark.parametrize("features,k", [(1000, 1000), (384, 64), (4096 + 128, 4096), (96, 200)])
+@pytest.mark.parametrize("features,k", [(1000, 1000), (384, 64), (4096 + 128, 4096), (96, 200), (130, 320)])
 def test_gemm_tc_tile_packed_weight_gives_the_same_bits(dev, status, tokens, features, k):
     """A weight stored tile by tile (zero-padded to whole tiles) multiplies to the same bits
     as the row-major weight, in both kernels, with split K and with the fused SiLU epilogue."""
