@@ -31,7 +31,7 @@ def load_model(model_dir, dtype=torch.float32):
 
 def _round(x, round_to):
     """Optional emulation of the reference's rounding points: it stores every
-    primitive's output in bf16 (SURVEY of the kernels: each kernel ends in
+    primitive's output in bf16 (each of its kernels ends in
     `.to(o.dtype.element_ty)`, e.g. kernels/triton_kernels/rmsnorm.py:93)."""
     return x if round_to is None else x.to(round_to).to(x.dtype)
 
