@@ -114,6 +114,7 @@ def decode_run(engine, batch, steps, warmup, seed, sample_clocks=False):
     while any(not r.is_decoding() for r in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()
     assert len(engine.scheduler.running) == batch
+    engine.step()                          # with async scheduling the first decode step's tokens come a call later
     for _ in range(warmup):
         assert len(engine.step()) == batch
     sampler = ClockSampler() if sample_clocks else None
@@ -143,6 +144,7 @@ def decode_run(engine, batch, steps, warmup, seed, sample_clocks=False):
     context_mid = context_start + steps // 2
     for i in range(batch):
         engine.abort(first + i)
+    engine.drain()
     assert not engine.has_unfinished()
     return {"device_ms": device_ms, "wall_ms": wall_ms, "launches": launches, "clocks": clocks,
             "h2d": h2d, "d2h": d2h, "context": context_mid}
@@ -162,6 +164,7 @@ def prefill_run(engine, repeats, seed):
         emitted = engine.step()
         end.record()
         torch.cuda.synchronize()
+        emitted.update(engine.drain())
         assert rid in emitted and not engine.has_unfinished()
         times.append(begin.elapsed_time(end))
     return min(times[1:]) if len(times) > 1 else times[0]
@@ -178,6 +181,8 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
     parser.add_argument("--no-cuda-graphs", action="store_true", help="launch decode kernels one by one (for profilers)")
+    parser.add_argument("--sync-scheduling", action="store_true",
+                        help="read every step's tokens before the next step is planned (default: the engine's async scheduling)")
     parser.add_argument("--batch-invariant", default="off", choices=["off", "decode", "full"],
                         help="measure with the engine's bitwise-invariance modes (the default run has them off)")
     args = parser.parse_args()
@@ -215,7 +220,7 @@ def main() -> int:
     engine = Engine(spec=spec, tensors=tensors, dtype="bfloat16", device="cuda:0", num_blocks=num_blocks,
                     block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=2 * CONTEXT,
                     enable_prefix_caching=False, cuda_graphs=not args.no_cuda_graphs,
-                    batch_invariant=args.batch_invariant)
+                    batch_invariant=args.batch_invariant, async_scheduling=not args.sync_scheduling)
     del tensors
     torch.cuda.empty_cache()
     weight_bytes = engine.runner.model.weight_bytes() - spec.vocab_size * spec.hidden_size * 2  # embedding rows: not read whole
@@ -249,6 +254,7 @@ def main() -> int:
         "config": {"model": "Qwen3-8B size", "layers": L, "layers_full": layers_full, "hidden": H, "heads": nq,
                    "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V, "global_batch": args.batch,
                    "seq_len": CONTEXT, "page_size": PAGE, "parallelism": "1 GPU", "invariance": args.batch_invariant,
+                   "scheduling": "sync" if args.sync_scheduling else "async",
                    "l2": "inputs larger than L2 (weights read every step)", "peaks": peak_kind},
         "e2e": {"value": round(args.batch * 1e3 / main_run["wall_ms"], 1), "unit": "tok/s",
                 "h2d_bytes_per_step": main_run["h2d"], "d2h_bytes_per_step": main_run["d2h"]},

@@ -182,3 +182,53 @@ def test_cuda_graphs_change_nothing(model_dirs, dtype):
         if graphs:
             assert engine.graphs.captures >= 2 and engine.graphs.replays > 60
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_async_scheduling_generates_the_same(model_dirs, plain_models, dtype):
+    """Launching a step before the last one's tokens are read changes no token: prompts in
+    portions beside decodes, temperature and greedy rows, staggered arrivals, CUDA graphs."""
+    path, config, page = model_dirs["c"]
+    from vosti_b200 import Engine
+    prompts = [R.random_tokens(config["vocab_size"], n, seed=300 + n) for n in (3, 50, 17, 90, 33)]
+    seeds = [4, 5, 6, 7, 8]
+    outs = []
+    for ahead in (False, True):
+        engine = Engine(path, dtype=dtype, num_blocks=256, block_size=page, max_num_seqs=3, max_num_batched_tokens=48,
+                        async_scheduling=ahead)
+        a = engine.generate(prompts, max_tokens=50, temperature=0.7, seeds=seeds, arrival_steps=[0, 0, 3, 9, 30])
+        b = engine.generate(prompts[:2], max_tokens=30)
+        outs.append((a, b))
+        assert not engine.has_unfinished()
+        engine.runner.cache.check()
+        if ahead:
+            assert engine.graphs.replays > 20
+    assert outs[0] == outs[1]
+    for prompt, out in zip(prompts[:2], outs[1][1]):
+        check_tokens(plain_models["c"], prompt, out, dtype)
+
+
+def test_async_scheduling_with_eos_and_too_few_pages(model_dirs, plain_models):
+    """The token that ends a request arrives after the next step is launched: the row the
+    request still has there is dropped, and its pages come back. With so few pages that
+    requests are preempted while their newest token is still on the device only."""
+    from vosti_b200 import Engine
+    path, config, page = model_dirs["b"]
+    prompts = [R.random_tokens(config["vocab_size"], n, seed=70 + n) for n in (30, 41, 25, 38)]
+    roomy = Engine(path, dtype="float32", num_blocks=256, block_size=page, max_num_seqs=4)
+    free_run = roomy.generate(prompts, max_tokens=40)
+    stops = [free_run[0][7], free_run[2][20]]
+    want = roomy.generate(prompts, max_tokens=40, eos_token_ids=stops)
+    assert any(len(out) < 40 for out in want)
+    for blocks, reuse, eos, expected in ((256, True, stops, want), (40, False, stops, want), (26, False, None, free_run)):
+        ahead = Engine(path, dtype="float32", num_blocks=blocks, block_size=page, max_num_seqs=4,
+                       enable_prefix_caching=reuse, async_scheduling=True)
+        got = ahead.generate(prompts, max_tokens=40, eos_token_ids=eos)
+        assert got == expected, blocks
+        assert not ahead.has_unfinished()
+        ahead.runner.cache.check()
+        assert reuse or ahead.runner.cache.available_pages() == blocks
+        if blocks == 26:
+            assert ahead.scheduler.preemptions > 0
+    for prompt, out in zip(prompts, want):
+        check_tokens(plain_models["b"], prompt, out, "float32")

@@ -233,3 +233,68 @@ def test_abort_gives_everything_back():
     while sched.has_unfinished():
         run_step(cache, sched)
     assert cache.available_pages() == 16
+
+
+def _token(rid, index):
+    """What the "model" samples: a function of the request and the place only."""
+    return (rid * 31 + index * 7) % 11
+
+
+def _workload(rng, cache):
+    arrivals = []
+    for i in range(10):
+        prompt = [rng.randrange(5) for _ in range(rng.randrange(1, 14))]
+        max_tokens = rng.randrange(1, 9)
+        eos = (rng.randrange(11),) if i % 2 else ()
+        if cache.pages_for(len(prompt) + max_tokens) <= cache.num_pages:
+            arrivals.append((rng.randrange(0, 20), i, prompt, max_tokens, eos))
+    return arrivals
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_commit_in_two_halves_gives_the_tokens_of_the_plain_commit(seed):
+    """commit_ahead, the next plan, then resolve (what the engine does when it launches a step
+    before it has read the last one's tokens) give every request the tokens and the finish
+    reason the plain commit gives: EOS, length limits, prefix reuse, and so few pages that
+    requests are preempted while their newest token is still pending. No page is lost."""
+    outcomes = []
+    for ahead in (False, True):
+        rng = random.Random(seed)
+        cache, sched = make(num_pages=rng.choice([6, 10, 24]), page_size=rng.choice([2, 4, 8]),
+                            max_num_seqs=rng.choice([1, 2, 4]), budget=rng.choice([8, 16, 64]),
+                            chunk=rng.choice([0, 8]), reuse=bool(seed % 2))
+        arrivals = _workload(rng, cache)
+        ids = [a[1] for a in arrivals]
+        sample = lambda plan: [_token(r.request.request_id, len(r.request.generated) - (1 if ahead else 0))
+                               if r.sample else None for r in plan.rows]
+        before, step = None, 0
+        while arrivals or sched.has_unfinished() or before is not None:
+            for item in [a for a in arrivals if a[0] <= step]:
+                arrivals.remove(item)
+                request = Request(item[1], item[2], item[3], item[4], ignore_eos=not item[4])
+                assert sched.add_request(request) is AdmissionStatus.ACCEPTED
+            if not ahead:
+                if sched.has_unfinished():
+                    plan = sched.plan()
+                    for row in plan.rows:
+                        cache.extend(row.request.request_id, row.count)
+                    sched.commit(plan, sample(plan))
+            else:
+                if before is not None:
+                    sched.commit_ahead(before)
+                plan = sched.plan() if sched.has_unfinished() else None
+                if plan is not None:
+                    for row in plan.rows:
+                        assert row.start == cache.length(row.request.request_id)
+                        cache.extend(row.request.request_id, row.count)
+                        tokens = row.request.token_range(row.start, row.count)
+                        assert Scheduler.PENDING not in tokens[:-1]          # only the newest token can be pending
+                if before is not None:
+                    sched.resolve(before, sample(before))
+                before = plan if plan is not None and plan.rows else None
+            cache.check()
+            step += 1
+            assert step < 4000
+        assert cache.available_pages() == cache.num_pages and not cache.live
+        outcomes.append({rid: (sched.finished[rid].generated, sched.finished[rid].finish_reason) for rid in ids})
+    assert outcomes[0] == outcomes[1]

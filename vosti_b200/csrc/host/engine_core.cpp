@@ -558,6 +558,78 @@ class SchedulerCore {
     return VH_OK;
   }
 
+  // ---- the same commit in two halves, for an engine that launches step n + 1 before it has read
+  // step n's tokens. commit_ahead applies everything that does not need the token values: the
+  // computed counts, page publication (it only needs tokens that were inputs of the step), and
+  // the end by length, which is known from the count; a sampling row gets the token PENDING.
+  // resolve, called once the tokens are on the host and before the next commit_ahead, writes
+  // them in and applies the end by EOS. A request whose newest token is pending is planned like
+  // any other (the engine feeds that token from the device); if resolve ends it, a row it
+  // already has in the launched step is ignored by the commit_ahead and resolve of that step.
+  static constexpr int32_t PENDING = -1;
+  static constexpr int32_t IGNORED = -1;                 // in finished_out: the row's request had ended before
+  int commit_ahead(int32_t* finished_out) {
+    const int count = (int)last_plan.size();
+    for (int i = 0; i < count; ++i) {
+      const PlanRow& row = last_plan[i];
+      finished_out[i] = IGNORED;
+      auto found = requests.find(row.id);
+      if (found == requests.end() || found->second->finish_reason != NOT_FINISHED) continue;
+      auto request = found->second;
+      Residency* res = cache->find(row.id);
+      if (res == nullptr) continue;
+      request->computed += row.count;
+      const int rc = cache->publish(*res, request->tokens.data(), request->computed);
+      if (rc < 0) return rc;
+      finished_out[i] = NOT_FINISHED;
+      if (!row.sample) continue;
+      request->tokens.push_back(PENDING);
+      if (request->generated() >= request->max_tokens) {
+        request->finish_reason = LENGTH;
+        finished_out[i] = LENGTH;
+        running.erase(std::find(running.begin(), running.end(), request));
+        const int rc2 = cache->finish(row.id);
+        if (rc2 != VH_OK) return rc2;
+      }
+    }
+    ahead_plan = last_plan;
+    ahead_state.assign(finished_out, finished_out + count);
+    last_plan.clear();
+    return count;
+  }
+  // sampled[i]: the token of row i of the plan commit_ahead took. finished_out[i]: IGNORED for a
+  // row that emits nothing, else the request's finish reason after this token.
+  int resolve(const int32_t* sampled, int count, int32_t* finished_out) {
+    if (count != (int)ahead_plan.size()) return fail(VH_BAD_ARGUMENT, "resolve of %d rows, the step had %zu", count, ahead_plan.size());
+    for (int i = 0; i < count; ++i) {
+      const PlanRow& row = ahead_plan[i];
+      finished_out[i] = IGNORED;
+      if (!row.sample || ahead_state[i] == IGNORED) continue;
+      auto found = requests.find(row.id);
+      if (found == requests.end()) continue;
+      auto request = found->second;
+      const int index = row.start + row.count;            // where the sampled token went
+      if (index >= (int)request->tokens.size() || request->tokens[index] != PENDING) continue;
+      if (request->finish_reason == ABORTED) continue;
+      const int32_t token = sampled[i];
+      request->tokens[index] = token;
+      finished_out[i] = request->finish_reason;           // LENGTH if commit_ahead ended it
+      if (request->finish_reason != NOT_FINISHED || request->ignore_eos) continue;
+      for (int e = 0; e < request->n_eos; ++e)
+        if (request->eos[e] == token) {
+          abort(row.id);                                  // leaves its queue, gives back what it holds
+          request->finish_reason = EOS;
+          finished_out[i] = EOS;
+          break;
+        }
+    }
+    ahead_plan.clear();
+    ahead_state.clear();
+    return VH_OK;
+  }
+  std::vector<PlanRow> ahead_plan;
+  std::vector<int32_t> ahead_state;
+
   CacheCore* cache;
   int max_num_seqs, max_batched_tokens, chunk_size, vocab_size, max_context;
   std::deque<std::shared_ptr<Request>> waiting, running;
@@ -740,6 +812,10 @@ VH_API int vh_plan(void* host, int64_t* ids_out, int32_t* rows_out, int capacity
 }
 VH_API int vh_commit(void* host, const int32_t* sampled, int count, int32_t* finished_out) {
   return ((Host*)host)->scheduler->commit(sampled, count, finished_out);
+}
+VH_API int vh_commit_ahead(void* host, int32_t* finished_out) { return ((Host*)host)->scheduler->commit_ahead(finished_out); }
+VH_API int vh_resolve(void* host, const int32_t* sampled, int count, int32_t* finished_out) {
+  return ((Host*)host)->scheduler->resolve(sampled, count, finished_out);
 }
 // which: 0 computed, 1 generated count, 2 preemptions, 3 finish reason, 4 total tokens
 VH_API int vh_request_field(void* host, int64_t id, int which) {

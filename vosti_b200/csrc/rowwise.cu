@@ -5,13 +5,17 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
+// With `source`, row t takes its id from values[source[t]] where source[t] >= 0: a token the
+// sampler of the step before left on the device, which the host has not read yet.
 template <typename T>
-__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+__global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ source,
+                                 const int* __restrict__ values, const T* __restrict__ table,
                                  T* __restrict__ out, int hidden, int vocab, unsigned* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   int id = ids[t];
+  if (source != nullptr && source[t] >= 0) id = values[source[t]];
   const bool bad = id < 0 || id >= vocab;
   if (bad) {
     if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_TOKEN_RANGE);
@@ -29,15 +33,15 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
   }
 }
 
-VOSTI_API int vosti_embedding(const int* ids, const void* table, void* out, int tokens, int hidden,
-                              int vocab, int is_f32, unsigned* status, cudaStream_t stream) {
+VOSTI_API int vosti_embedding(const int* ids, const int* source, const int* values, const void* table, void* out,
+                              int tokens, int hidden, int vocab, int is_f32, unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d",
                 tokens, hidden, vocab);
   if (tokens == 0) return VOSTI_OK;
   if (is_f32)
-    vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, (const float*)table, (float*)out, hidden, vocab, status);
+    vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, (float*)out, hidden, vocab, status);
   else
-    vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, (const bf16*)table, (bf16*)out, hidden, vocab, status);
+    vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, (bf16*)out, hidden, vocab, status);
   VOSTI_LAUNCH_CHECK();
 }
 

@@ -63,6 +63,9 @@ class StepContext:
     max_kv_len: int = 0
     all_decode: bool = False
     extras: dict = field(default_factory=dict)   # further per-step device arrays by name
+    # extras["feedback"] (int32 [T], -1 or an index) names tokens to take from this device array
+    # instead of `tokens`: what the step before sampled and the host has not read yet
+    feedback_values: Optional[torch.Tensor] = None
     # attention work lists: tokens of requests that bring at most SHORT_ROW tokens (served
     # one query at a time) and the requests that bring more (served as portions)
     short_tokens: Optional[torch.Tensor] = None   # int32 token indices, None: every token

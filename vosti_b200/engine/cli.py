@@ -144,6 +144,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     parser.add_argument("--step-trace", default=_env("VOSTI_ENGINE_STEP_TRACE"))
     parser.add_argument("--no-prefix-caching", action="store_true")
     parser.add_argument("--cuda-graph", type=int, choices=[0, 1], default=int(_env("VOSTI_CUDA_GRAPH", 1)))
+    parser.add_argument("--async-scheduling", type=int, choices=[0, 1], default=int(_env("VOSTI_ASYNC_SCHEDULING", 1)),
+                        help="launch the next step before the last one's tokens are read (1, default) or after (0)")
     parser.add_argument("--batch-invariant", nargs="?", const="full", choices=["off", "decode", "full"],
                         default={"0": "off", "1": "full"}.get(_env("VOSTI_BATCH_INVARIANT", "off"),
                                                               _env("VOSTI_BATCH_INVARIANT", "off")),
@@ -173,7 +175,8 @@ def main(argv: Optional[List[str]] = None) -> int:
                     block_size=args.block_size, max_num_seqs=max_seqs,
                     max_num_batched_tokens=args.max_batched_tokens, prefill_chunk_size=args.chunk_size,
                     enable_prefix_caching=not args.no_prefix_caching, step_trace=args.step_trace,
-                    cuda_graphs=bool(args.cuda_graph), batch_invariant=args.batch_invariant)
+                    cuda_graphs=bool(args.cuda_graph), batch_invariant=args.batch_invariant,
+                    async_scheduling=bool(args.async_scheduling))
     print(f"MODEL_RUNTIME architecture={engine.runner.spec.architecture} dtype={args.dtype} "
           f"device={args.device}", flush=True)
 
@@ -203,7 +206,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     if status.value != "accepted":
         raise SystemExit(f"invalid request: {status.value}")
     output: List[int] = []
-    for _ in range(len(prompt) + args.max_tokens + 2):
+    for _ in range(len(prompt) + args.max_tokens + 4):
         if not engine.has_unfinished():
             break
         emitted = engine.step()

@@ -20,6 +20,7 @@ import json
 import time
 from typing import Dict, Iterable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..sampling import sample_rows, sampling_arrays
@@ -27,6 +28,15 @@ from .batch import StepEntry
 from .request import AdmissionStatus, Request
 from .runner import DeviceFault, ModelRunner, _FAULTS
 from .scheduler import Scheduler, SchedulerConfig, StepPlan
+
+
+class _Launched:
+    """A step that was launched: its plan, how many rows sample, and where its result lands."""
+
+    __slots__ = ("plan", "count", "host", "event")
+
+    def __init__(self, plan: StepPlan, count: int, host: torch.Tensor, event: torch.cuda.Event):
+        self.plan, self.count, self.host, self.event = plan, count, host, event
 
 
 def _is_bfloat16(dtype) -> bool:
@@ -38,7 +48,8 @@ class Engine:
                  num_blocks: int = 32, block_size: int = 16, max_num_seqs: int = 1,
                  max_num_batched_tokens: int = 4096, prefill_chunk_size: int = 0,
                  enable_prefix_caching: bool = True, step_trace: Optional[str] = None,
-                 cuda_graphs: bool = True, batch_invariant=False, spec=None, tensors=None):
+                 cuda_graphs: bool = True, batch_invariant=False, async_scheduling: bool = False, spec=None,
+                 tensors=None):
         """`num_blocks` pages of `block_size` tokens; `max_num_seqs` rows and
         `max_num_batched_tokens` tokens per step at most (the reference's VOSTI_NUM_BLOCKS,
         VOSTI_MAX_SEQS, VOSTI_MAX_BATCHED_TOKENS; its page size is fixed at 64).
@@ -47,7 +58,10 @@ class Engine:
         depend on how prompts are cut into portions, on reused prefixes or on the batch around
         it, at the price of slower decoding; "decode" only pins the decode attention's segment
         length, which makes decode steps of up to 64 rows independent of the batch and costs
-        little; the default lets every launch cut its work to fit its shape."""
+        little; the default lets every launch cut its work to fit its shape.
+        `async_scheduling`: `step` launches the next step before it reads the last one's tokens,
+        so the GPU does not idle while the host plans; the tokens a call returns are then those
+        of the step launched by the call before (one call later than without it)."""
         from .. import ops
         if _is_bfloat16(dtype):
             ops.set_invariance(batch_invariant)
@@ -60,6 +74,12 @@ class Engine:
             prefill_chunk_size=prefill_chunk_size, vocab_size=spec.vocab_size, max_context=spec.max_positions))
         from .graphs import DecodeGraphs
         self.graphs = DecodeGraphs(self.runner) if cuda_graphs else None
+        self.async_scheduling = bool(async_scheduling)
+        self._inflight: Optional[_Launched] = None
+        rows = 1 + max(max_num_seqs, 1)
+        self._host_results = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events = [torch.cuda.Event() for _ in range(2)]
+        self._host_turn = 0
         self.step_trace = open(step_trace, "a") if step_trace else None
         self.step_index = 0
         self.last_plan: Optional[StepPlan] = None
@@ -80,7 +100,7 @@ class Engine:
         return self.scheduler.abort(request_id)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self._inflight is not None or self.scheduler.has_unfinished()
 
     def request(self, request_id) -> Optional[Request]:
         for r in self.scheduler.running + self.scheduler.waiting:
@@ -90,26 +110,84 @@ class Engine:
 
     # ------------------------------------------------------------ one step
     def step(self) -> Dict[object, int]:
-        """Plan, run, sample and commit one step; returns the tokens emitted by it."""
+        """Plan, run, sample and commit one step; returns the tokens emitted by it. With
+        `async_scheduling` the step that is planned and launched is the next one, and the
+        tokens returned are those of the step launched by the call before."""
+        if self.async_scheduling:
+            return self._step_ahead(launch=True)
         plan = self.scheduler.plan()
         self.last_plan = plan
         self.step_index += 1
         if not plan.rows:
             self._trace(plan, {})
             return {}
-        entries, temps, seeds, counters = [], [], [], []
+        launched = self._launch(plan, None)
+        emitted = self.scheduler.commit(plan, self._collect(launched))
+        self._trace(plan, emitted)
+        return emitted
+
+    def drain(self) -> Dict[object, int]:
+        """Read the step that is still in flight, if any, without launching another."""
+        return self._step_ahead(launch=False) if self._inflight is not None else {}
+
+    def _step_ahead(self, launch: bool) -> Dict[object, int]:
+        """Launch step n + 1 before step n's tokens are read, so that the GPU does not wait for
+        the host between steps. The scheduler commits step n in two halves (what needs no token
+        values now, the tokens and the end by EOS once they are read); a request's newest
+        token, while the host does not have it, is fed to the next step on the device from
+        where the sampler left it. A request that step n's tokens end still has a row in the
+        step launched meanwhile: that row's result is dropped."""
+        before = self._inflight
+        if before is not None:
+            self.scheduler.commit_ahead(before.plan)
+        launched = None
+        if launch:
+            plan = self.scheduler.plan()
+            self.last_plan = plan
+            self.step_index += 1
+            if plan.rows:
+                launched = self._launch(plan, before)
+            elif before is None:
+                self._trace(plan, {})
+        emitted: Dict[object, int] = {}
+        if before is not None:
+            emitted = self.scheduler.resolve(before.plan, self._collect(before))
+            self._trace(before.plan, emitted)
+        self._inflight = launched
+        return emitted
+
+    def _launch(self, plan: StepPlan, before: Optional["_Launched"]) -> "_Launched":
+        """Lay out and launch the plan's step, sampling included, and start the copy of its
+        result to the host. `before` is the step launched earlier whose tokens the host has not
+        read: a row whose last token is one of them names its place in that step's result."""
+        runner = self.runner
+        entries, temps, seeds, counters, feedback = [], [], [], [], []
+        slot_before = {}
+        if before is not None:
+            slot = 0
+            for row in before.plan.rows:
+                if row.sample:
+                    slot_before[row.request.request_id] = slot
+                    slot += 1
         for row in plan.rows:
             request = row.request
             tokens = request.token_range(row.start, row.count)
+            source = [-1] * row.count
+            if tokens[-1] == Scheduler.PENDING:
+                if request.request_id not in slot_before:
+                    raise RuntimeError(f"request {request.request_id!r}: its newest token is neither known nor on the device")
+                tokens[-1], source[-1] = 0, slot_before[request.request_id]
+            feedback.extend(source)
             entries.append(StepEntry(request.request_id, tokens, [row.count - 1] if row.sample else []))
             if row.sample:
                 temps.append(request.temperature)
                 seeds.append(request.seed)
                 counters.append(len(request.generated))
-        runner = self.runner
         arrays = sampling_arrays(temps, seeds, counters)
         extras = None if arrays is None else {"temperature": arrays[0], "seeds": arrays[1], "counters": arrays[2]}
-        sampled: List[Optional[int]] = [None] * len(plan.rows)
+        if self.async_scheduling:
+            extras = dict(extras or {})
+            extras["feedback"] = np.asarray(feedback, dtype=np.int32)
         count = len(temps)
         if self.graphs is not None and all(row.count == 1 and row.sample for row in plan.rows):
             self.graphs.step(entries, extras, longest=max(row.start for row in plan.rows) + 1)
@@ -120,22 +198,26 @@ class Engine:
                 ex = ctx.extras
                 sample_rows(logits, ex.get("temperature"), ex.get("seeds"), ex.get("counters"),
                             out=runner.result[1:1 + count])
-        runner.result_host[:1 + count].copy_(runner.result[:1 + count], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        host = runner.result_host[:1 + count].tolist()
-        if host[0]:
-            runner.status.zero_()
-            raise DeviceFault("device reported: " + "; ".join(t for b, t in _FAULTS.items() if host[0] & b))
-        it = iter(host[1:])
-        for i, row in enumerate(plan.rows):
-            if row.sample:
-                sampled[i] = next(it)
+        self._host_turn ^= 1
+        host = self._host_results[self._host_turn]
+        host[:1 + count].copy_(runner.result[:1 + count], non_blocking=True)
+        event = self._events[self._host_turn]
+        event.record()
         if runner.cache.has_windows:
             for e in entries:
                 runner.cache.trim(e.request_id)
-        emitted = self.scheduler.commit(plan, sampled)
-        self._trace(plan, emitted)
-        return emitted
+        return _Launched(plan, count, host, event)
+
+    def _collect(self, launched: "_Launched") -> List[Optional[int]]:
+        """Wait for a launched step's result; returns the token of every row (None where the
+        row does not sample)."""
+        launched.event.synchronize()
+        host = launched.host[:1 + launched.count].tolist()
+        if host[0]:
+            self.runner.status.zero_()
+            raise DeviceFault("device reported: " + "; ".join(t for b, t in _FAULTS.items() if host[0] & b))
+        it = iter(host[1:])
+        return [next(it) if row.sample else None for row in launched.plan.rows]
 
     def _trace(self, plan: StepPlan, emitted: Dict[object, int]) -> None:
         """One JSON line per step, as the reference's VOSTI_ENGINE_STEP_TRACE

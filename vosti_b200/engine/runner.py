@@ -77,6 +77,7 @@ class ModelRunner:
         self.result = torch.zeros(1 + max(max_requests, 1), dtype=torch.int32, device=self.device)
         self.result_host = torch.zeros(1 + max(max_requests, 1), dtype=torch.int32, pin_memory=True)
         self.status = self.result[:1]
+        self.sampled = self.result[1:]            # where the sampler leaves a step's tokens
         self.steps = 0
         self.kernel_launches = 0
 
@@ -92,8 +93,10 @@ class ModelRunner:
                 kv_bucket: int = 0) -> StepContext:
         """Reserve cache entries for the step's tokens (all requests or none) and copy the
         batch to the device."""
-        return build_context(self.staging, self.cache, entries, self.status, self.dtype, extras=extras,
-                             min_pages=min_pages, kv_bucket=kv_bucket, position_limit=self.spec.max_positions)
+        ctx = build_context(self.staging, self.cache, entries, self.status, self.dtype, extras=extras,
+                            min_pages=min_pages, kv_bucket=kv_bucket, position_limit=self.spec.max_positions)
+        ctx.feedback_values = self.sampled
+        return ctx
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """The model over the prepared batch; float32 logits [wanted, vocab] or None."""

@@ -201,3 +201,45 @@ class Scheduler:
                 request.finished, request.finish_reason = True, _FINISH[finished[i]]
                 self.finished[request.request_id] = request
         return emitted
+
+    # ------------------------------------------------------------ the commit in two halves
+    PENDING = -1          # a sampled token the host has not read yet
+
+    def commit_ahead(self, plan: StepPlan) -> List[int]:
+        """Apply what a step's commit does without its tokens (counts, publication, the end by
+        length); sampling rows get the token PENDING. Returns a state per row: -1 for a row
+        whose request had ended before (it is ignored from here on)."""
+        count = len(plan.rows)
+        state = (ctypes.c_int32 * max(count, 1))()
+        host.check(self._lib.vh_commit_ahead(self._h, state))
+        for i, row in enumerate(plan.rows):
+            if state[i] < 0:
+                continue
+            request = row.request
+            request.computed += row.count
+            if row.sample:
+                request.generated.append(self.PENDING)
+                if state[i]:
+                    request.finished, request.finish_reason = True, _FINISH[state[i]]
+                    self.finished[request.request_id] = request
+        return list(state[:count])
+
+    def resolve(self, plan: StepPlan, sampled: Sequence[Optional[int]]) -> Dict[object, int]:
+        """Write the tokens of a step that commit_ahead took in and apply the end by EOS.
+        Returns request id -> emitted token."""
+        count = len(plan.rows)
+        tokens = [int(t) if (row.sample and t is not None) else 0 for row, t in zip(plan.rows, sampled)]
+        finished = (ctypes.c_int32 * max(count, 1))()
+        host.check(self._lib.vh_resolve(self._h, host.ints(tokens), count, finished))
+        emitted: Dict[object, int] = {}
+        for i, row in enumerate(plan.rows):
+            if not row.sample or finished[i] < 0:
+                continue
+            request = row.request
+            index = row.start + row.count - len(request.prompt_tokens)
+            request.generated[index] = tokens[i]
+            emitted[request.request_id] = tokens[i]
+            if finished[i] and not request.finished:
+                request.finished, request.finish_reason = True, _FINISH[finished[i]]
+                self.finished[request.request_id] = request
+        return emitted

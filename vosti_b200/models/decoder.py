@@ -94,7 +94,9 @@ class DecoderModel:
     def forward(self, ctx, layer_caches: List):
         """Run every entry of the run order over the batch in `ctx`; returns the last
         block's (hidden, residual), both [T, hidden] (residual None without blocks)."""
-        hidden = ops.embedding(ctx.tokens, self.embed, ctx.status)
+        source = ctx.extras.get("feedback") if ctx.extras else None
+        hidden = ops.embedding(ctx.tokens, self.embed, ctx.status,
+                               feedback=None if source is None else (source, ctx.feedback_values))
         residual: Optional[torch.Tensor] = None
         for entry in self.spec.run_order:
             owner = entry.layer if entry.cache_from is None else entry.cache_from

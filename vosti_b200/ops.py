@@ -87,10 +87,17 @@ def _contig(*tensors):
             raise KernelError("kernels take contiguous tensors")
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
+              feedback: Optional[tuple] = None) -> torch.Tensor:
+    """table[ids]. `feedback` = (source, values), int32: row t takes values[source[t]] as its id
+    where source[t] >= 0 (a token sampled on the device that the host has not read yet)."""
     _contig(ids, table)
+    source, values = feedback if feedback is not None else (None, None)
+    if source is not None:
+        _contig(source, values)
+        assert source.shape[0] == ids.shape[0] and source.dtype == values.dtype == torch.int32
     out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
-    _check(library().vosti_embedding(_p(ids), _p(table), _p(out), ids.shape[0], table.shape[1],
+    _check(library().vosti_embedding(_p(ids), _p(source), _p(values), _p(table), _p(out), ids.shape[0], table.shape[1],
                                      table.shape[0], _is_f32(table), _p(status), _stream()), "embedding")
     return out
 
