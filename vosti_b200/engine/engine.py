@@ -33,10 +33,10 @@ from .scheduler import Scheduler, SchedulerConfig, StepPlan
 class _Launched:
     """A step that was launched: its plan, how many rows sample, and where its result lands."""
 
-    __slots__ = ("plan", "count", "host", "event")
+    __slots__ = ("plan", "count", "host", "event", "index")
 
-    def __init__(self, plan: StepPlan, count: int, host: torch.Tensor, event: torch.cuda.Event):
-        self.plan, self.count, self.host, self.event = plan, count, host, event
+    def __init__(self, plan: StepPlan, count: int, host: torch.Tensor, event: torch.cuda.Event, index: int):
+        self.plan, self.count, self.host, self.event, self.index = plan, count, host, event, index
 
 
 def _is_bfloat16(dtype) -> bool:
@@ -152,7 +152,7 @@ class Engine:
         emitted: Dict[object, int] = {}
         if before is not None:
             emitted = self.scheduler.resolve(before.plan, self._collect(before))
-            self._trace(before.plan, emitted)
+            self._trace(before.plan, emitted, before.index)
         self._inflight = launched
         return emitted
 
@@ -206,7 +206,7 @@ class Engine:
         if runner.cache.has_windows:
             for e in entries:
                 runner.cache.trim(e.request_id)
-        return _Launched(plan, count, host, event)
+        return _Launched(plan, count, host, event, self.step_index)
 
     def _collect(self, launched: "_Launched") -> List[Optional[int]]:
         """Wait for a launched step's result; returns the token of every row (None where the
@@ -219,13 +219,13 @@ class Engine:
         it = iter(host[1:])
         return [next(it) if row.sample else None for row in launched.plan.rows]
 
-    def _trace(self, plan: StepPlan, emitted: Dict[object, int]) -> None:
+    def _trace(self, plan: StepPlan, emitted: Dict[object, int], index: Optional[int] = None) -> None:
         """One JSON line per step, as the reference's VOSTI_ENGINE_STEP_TRACE
         (examples/support/engine_benchmark.rs:273-317)."""
         if self.step_trace is None:
             return
         self.step_trace.write(json.dumps({
-            "step": self.step_index,
+            "step": self.step_index if index is None else index,
             "scheduled": [[str(r.request.request_id), r.start, r.count, r.sample] for r in plan.rows],
             "emitted": {str(k): v for k, v in emitted.items()},
             "preempted": [str(r) for r in plan.preempted], "dropped": [str(r) for r in plan.dropped],
