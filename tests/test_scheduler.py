@@ -298,3 +298,20 @@ def test_commit_in_two_halves_gives_the_tokens_of_the_plain_commit(seed):
         assert cache.available_pages() == cache.num_pages and not cache.live
         outcomes.append({rid: (sched.finished[rid].generated, sched.finished[rid].finish_reason) for rid in ids})
     assert outcomes[0] == outcomes[1]
+
+
+def test_reuse_counters_do_not_count_a_blocked_admission_twice():
+    """A waiting request whose prefix matches but which does not fit yet is tried every step;
+    only its admission counts."""
+    cache, sched = make(num_pages=8, page_size=4, max_num_seqs=2, budget=64)
+    shared = [1, 2, 3, 4, 5, 6, 7, 8]
+    sched.add_request(Request(0, shared + [9], 12, ignore_eos=True))
+    run_step(cache, sched)
+    sched.add_request(Request(1, shared + [3] * 23, 1, ignore_eos=True))      # needs more pages than are free
+    for _ in range(4):
+        plan, _ = run_step(cache, sched)
+        assert [r.request.request_id for r in plan.rows] == [0]
+    assert cache.requests_with_reuse == 0 and cache.reused_prefix_pages == 0
+    while sched.has_unfinished():
+        run_step(cache, sched)
+    assert cache.requests_with_reuse == 1 and cache.reused_prefix_pages == 2

@@ -486,7 +486,11 @@ class SchedulerCore {
       const int count = chunk(request->remaining(), budget);
       const int need = count > 0 ? cache->pages_needed(*res, count) : 0;
       if (count <= 0 || reserved + need > cache->available_pages()) {
-        cache->finish(request->id);                       // roll back: nothing of it is held
+        if (res->cached_prefix_pages > 0) {               // roll back: nothing of it is held or counted
+          cache->reused_prefix_pages -= res->cached_prefix_pages;
+          --cache->requests_with_reuse;
+        }
+        cache->finish(request->id);
         request->computed = 0;
         break;
       }
