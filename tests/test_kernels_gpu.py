@@ -583,3 +583,36 @@ def test_deferred_split_sums_feed_the_norm_and_the_head_kernel(dev, status):
     q2 = ops.qkv_post(ops.gemm_tc(x, w2, status, allow_partial=True), kc2, vc2, **args)
     assert torch.allclose(q1.float(), q2.float(), atol=2e-2, rtol=2e-2)
     assert torch.allclose(kc1.float(), kc2.float(), atol=2e-2, rtol=2e-2) and torch.allclose(vc1.float(), vc2.float(), atol=2e-2)
+
+
+def test_gemm_tc_on_pairs_of_sms_gives_the_same_bits(tmp_path):
+    """The two-CTA form of the product for many tokens (tcgen05 cta_group::2, chosen with
+    VOSTI_GEMM_PAIR=1 when the library is loaded, hence a process of its own) gives the bits of
+    the unsplit single-CTA kernels: row-major and tile-packed weights, every epilogue, edges in
+    tokens, features and K."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    script = r'''
+import sys, torch
+from vosti_b200 import ops
+dev = torch.device("cuda:0")
+status = torch.zeros(1, dtype=torch.int32, device=dev)
+ops.set_fixed_order(True)
+torch.manual_seed(0)
+for (T, f, k) in [(300, 512, 256), (129, 1000, 200), (1100, 4096 + 160, 1024), (640, 1536, 4096)]:
+    w = (torch.randn(f, k, device=dev) / 8).bfloat16()
+    x = torch.randn(T, k, device=dev).bfloat16()
+    for W in (w, ops.PackedWeight(w)):
+        for kw in (dict(), dict(out_dtype=torch.float32)) + ((dict(swiglu=True),) if f % 32 == 0 else ()):
+            got = ops.gemm_tc(x, W, status, **kw)
+            want = torch.cat([ops.gemm_tc(x[i:i + 128].contiguous(), W, status, **kw) for i in range(0, T, 128)])
+            assert torch.equal(got, want), (T, f, k, kw)
+assert status.item() == 0
+print("pairs ok")
+'''
+    root = Path(__file__).resolve().parents[1]
+    env = dict(os.environ, VOSTI_GEMM_PAIR="1", PYTHONPATH=str(root))
+    done = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and "pairs ok" in done.stdout, done.stderr[-2000:]

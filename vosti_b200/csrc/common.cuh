@@ -135,3 +135,24 @@ inline cudaError_t vosti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   config.numAttrs = 1;
   return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
+
+// The same with thread-block clusters of `cluster` CTAs along x (the grid's x must be a multiple).
+template <typename... KArgs, typename... Args>
+inline cudaError_t vosti_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster, size_t smem,
+                                         cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = vosti_pdl_enabled() ? 1 : 0;
+  attribute[1].id = cudaLaunchAttributeClusterDimension;
+  attribute[1].val.clusterDim.x = cluster;
+  attribute[1].val.clusterDim.y = 1;
+  attribute[1].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 2;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}

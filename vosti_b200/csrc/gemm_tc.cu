@@ -216,6 +216,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 
+// One token's 32 consecutive accumulator columns (features f0 .. f0 + 31) through the epilogue
+// into the output: bf16, float32, or SiLU(gate) * up of 16 gate and 16 up columns.
+__device__ __forceinline__ void store_token_columns(const uint32_t (&r)[32], void* __restrict__ out, int token, int f0,
+                                                    int features, int ld_out, int epilogue) {
+  if (epilogue == EPI_SWIGLU) {
+    // columns f0..f0+15 are gate rows, f0+16..f0+31 their up rows (features % 32 == 0)
+    bf16* y = reinterpret_cast<bf16*>(out) + (int64_t)token * ld_out + f0 / 2;
+    uint32_t packed[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = silu(__uint_as_float(r[2 * j])) * __uint_as_float(r[16 + 2 * j]);
+      const float b = silu(__uint_as_float(r[2 * j + 1])) * __uint_as_float(r[17 + 2 * j]);
+      __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+      packed[j] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    if ((ld_out & 7) == 0) {
+      reinterpret_cast<uint4*>(y)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      reinterpret_cast<uint4*>(y)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) reinterpret_cast<uint32_t*>(y)[j] = packed[j];   // ld_out is even
+    }
+  } else if (epilogue == EPI_BF16) {
+    bf16* y = reinterpret_cast<bf16*>(out) + (int64_t)token * ld_out + f0;
+    if (f0 + 32 <= features && (ld_out & 7) == 0) {
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        uint32_t p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * v4 + 2 * j]), __uint_as_float(r[8 * v4 + 2 * j + 1]));
+          p[j] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        reinterpret_cast<uint4*>(y)[v4] = make_uint4(p[0], p[1], p[2], p[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (f0 + j < features) y[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+    }
+  } else {  // EPI_F32
+    float* y = reinterpret_cast<float*>(out) + (int64_t)token * ld_out + f0;
+    if (f0 + 32 <= features && (ld_out & 3) == 0) {
+#pragma unroll
+      for (int v4 = 0; v4 < 8; ++v4)
+        reinterpret_cast<uint4*>(y)[v4] = make_uint4(r[4 * v4], r[4 * v4 + 1], r[4 * v4 + 2], r[4 * v4 + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (f0 + j < features) y[j] = __uint_as_float(r[j]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ the kernel for many tokens
 // For more than 128 tokens the roles are swapped: 128 tokens fill the MMA's M (one
 // accumulator lane per token) and 256 features are the N side, so that a thread of the
@@ -332,54 +386,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         uint32_t r[32];
         tmem_load32(tmem_base + as * WIDE_BN + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         if (!row_ok) continue;
-        if (epilogue == EPI_SWIGLU) {
-          // columns f0..f0+15 are gate rows, f0+16..f0+31 their up rows (features % 32 == 0)
-          bf16* y = reinterpret_cast<bf16*>(out) + (int64_t)token * ld_out + f0 / 2;
-          uint32_t packed[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float a = silu(__uint_as_float(r[2 * j])) * __uint_as_float(r[16 + 2 * j]);
-            const float b = silu(__uint_as_float(r[2 * j + 1])) * __uint_as_float(r[17 + 2 * j]);
-            __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-            packed[j] = *reinterpret_cast<uint32_t*>(&v);
-          }
-          if ((ld_out & 7) == 0) {
-            reinterpret_cast<uint4*>(y)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            reinterpret_cast<uint4*>(y)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) reinterpret_cast<uint32_t*>(y)[j] = packed[j];   // ld_out is even
-          }
-        } else if (epilogue == EPI_BF16) {
-          bf16* y = reinterpret_cast<bf16*>(out) + (int64_t)token * ld_out + f0;
-          if (f0 + 32 <= features && (ld_out & 7) == 0) {
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint32_t p[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * v4 + 2 * j]), __uint_as_float(r[8 * v4 + 2 * j + 1]));
-                p[j] = *reinterpret_cast<uint32_t*>(&v);
-              }
-              reinterpret_cast<uint4*>(y)[v4] = make_uint4(p[0], p[1], p[2], p[3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (f0 + j < features) y[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-          }
-        } else {  // EPI_F32
-          float* y = reinterpret_cast<float*>(out) + (int64_t)token * ld_out + f0;
-          if (f0 + 32 <= features && (ld_out & 3) == 0) {
-#pragma unroll
-            for (int v4 = 0; v4 < 8; ++v4)
-              reinterpret_cast<uint4*>(y)[v4] = make_uint4(r[4 * v4], r[4 * v4 + 1], r[4 * v4 + 2], r[4 * v4 + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (f0 + j < features) y[j] = __uint_as_float(r[j]);
-          }
-        }
+        store_token_columns(r, out, token, f0, features, ld_out, epilogue);
       }
       // this warp is done reading the accumulator: hand it back to the MMA warp
       tc_fence_before();
@@ -398,6 +405,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tmem_dealloc(tmem_base, 2 * WIDE_BN);
   }
 }
+
+#include "gemm_tc_pair.cuh"
 
 // Sum the K splits in split order and apply the epilogue.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int splits,
@@ -540,6 +549,34 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
   // tensor map is that of a matrix of 64 columns
   const int w_tiles = w_packed ? (features + BM - 1) / BM : 0;
   const int w_rows = w_packed ? k_blocks * w_tiles * BM : features, w_cols = w_packed ? BK : k;
+  static const bool use_pairs = [] {
+    const char* env = getenv("VOSTI_GEMM_PAIR");
+    return env != nullptr && env[0] == '1';
+  }();
+  if (tokens > 128 && use_pairs) {
+    // many tokens, two SMs per tile (cta_group::2)
+    using namespace pair_kernel;
+    VOSTI_REQUIRE(weight_map(w, w_rows, w_cols, BM, &mw_storage) && make_map(&mx, x, tokens, k, BM),
+                  "gemm_tc: cuTensorMapEncodeTiled failed");
+    constexpr size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+    static int pair_sms = 0;
+    if (pair_sms == 0) {
+      int device = 0;
+      cudaGetDevice(&device);
+      cudaDeviceGetAttribute(&pair_sms, cudaDevAttrMultiProcessorCount, device);
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess || pair_sms <= 1) {
+        pair_sms = 0;
+        vosti_set_error("gemm_tc: cannot configure the paired kernel: %s", cudaGetErrorString(e));
+        return e != cudaSuccess ? (int)e : VOSTI_UNSUPPORTED;
+      }
+    }
+    const int tiles = ((tokens + 2 * BM - 1) / (2 * BM)) * ((features + PAIR_BN - 1) / PAIR_BN);
+    const int pairs = tiles < pair_sms / 2 ? tiles : pair_sms / 2;
+    vosti_launch_clusters(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(PAIR_THREADS), 2, smem, stream, mx, *mw, y, tokens,
+                          features, k_blocks, ld_out, epilogue, w_tiles, status);
+    VOSTI_LAUNCH_CHECK();
+  }
   if (tokens > 128) {
     // many tokens: persistent kernel with tokens on the M side
     VOSTI_REQUIRE(weight_map(w, w_rows, w_cols, WIDE_BN, &mw_storage) && make_map(&mx, x, tokens, k, BM),
