@@ -12,7 +12,9 @@ The surface is the reference's Rust API as its example drives it: `Engine::init`
 `try_add_request`, `step` -> emitted tokens (src/exec/engine.rs:2515, 2664, 2795;
 examples/support/engine_serving.rs:211-219). One step is plan -> forward -> sample ->
 publish completed pages -> commit (src/exec/engine.rs:2781-2782), with one device-to-host
-copy for the sampled tokens and the device fault word.
+copy for the sampled tokens and the device fault word. With `async_scheduling` the order
+becomes plan -> launch the next step -> read the last step's tokens, and the commit is split
+in two around the plan (`Scheduler.commit_ahead`, `Scheduler.resolve`).
 """
 from __future__ import annotations
 
