@@ -585,11 +585,13 @@ def test_deferred_split_sums_feed_the_norm_and_the_head_kernel(dev, status):
     assert torch.allclose(kc1.float(), kc2.float(), atol=2e-2, rtol=2e-2) and torch.allclose(vc1.float(), vc2.float(), atol=2e-2)
 
 
-def test_gemm_tc_on_pairs_of_sms_gives_the_same_bits(tmp_path):
-    """The two-CTA form of the product for many tokens (tcgen05 cta_group::2, chosen with
-    VOSTI_GEMM_PAIR=1 when the library is loaded, hence a process of its own) gives the bits of
-    the unsplit single-CTA kernels: row-major and tile-packed weights, every epilogue, edges in
-    tokens, features and K."""
+@pytest.mark.parametrize("pairs", ["1", "0"])
+def test_gemm_tc_for_many_tokens_gives_the_bits_of_the_unsplit_narrow_kernel(pairs):
+    """Both forms of the product for many tokens, on pairs of SMs (tcgen05 cta_group::2, the
+    default) and on single SMs (VOSTI_GEMM_PAIR=0, read when the library is loaded, hence a
+    process of its own), give the bits of the unsplit kernel for up to 128 tokens: row-major and
+    tile-packed weights, every epilogue, edges in tokens, features and K, an odd number of
+    k-blocks."""
     import os
     import subprocess
     import sys
@@ -601,7 +603,7 @@ dev = torch.device("cuda:0")
 status = torch.zeros(1, dtype=torch.int32, device=dev)
 ops.set_fixed_order(True)
 torch.manual_seed(0)
-for (T, f, k) in [(300, 512, 256), (129, 1000, 200), (1100, 4096 + 160, 1024), (640, 1536, 4096)]:
+for (T, f, k) in [(300, 512, 256), (129, 1000, 200), (1100, 4096 + 160, 1024), (640, 1536, 4096), (257, 200, 320)]:
     w = (torch.randn(f, k, device=dev) / 8).bfloat16()
     x = torch.randn(T, k, device=dev).bfloat16()
     for W in (w, ops.PackedWeight(w)):
@@ -613,6 +615,6 @@ assert status.item() == 0
 print("pairs ok")
 '''
     root = Path(__file__).resolve().parents[1]
-    env = dict(os.environ, VOSTI_GEMM_PAIR="1", PYTHONPATH=str(root))
+    env = dict(os.environ, VOSTI_GEMM_PAIR=pairs, PYTHONPATH=str(root))
     done = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0 and "pairs ok" in done.stdout, done.stderr[-2000:]

@@ -549,9 +549,9 @@ VOSTI_API int vosti_gemm_tc(const void* x, const void* w, void* y, int tokens, i
   // tensor map is that of a matrix of 64 columns
   const int w_tiles = w_packed ? (features + BM - 1) / BM : 0;
   const int w_rows = w_packed ? k_blocks * w_tiles * BM : features, w_cols = w_packed ? BK : k;
-  static const bool use_pairs = [] {
+  static const bool use_pairs = [] {                 // VOSTI_GEMM_PAIR=0: the single-CTA kernel below instead
     const char* env = getenv("VOSTI_GEMM_PAIR");
-    return env != nullptr && env[0] == '1';
+    return env == nullptr || env[0] != '0';
   }();
   if (tokens > 128 && use_pairs) {
     // many tokens, two SMs per tile (cta_group::2)

@@ -4,7 +4,10 @@
 // in its own shared memory, the first CTA of the pair issues every MMA for both tensor cores,
 // and each CTA's tensor memory receives the 256 columns of its own 128 tokens. Against the
 // single-CTA tile (128 x 256: 48 KB of operands per k-block and SM) an SM takes in 32 KB per
-// k-block, and one lane's issue cost is spread over two tensor cores.
+// k-block, so a ring stage can hold two k-blocks and still be three stages deep: the lane that
+// issues the MMAs then pays one barrier wait (about 200 cycles, even when the stage landed long
+// before) and one commit per eight MMAs, 830 cycles for the 1,024 the tensor cores need, where the
+// single-CTA kernel with one k-block per stage pays 610 for 512.
 //
 // Barriers. full[s] lives in the first CTA and counts the bytes of both CTAs' copies (the copies of
 // the second CTA name it through the shared::cluster window); empty[s] and acc_full[a] exist in
@@ -16,8 +19,10 @@
 
 namespace pair_kernel {
 constexpr int PAIR_BN = 256;                       // features per tile (128 per CTA)
-constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_STAGE_BYTES = 2 * A_BYTES;      // 128 tokens x 64 + 128 features x 64, bf16
+constexpr int PAIR_KPS = 2;                        // k-blocks per ring stage: one wait and one commit per eight MMAs
+constexpr int PAIR_STAGES = 3;
+constexpr int PAIR_BLOCK_BYTES = 2 * A_BYTES;      // one k-block: 128 tokens x 64 + 128 features x 64, bf16
+constexpr int PAIR_STAGE_BYTES = PAIR_KPS * PAIR_BLOCK_BYTES;
 constexpr int PAIR_THREADS = 192;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -117,18 +122,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       pdl_wait();
       for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
         const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM, n0 = (tile / m_tiles) * PAIR_BN + (int)rank * BM;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += PAIR_KPS, ++it) {
           const int s = it % PAIR_STAGES;
           if (it >= PAIR_STAGES && !mbar_wait(smem_u32(&empty_bar[s]), (it / PAIR_STAGES - 1) & 1, &abort_flag, status)) {
             ok = false;
             break;
           }
-          if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * PAIR_STAGE_BYTES);   // both CTAs' bytes
+          const int held = k_blocks - kb0 < PAIR_KPS ? k_blocks - kb0 : PAIR_KPS;
+          if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), (uint32_t)(2 * held * PAIR_BLOCK_BYTES));   // both CTAs' bytes
           const uint32_t bar = in_cta(smem_u32(&full_bar[s]), 0);
-          const uint32_t dst = smem_u32(smem + s * PAIR_STAGE_BYTES);
-          tma_load_2d_pair(dst, &map_x, kb * BK, m0, bar);
-          if (w_tiles) tma_load_2d_pair(dst + A_BYTES, &map_w, 0, (kb * w_tiles + n0 / BM) * BM, bar);
-          else tma_load_2d_pair(dst + A_BYTES, &map_w, kb * BK, n0, bar);
+          for (int q = 0; q < held; ++q) {
+            const int kb = kb0 + q;
+            const uint32_t dst = smem_u32(smem + s * PAIR_STAGE_BYTES + q * PAIR_BLOCK_BYTES);
+            tma_load_2d_pair(dst, &map_x, kb * BK, m0, bar);
+            if (w_tiles) tma_load_2d_pair(dst + A_BYTES, &map_w, 0, (kb * w_tiles + n0 / BM) * BM, bar);
+            else tma_load_2d_pair(dst + A_BYTES, &map_w, kb * BK, n0, bar);
+          }
         }
       }
     }
@@ -144,15 +153,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * PAIR_BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += PAIR_KPS, ++it) {
           const int s = it % PAIR_STAGES;
           ok = mbar_wait(smem_u32(&full_bar[s]), (it / PAIR_STAGES) & 1, &abort_flag, status);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * PAIR_STAGE_BYTES);
-          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+          const int held = k_blocks - kb0 < PAIR_KPS ? k_blocks - kb0 : PAIR_KPS;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int q = 0; q < PAIR_KPS; ++q) {
+            if (q < held) {
+              const uint32_t a_addr = smem_u32(smem + s * PAIR_STAGE_BYTES + q * PAIR_BLOCK_BYTES);
+              const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb0 > 0 || q > 0 || k > 0) ? 1u : 0u);
+            }
+          }
           umma_commit_pair(smem_u32(&empty_bar[s]));
         }
         if (ok) umma_commit_pair(smem_u32(&acc_full[as]));
