@@ -126,15 +126,22 @@ def swiglu(x, w_gate, w_up, w_down, round_to=None):
 
 
 def attention_block(x, positions, W, prefix, cfg, round_to=None, window=0):
-    """q,k,v projections without bias; per-head q/k norm before RoPE; v neither
-    normed nor rotated; attention; output projection
+    """q,k,v projections (without bias in Qwen3; a `*_proj.bias` in W is added, for the
+    tests of the projection bias other architectures have); per-head q/k norm before RoPE; v
+    neither normed nor rotated; attention; output projection
     (src/exec/dense_swiglu_decoder.rs:171-367)."""
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
     T = x.shape[0]
-    q = _round(x @ W[prefix + "q_proj.weight"].T, round_to).view(T, nq, d)
-    k = _round(x @ W[prefix + "k_proj.weight"].T, round_to).view(T, nkv, d)
-    v = _round(x @ W[prefix + "v_proj.weight"].T, round_to).view(T, nkv, d)
+
+    def project(name, inp):
+        y = inp @ W[prefix + name + ".weight"].T
+        bias = W.get(prefix + name + ".bias")
+        return _round(y if bias is None else y + bias.to(y.dtype), round_to)
+
+    q = project("q_proj", x).view(T, nq, d)
+    k = project("k_proj", x).view(T, nkv, d)
+    v = project("v_proj", x).view(T, nkv, d)
     q = _round(head_rms_norm(q, W[prefix + "q_norm.weight"], eps), round_to)
     k = _round(head_rms_norm(k, W[prefix + "k_norm.weight"], eps), round_to)
     table_dtype = torch.float32 if round_to is None else round_to
@@ -143,7 +150,7 @@ def attention_block(x, positions, W, prefix, cfg, round_to=None, window=0):
     k = _round(apply_rope(k, cos, sin), round_to)
     attn = causal_attention(q, k, v, float(d) ** -0.5, window=window, round_p_to=round_to)
     attn = _round(attn, round_to).reshape(T, nq * d)
-    return _round(attn @ W[prefix + "o_proj.weight"].T, round_to)
+    return project("o_proj", attn)
 
 
 def forward_hidden(config, W, tokens, round_to=None):

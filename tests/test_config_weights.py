@@ -90,17 +90,35 @@ def test_random_model_folder_roundtrip(tmp_path):
 
 def test_resident_dtypes(tmp_path):
     """bf16 stays bf16; a tensor stored in 32-bit stays 32-bit; integer tables become int32."""
-    tensors = {"a": torch.randn(4, 4).bfloat16(), "b": torch.randn(4), "c": torch.arange(6, dtype=torch.int64),
-               "d": torch.randn(3).half()}
+    tensors = {"a": torch.randn(4, 4).bfloat16(), "b": torch.randn(4), "c": torch.arange(6, dtype=torch.int64)}
     (tmp_path / "m").mkdir()
     write_safetensors(tmp_path / "m" / "model.safetensors", tensors)
-    expected = {"a": WeightSpec((4, 4)), "b": WeightSpec((4,)), "c": WeightSpec((6,), integer=True),
-                "d": WeightSpec((3,))}
+    expected = {"a": WeightSpec((4, 4)), "b": WeightSpec((4,)), "c": WeightSpec((6,), integer=True)}
     got = load_weights(tmp_path / "m", expected, device="cpu", dtype=torch.bfloat16)
-    assert [got[k].dtype for k in "abcd"] == [torch.bfloat16, torch.float32, torch.int32, torch.bfloat16]
+    assert [got[k].dtype for k in "abc"] == [torch.bfloat16, torch.float32, torch.int32]
     assert torch.equal(got["b"], tensors["b"]) and got["c"].tolist() == list(range(6))
     wide = load_weights(tmp_path / "m", expected, device="cpu", dtype=torch.float32)
-    assert [wide[k].dtype for k in "abcd"] == [torch.float32, torch.float32, torch.int32, torch.float32]
+    assert [wide[k].dtype for k in "abc"] == [torch.float32, torch.float32, torch.int32]
+
+
+def test_floating_tensors_stored_in_another_dtype_are_refused_not_rounded(tmp_path):
+    """F16 and F64 are listed in the one error beside the other faults
+    (python/vosti_kernels/checkpoint.py:61-62 takes BF16 only; F32 is kept here as stored)."""
+    from vosti_b200.weights import check_tensors
+    tensors = {"a": torch.randn(4, 4).half(), "b": torch.randn(4).double(), "c": torch.randn(2).bfloat16(),
+               "i": torch.arange(3, dtype=torch.int16)}
+    (tmp_path / "m").mkdir()
+    write_safetensors(tmp_path / "m" / "model.safetensors", tensors)
+    expected = {"a": WeightSpec((4, 4)), "b": WeightSpec((4,)), "c": WeightSpec((3,)), "i": WeightSpec((3,), integer=True)}
+    for dtype in (torch.bfloat16, torch.float32):
+        with pytest.raises(WeightError) as caught:
+            load_weights(tmp_path / "m", expected, device="cpu", dtype=dtype)
+        assert caught.value.wrong_dtype == [("a", "F16"), ("b", "F64")]
+        assert caught.value.wrong_shape == [("c", (2,), (3,))]
+        assert "a is stored as F16" in str(caught.value) and "BF16 or F32" in str(caught.value)
+    with pytest.raises(WeightError) as caught:
+        check_tensors(tensors, expected)
+    assert [name for name, _ in caught.value.wrong_dtype] == ["a", "b"]
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
@@ -132,8 +150,35 @@ def test_tied_checkpoint_may_carry_a_head(tmp_path):
     tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
     (tmp_path / "m").mkdir()
     write_safetensors(tmp_path / "m" / "model.safetensors", tensors)
-    got = load_weights(tmp_path / "m", expected, device="cpu", dtype=torch.bfloat16, ignore=model.ignorable_weights())
+    got = load_weights(tmp_path / "m", expected, device="cpu", dtype=torch.bfloat16, ignore=model.ignorable_weights(),
+                       aliases=model.tied_weights())
     assert "lm_head.weight" not in got
+
+
+def test_tied_checkpoint_with_a_different_head_is_refused(tmp_path):
+    """`tie_word_embeddings: true` says the head is the embedding table; a folder whose
+    lm_head.weight differs from it contradicts its own configuration
+    (python/vosti_kernels/model_families/qwen3/physical.py:131-134)."""
+    from vosti_b200.models import build_model
+    from vosti_b200.weights import check_tensors
+    model = build_model(model_spec_from_config(TINY_A))
+    expected = model.expected_weights()
+    tensors = draw_tensors(expected, seed=0)
+    head = tensors["model.embed_tokens.weight"].clone()
+    head[3, 5] += 1.0
+    tensors["lm_head.weight"] = head
+    (tmp_path / "m").mkdir()
+    write_safetensors(tmp_path / "m" / "model.safetensors", tensors)
+    with pytest.raises(WeightError) as caught:
+        load_weights(tmp_path / "m", expected, device="cpu", dtype=torch.bfloat16, ignore=model.ignorable_weights(),
+                     aliases=model.tied_weights())
+    assert caught.value.conflicts == [("lm_head.weight", "model.embed_tokens.weight", "holds different values")]
+    assert "lm_head.weight must equal model.embed_tokens.weight" in str(caught.value)
+    with pytest.raises(WeightError):
+        check_tensors(tensors, expected, ignore=model.ignorable_weights(), aliases=model.tied_weights())
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"][:-1]
+    with pytest.raises(WeightError, match="has shape"):
+        check_tensors(tensors, expected, ignore=model.ignorable_weights(), aliases=model.tied_weights())
 
 
 def test_sharded_folder_and_broken_files(tmp_path):

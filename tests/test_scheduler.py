@@ -315,3 +315,87 @@ def test_reuse_counters_do_not_count_a_blocked_admission_twice():
     while sched.has_unfinished():
         run_step(cache, sched)
     assert cache.requests_with_reuse == 1 and cache.reused_prefix_pages == 2
+
+
+def test_a_step_cap_below_one_page_is_refused():
+    """Prompts are cut into whole pages: with a per-step cap below the page size a long prompt
+    could never be scheduled, so such settings are refused when the scheduler is made."""
+    with pytest.raises(ValueError, match="less than one page"):
+        make(num_pages=16, page_size=16, budget=64, chunk=8)
+    with pytest.raises(ValueError, match="less than one page"):
+        make(num_pages=16, page_size=16, budget=12)
+    cache, sched = make(num_pages=16, page_size=16, budget=64, chunk=16)
+    sched.add_request(Request(0, list(range(20)), 2, ignore_eos=True))
+    plan, _ = run_step(cache, sched)
+    assert rows(plan) == [(0, 0, 16, False)]
+    plan, emitted = run_step(cache, sched)
+    assert rows(plan) == [(0, 16, 4, True)] and 0 in emitted
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_host_records_do_not_grow_with_the_number_of_requests(ahead):
+    """A finished request leaves nothing behind but its id and (for the newest few) its record."""
+    import ctypes
+    cache = CacheManager([SPEC], [None], num_pages=16, page_size=4, max_requests=2, prefix_reuse=True)
+    sched = Scheduler(cache, SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=64, keep_finished=5))
+    before = None
+    for i in range(60):
+        sched.add_request(Request(i, [i % 7, 3, 4, 5, 6], 2, eos_token_ids=(9,)))
+        if i % 10 == 3:
+            assert sched.abort(i)
+        for _ in range(2):
+            if not ahead:
+                run_step(cache, sched, lambda r: 9 if r.request.request_id % 3 == 0 else 1)
+                continue
+            if before is not None:
+                sched.commit_ahead(before)
+            plan = sched.plan() if sched.has_unfinished() else None
+            for row in (plan.rows if plan else []):
+                cache.extend(row.request.request_id, row.count)
+            if before is not None:
+                sched.resolve(before, [(9 if r.request.request_id % 3 == 0 else 1) if r.sample else None
+                                       for r in before.rows])
+            before = plan if plan is not None and plan.rows else None
+        assert len(sched._requests) <= 4 and len(cache._handles) <= 4 and len(cache._names) <= 4
+        assert len(sched.finished) <= 5
+    while sched.has_unfinished() or before is not None:
+        if not ahead:
+            run_step(cache, sched)
+        else:
+            sched.commit_ahead(before)
+            sched.resolve(before, [1 if r.sample else None for r in before.rows])
+            before = None
+    assert not sched._requests and not cache._handles and not cache._names
+    assert sched._lib.vh_request_field(sched._h, ctypes.c_int64(1), 0) < 0     # the core forgot it too
+    assert sched.add_request(Request(0, [1], 1, ignore_eos=True)) is AdmissionStatus.DUPLICATE_ID
+    assert sched.release(59) and not sched.release(59)
+    cache.check()
+
+
+def test_state_slots_handed_out_by_the_scheduler_are_reported_for_clearing():
+    """A model with per-request state: every admission, by `begin` or inside the scheduler's
+    plan, and every re-admission after a preemption, puts the slot on the list the step
+    function clears before it runs."""
+    import ctypes
+    from vosti_b200 import host
+    from vosti_b200.parts import StateSpec
+    cache = CacheManager([SPEC], [StateSpec((4,))], num_pages=6, page_size=4, max_requests=2, prefix_reuse=True)
+    assert cache.has_state and not cache.prefix_reuse
+    sched = Scheduler(cache, SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=64))
+    buf = (ctypes.c_int32 * 8)()
+    take = lambda: sorted(buf[:cache._lib.vh_take_fresh_slots(cache._h, buf, 8)])
+    assert take() == []
+    for i in range(2):
+        sched.add_request(Request(i, [1] * 8, 8, ignore_eos=True))
+    plan, _ = run_step(cache, sched)
+    first = {r.request.request_id: cache.slot(r.request.request_id) for r in plan.rows}
+    assert take() == sorted(first.values()) and take() == []
+    fresh, preempted = [], []
+    while sched.has_unfinished():
+        plan, _ = run_step(cache, sched)
+        preempted += plan.preempted
+        fresh += take()
+    assert preempted and len(fresh) >= len(preempted)      # each re-admission was reported again
+    sched.add_request(Request(7, [1] * 3, 1, ignore_eos=True))
+    run_step(cache, sched)
+    assert len(take()) == 1

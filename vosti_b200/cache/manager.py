@@ -153,6 +153,8 @@ class CacheManager:
             for g, (window, layers) in enumerate(zip(windows, layers_of))]
         self._handles: Dict[object, int] = {}
         self._names: Dict[int, object] = {}
+        self._next_handle = 1
+        self._fresh = (ctypes.c_int32 * max_requests)()
         self.live = _LiveView(self)
 
     def __del__(self):
@@ -164,10 +166,34 @@ class CacheManager:
         """The integer the C++ core knows the request by."""
         h = self._handles.get(request_id)
         if h is None:
-            h = len(self._handles) + 1
+            h = self._next_handle
+            self._next_handle += 1
             self._handles[request_id] = h
             self._names[h] = request_id
         return h
+
+    def forget(self, request_id) -> None:
+        """Drop the name of a request that is no longer live, so that what the host keeps does
+        not grow with the number of requests served."""
+        if request_id in self.live:
+            raise ValueError(f"request {request_id!r} is still live")
+        h = self._handles.pop(request_id, None)
+        if h is not None:
+            self._names.pop(h, None)
+
+    def clear_fresh_state(self) -> int:
+        """Zero the state slots that were handed out since the last call, on the current
+        stream. Requests are admitted (and re-admitted after a preemption) inside the C++ core,
+        by `begin` here or by the scheduler's plan; whichever did it, the slot still holds its
+        last tenant's state until this runs, so the step function calls it before every step."""
+        if not self.has_state:
+            return 0
+        count = self._lib.vh_take_fresh_slots(self._h, self._fresh, self.max_requests)
+        for slot in self._fresh[:count]:
+            for cache in self.layer_caches:
+                if cache.state is not None:
+                    cache.state[slot].zero_()
+        return count
 
     def _rid(self, request_id) -> ctypes.c_int64:
         h = self._handles.get(request_id)
@@ -214,10 +240,8 @@ class CacheManager:
             prompt = list(prompt_for_reuse)
             slot = host.check(self._lib.vh_begin(self._h, rid, host.ints(prompt), len(prompt)))
         else:
-            slot = host.check(self._lib.vh_begin(self._h, rid, None, 0))
-        for cache in self.layer_caches:
-            if cache.state is not None:
-                cache.state[slot].zero_()
+            host.check(self._lib.vh_begin(self._h, rid, None, 0))
+        self.clear_fresh_state()
         return self.live[request_id]
 
     def pages_needed(self, request_id, new_tokens: int) -> int:

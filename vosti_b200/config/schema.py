@@ -92,6 +92,8 @@ class ModelSpec:
     final_norm_name: str = "model.norm.weight"
     lm_head_name: str = "lm_head.weight"
     layer_prefix: str = "model.layers.{i}."
+    embedding: PartSpec = PartSpec("table")      # token ids -> hidden rows (parameter: scale)
+    head: PartSpec = PartSpec("linear")          # hidden rows -> logits (parameters: bias, scale, softcap)
     extra: Mapping[str, Any] = field(default_factory=dict)
 
     def validate(self) -> None:

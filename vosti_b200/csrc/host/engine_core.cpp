@@ -216,7 +216,7 @@ struct Residency {
 class CacheCore {
  public:
   CacheCore(int groups, const int* group_windows, int pages, int page, int requests, bool reuse, bool has_state)
-      : page_size(page), num_pages(pages), max_requests(requests) {
+      : page_size(page), num_pages(pages), max_requests(requests), has_state(has_state) {
     for (int g = 0; g < groups; ++g) {
       windows.push_back(group_windows[g]);
       pools.emplace_back(new PagePool(pages));
@@ -261,6 +261,9 @@ class CacheCore {
     }
     const int slot = res.slot;
     live[id] = std::move(res);
+    // A slot of per-request state still holds what its last tenant left: whoever owns the
+    // device storage takes this list before the next step and clears those slots.
+    if (has_state) fresh_slots.push_back(slot);
     return slot;
   }
   int pages_needed(const Residency& res, int new_tokens) const {
@@ -371,6 +374,8 @@ class CacheCore {
   }
 
   int page_size, num_pages, max_requests;
+  bool has_state = false;
+  std::vector<int> fresh_slots;                           // handed out by begin() since they were last taken
   bool prefix_reuse = false;
   std::vector<int> windows;
   std::vector<std::unique_ptr<PagePool>> pools;
@@ -780,6 +785,17 @@ VH_API int vh_live_ids(void* host, int64_t* out, int capacity) {
   return (int)((Host*)host)->cache->live.size();
 }
 VH_API int vh_check(void* host) { return ((Host*)host)->cache->check(); }
+// The state slots begin() handed out since the last call (a slot may appear more than once, and a
+// slot whose admission was rolled back may appear although nobody holds it); the list is cleared.
+VH_API int vh_take_fresh_slots(void* host, int32_t* out, int capacity) {
+  auto& slots = ((Host*)host)->cache->fresh_slots;
+  std::sort(slots.begin(), slots.end());
+  slots.erase(std::unique(slots.begin(), slots.end()), slots.end());
+  const int n = std::min((int)slots.size(), capacity);
+  std::copy(slots.begin(), slots.begin() + n, out);
+  slots.clear();
+  return n;
+}
 
 VH_API int vh_add_request(void* host, int64_t id, const int32_t* prompt, int count, int max_tokens, const int32_t* eos,
                           int n_eos, int ignore_eos, float temperature) {

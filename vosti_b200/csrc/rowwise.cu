@@ -7,10 +7,12 @@
 // ---------------------------------------------------------------- embedding
 // With `source`, row t takes its id from values[source[t]] where source[t] >= 0: a token the
 // sampler of the step before left on the device, which the host has not read yet.
+// `scale` multiplies the row in float32 (1: a plain copy), for architectures that scale
+// their embeddings.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ source,
                                  const int* __restrict__ values, const T* __restrict__ table,
-                                 T* __restrict__ out, int hidden, int vocab, unsigned* status) {
+                                 T* __restrict__ out, int hidden, int vocab, float scale, unsigned* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -24,7 +26,10 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restr
   const T* src = table + (int64_t)id * hidden;
   T* dst = out + (int64_t)t * hidden;
   const int bytes = hidden * (int)sizeof(T);
-  if (bytes % 16 == 0) {
+  if (scale != 1.f) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      dst[i] = bad ? from_f32<T>(0.f) : from_f32<T>(to_f32(src[i]) * scale);
+  } else if (bytes % 16 == 0) {
     const int4* s4 = reinterpret_cast<const int4*>(src);
     int4* d4 = reinterpret_cast<int4*>(dst);
     for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) d4[i] = bad ? make_int4(0, 0, 0, 0) : s4[i];
@@ -34,14 +39,15 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restr
 }
 
 VOSTI_API int vosti_embedding(const int* ids, const int* source, const int* values, const void* table, void* out,
-                              int tokens, int hidden, int vocab, int is_f32, unsigned* status, cudaStream_t stream) {
+                              int tokens, int hidden, int vocab, int is_f32, float scale, unsigned* status,
+                              cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d",
                 tokens, hidden, vocab);
   if (tokens == 0) return VOSTI_OK;
   if (is_f32)
-    vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, (float*)out, hidden, vocab, status);
+    vosti_launch(embedding_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const float*)table, (float*)out, hidden, vocab, scale, status);
   else
-    vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, (bf16*)out, hidden, vocab, status);
+    vosti_launch(embedding_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, ids, source, values, (const bf16*)table, (bf16*)out, hidden, vocab, scale, status);
   VOSTI_LAUNCH_CHECK();
 }
 
@@ -294,5 +300,45 @@ VOSTI_API int vosti_silu_mul(const void* gate_up, void* out, int rows, int inter
     silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, rows, inter);
   else
     silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, rows, inter);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- scale, bias, soft cap
+// out[r, c] = cap(in[r, c] * scale + bias[c]) from a float32 product, rounded once:
+// cap(y) = softcap * tanh(y / softcap) when softcap > 0, else y. `bias` may be null; `out` may
+// be `in` when it is float32. This is what a projection with a bias or an output head with a
+// logit scale or soft cap adds after the product; Qwen3 has none of them and never launches it.
+template <typename TO>
+__global__ void affine_rows_kernel(const float* in, int64_t in_stride, const void* __restrict__ bias, int bias_is_f32,
+                                   TO* out, int64_t out_stride, int width, float scale, float softcap) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* src = in + (int64_t)blockIdx.y * in_stride;
+  TO* dst = out + (int64_t)blockIdx.y * out_stride;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
+    float y = src[c] * scale;
+    if (bias != nullptr) y += load_flex(bias, bias_is_f32, c);
+    if (softcap > 0.f) y = softcap * tanhf(y * inv_cap);
+    dst[c] = from_f32<TO>(y);
+  }
+}
+
+VOSTI_API int vosti_affine_rows(const float* in, int64_t in_stride, const void* bias, int bias_is_f32, void* out,
+                                int64_t out_stride, int out_is_f32, int rows, int width, float scale, float softcap,
+                                cudaStream_t stream) {
+  VOSTI_REQUIRE(rows >= 0 && width > 0 && in_stride >= width && out_stride >= width,
+                "affine_rows: bad sizes rows=%d width=%d", rows, width);
+  VOSTI_REQUIRE(rows <= 65535, "affine_rows: %d rows exceed one launch", rows);
+  VOSTI_REQUIRE(softcap >= 0.f && scale == scale, "affine_rows: softcap must be >= 0 and scale a number");
+  VOSTI_REQUIRE(out_is_f32 || (const void*)in != out, "affine_rows: only a float32 output may overwrite its input");
+  if (rows == 0) return VOSTI_OK;
+  const int blocks = (width + 1023) / 1024 < 1024 ? (width + 1023) / 1024 : 1024;
+  if (out_is_f32)
+    vosti_launch(affine_rows_kernel<float>, dim3(blocks, rows), dim3(256), 0, stream, in, in_stride, bias, bias_is_f32,
+                 (float*)out, out_stride, width, scale, softcap);
+  else
+    vosti_launch(affine_rows_kernel<bf16>, dim3(blocks, rows), dim3(256), 0, stream, in, in_stride, bias, bias_is_f32,
+                 (bf16*)out, out_stride, width, scale, softcap);
   VOSTI_LAUNCH_CHECK();
 }

@@ -63,7 +63,9 @@ class Engine:
         little; the default lets every launch cut its work to fit its shape.
         `async_scheduling`: `step` launches the next step before it reads the last one's tokens,
         so the GPU does not idle while the host plans; the tokens a call returns are then those
-        of the step launched by the call before (one call later than without it)."""
+        of the step launched by the call before (one call later than without it).
+        `cuda_graphs`: decode steps are recorded once per shape and replayed; it is switched
+        off by itself for a model with a part that declares `capture_safe = False`."""
         from .. import ops
         if _is_bfloat16(dtype):
             ops.set_invariance(batch_invariant)
@@ -75,7 +77,8 @@ class Engine:
             max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
             prefill_chunk_size=prefill_chunk_size, vocab_size=spec.vocab_size, max_context=spec.max_positions))
         from .graphs import DecodeGraphs
-        self.graphs = DecodeGraphs(self.runner) if cuda_graphs else None
+        # a part that reads a step's host-side values cannot be replayed from a recording
+        self.graphs = DecodeGraphs(self.runner) if cuda_graphs and self.runner.model.capture_safe else None
         self.async_scheduling = bool(async_scheduling)
         self._inflight: Optional[_Launched] = None
         rows = 1 + max(max_num_seqs, 1)
@@ -100,6 +103,11 @@ class Engine:
     def abort(self, request_id) -> bool:
         """End a queued or running request between steps; its pages and slot come back."""
         return self.scheduler.abort(request_id)
+
+    def release(self, request_id) -> bool:
+        """Drop the record of a finished request (`request(id)` no longer finds it). Records
+        are also dropped by age: the scheduler keeps the newest `keep_finished` of them."""
+        return self.scheduler.release(request_id)
 
     def has_unfinished(self) -> bool:
         return self._inflight is not None or self.scheduler.has_unfinished()

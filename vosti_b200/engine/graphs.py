@@ -34,6 +34,9 @@ def _round_up(value: int, multiple: int) -> int:
 
 class DecodeGraphs:
     def __init__(self, runner, max_graphs: int = 12):
+        if not runner.model.capture_safe:
+            raise ValueError("this model has a part that declares capture_safe = False: its decode steps "
+                             "cannot be replayed from a recorded CUDA graph")
         self.runner = runner
         self.max_graphs = max_graphs
         self.graphs: "OrderedDict[tuple, dict]" = OrderedDict()

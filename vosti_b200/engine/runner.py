@@ -61,9 +61,10 @@ class ModelRunner:
         expected = self.model.expected_weights()
         if tensors is None:
             tensors = load_weights(model_dir, expected, device=self.device, dtype=self.dtype,
-                                   ignore=self.model.ignorable_weights())
+                                   ignore=self.model.ignorable_weights(), aliases=self.model.tied_weights())
         else:
-            check_tensors(tensors, expected, ignore=self.model.ignorable_weights())
+            check_tensors(tensors, expected, ignore=self.model.ignorable_weights(),
+                          aliases=self.model.tied_weights())
             if self.dtype == torch.float32:
                 tensors = {k: (v.float() if v.is_floating_point() else v) for k, v in tensors.items()}
         self.model.load(tensors, self.dtype)
@@ -93,6 +94,7 @@ class ModelRunner:
                 kv_bucket: int = 0) -> StepContext:
         """Reserve cache entries for the step's tokens (all requests or none) and copy the
         batch to the device."""
+        self.cache.clear_fresh_state()       # slots the scheduler handed out since the last step
         ctx = build_context(self.staging, self.cache, entries, self.status, self.dtype, extras=extras,
                             min_pages=min_pages, kv_bucket=kv_bucket, position_limit=self.spec.max_positions)
         ctx.feedback_values = self.sampled

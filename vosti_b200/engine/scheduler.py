@@ -42,12 +42,23 @@ class SchedulerConfig:
     prefill_chunk_size: int = 0      # 0: limited by the token budget only
     vocab_size: int = 0              # 0: prompt tokens are not range-checked here
     max_context: int = 0             # 0: no limit
+    keep_finished: int = 1024        # records of finished requests kept for `finished[...]`; older ones go
 
-    def validate(self) -> None:
+    def validate(self, page_size: int = 0) -> None:
         if self.max_num_seqs <= 0 or self.max_num_batched_tokens <= 0:
             raise ValueError("max_num_seqs and max_num_batched_tokens must be positive")
         if self.prefill_chunk_size < 0:
             raise ValueError("prefill_chunk_size must be >= 0")
+        if self.keep_finished < 0:
+            raise ValueError("keep_finished must be >= 0")
+        # A prompt longer than a step's cap is cut into whole pages; a cap below one page would
+        # leave nothing to schedule for it.
+        cap = min(self.max_num_batched_tokens, self.prefill_chunk_size or self.max_num_batched_tokens)
+        if page_size and cap < page_size:
+            raise ValueError(f"a step may take at most {cap} tokens of a prompt (the smaller of "
+                             f"max_num_batched_tokens={self.max_num_batched_tokens} and prefill_chunk_size="
+                             f"{self.prefill_chunk_size or 'unset'}), which is less than one page of {page_size} "
+                             f"tokens: prompts are cut into whole pages, so raise it to at least {page_size}")
 
 
 @dataclass
@@ -80,7 +91,7 @@ class Scheduler:
     what the core decides."""
 
     def __init__(self, cache: CacheManager, config: SchedulerConfig):
-        config.validate()
+        config.validate(cache.page_size)
         self.cache, self.config = cache, config
         self._lib, self._h = host.library(), cache._h
         self._lib.vh_configure_scheduler(self._h, config.max_num_seqs, config.max_num_batched_tokens,
@@ -144,9 +155,29 @@ class Scheduler:
             return False
         if not self._lib.vh_abort(self._h, ctypes.c_int64(self.cache.handle_of(request_id))):
             return False
-        request.finished, request.finish_reason = True, "aborted"
-        self.finished[request_id] = request
+        self._retire(request, "aborted")
         return True
+
+    def _retire(self, request: Request, reason: Optional[str] = None) -> None:
+        """A request has ended and its last token has been handed out: keep its record among the
+        `keep_finished` newest ones and drop everything else the host holds for it (the core's
+        copy of its tokens, its handle), so that a long-lived engine does not grow."""
+        if reason is not None:
+            request.finished, request.finish_reason = True, reason
+        rid = request.request_id
+        if self._requests.pop(rid, None) is None:
+            return
+        self.finished[rid] = request
+        while len(self.finished) > self.config.keep_finished:
+            del self.finished[next(iter(self.finished))]
+        h = self.cache._handles.get(rid)
+        if h is not None:
+            self._lib.vh_forget(self._h, ctypes.c_int64(h))
+            self.cache.forget(rid)
+
+    def release(self, request_id) -> bool:
+        """Drop the record of a finished request."""
+        return self.finished.pop(request_id, None) is not None
 
     def has_unfinished(self) -> bool:
         return bool(self._lib.vh_unfinished(self._h))
@@ -167,9 +198,8 @@ class Scheduler:
             plan.preempted.append(request.request_id)
         for h in self._side2[:n_drop.value]:
             request = self._requests[names[h]]
-            request.finished, request.finish_reason = True, "capacity"
-            self.finished[request.request_id] = request
             plan.dropped.append(request.request_id)
+            self._retire(request, "capacity")
         rows = self._rows
         for i in range(n):
             request = self._requests[names[self._ids[i]]]
@@ -198,8 +228,7 @@ class Scheduler:
             request.generated.append(tokens[i])
             emitted[request.request_id] = tokens[i]
             if finished[i]:
-                request.finished, request.finish_reason = True, _FINISH[finished[i]]
-                self.finished[request.request_id] = request
+                self._retire(request, _FINISH[finished[i]])
         return emitted
 
     # ------------------------------------------------------------ the commit in two halves
@@ -219,9 +248,8 @@ class Scheduler:
             request.computed += row.count
             if row.sample:
                 request.generated.append(self.PENDING)
-                if state[i]:
+                if state[i]:       # ended by length; its record is retired when its token is resolved
                     request.finished, request.finish_reason = True, _FINISH[state[i]]
-                    self.finished[request.request_id] = request
         return list(state[:count])
 
     def resolve(self, plan: StepPlan, sampled: Sequence[Optional[int]]) -> Dict[object, int]:
@@ -239,7 +267,6 @@ class Scheduler:
             index = row.start + row.count - len(request.prompt_tokens)
             request.generated[index] = tokens[i]
             emitted[request.request_id] = tokens[i]
-            if finished[i] and not request.finished:
-                request.finished, request.finish_reason = True, _FINISH[finished[i]]
-                self.finished[request.request_id] = request
+            if finished[i]:
+                self._retire(request, None if request.finished else _FINISH[finished[i]])
         return emitted

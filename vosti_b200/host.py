@@ -54,7 +54,7 @@ def library() -> ctypes.CDLL:
                      "vh_trim", "vh_publish", "vh_finish", "vh_length", "vh_slot", "vh_residency_field",
                      "vh_block_row", "vh_free_slots", "vh_live_ids", "vh_check", "vh_add_request", "vh_abort",
                      "vh_unfinished", "vh_queue", "vh_plan", "vh_commit", "vh_commit_ahead", "vh_resolve", "vh_request_field", "vh_request_tokens",
-                     "vh_forget", "vh_step_extend", "vh_step_fill"):
+                     "vh_forget", "vh_step_extend", "vh_step_fill", "vh_take_fresh_slots"):
             getattr(lib, name).argtypes = None      # variadic-style calls; handles are wrapped below
         _LIB = lib
     return _LIB

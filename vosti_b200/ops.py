@@ -88,9 +88,9 @@ def _contig(*tensors):
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
-              feedback: Optional[tuple] = None) -> torch.Tensor:
-    """table[ids]. `feedback` = (source, values), int32: row t takes values[source[t]] as its id
-    where source[t] >= 0 (a token sampled on the device that the host has not read yet)."""
+              feedback: Optional[tuple] = None, scale: float = 1.0) -> torch.Tensor:
+    """table[ids] * scale. `feedback` = (source, values), int32: row t takes values[source[t]] as
+    its id where source[t] >= 0 (a token sampled on the device that the host has not read yet)."""
     _contig(ids, table)
     source, values = feedback if feedback is not None else (None, None)
     if source is not None:
@@ -98,14 +98,20 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
         assert source.shape[0] == ids.shape[0] and source.dtype == values.dtype == torch.int32
     out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
     _check(library().vosti_embedding(_p(ids), _p(source), _p(values), _p(table), _p(out), ids.shape[0], table.shape[1],
-                                     table.shape[0], _is_f32(table), _p(status), _stream()), "embedding")
+                                     table.shape[0], _is_f32(table), ctypes.c_float(scale), _p(status), _stream()),
+           "embedding")
     return out
+
+
+RMSNORM_PARTIAL_MAX_WIDTH = 24576    # floats of shared memory the split-summing norm keeps a row in
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
             residual: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None):
     """out = rmsnorm(x [+ residual]) * weight; with `residual` the sum is written to
     `residual_out` (which may be `residual` itself). Returns (out, residual_out)."""
+    if isinstance(x, PartialSum) and x.width > RMSNORM_PARTIAL_MAX_WIDTH:
+        x = x.materialize()          # wider than the fused kernel's row buffer: sum the splits first
     if isinstance(x, PartialSum):
         x.check()
         _contig(weight, residual, residual_out)
@@ -126,6 +132,23 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
                                    _p(residual_out), rows, x.shape[-1], ctypes.c_float(eps), flag,
                                    _stream()), "rmsnorm")
     return out, residual_out
+
+
+def affine_rows(x: torch.Tensor, *, bias: Optional[torch.Tensor] = None, scale: float = 1.0, softcap: float = 0.0,
+                out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """cap(x * scale + bias) per row from a float32 product, rounded once to `out_dtype`:
+    cap(y) = softcap * tanh(y / softcap) when softcap > 0. A float32 result overwrites x."""
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("affine_rows takes a float32 [rows, width] matrix with unit inner stride")
+    _contig(bias)
+    if bias is not None and bias.numel() != x.shape[1]:
+        raise KernelError(f"affine_rows: bias has {bias.numel()} entries, the rows have {x.shape[1]}")
+    out = x if out_dtype == torch.float32 else torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _check(library().vosti_affine_rows(_p(x), ctypes.c_int64(x.stride(0)), _p(bias),
+                                       0 if bias is None else _is_f32(bias), _p(out), ctypes.c_int64(out.stride(0)),
+                                       _is_f32(out), x.shape[0], x.shape[1], ctypes.c_float(scale),
+                                       ctypes.c_float(softcap), _stream()), "affine_rows")
+    return out
 
 
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:

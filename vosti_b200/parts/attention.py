@@ -7,7 +7,9 @@ rotated) and values are stored in the cache before the layer's attention, so a q
 reads its own key through the cache; attention with scale `scale`, causal, optionally
 limited to a window; output projection. Sizes and constants are parameters of the spec:
 num_heads, num_kv_heads, head_dim, scale, window (0 = all keys), head_norm_eps (None =
-no head norm).
+no head norm), qkv_bias and o_bias (false for Qwen3, whose configuration must say
+attention_bias=false; true adds `{q,k,v}_proj.bias` / `o_proj.bias` to the tensors the part
+asks for, added to the float32 products before they are rounded).
 """
 from __future__ import annotations
 
@@ -39,7 +41,8 @@ class Attention(Mixer):
             raise ConfigError(f"attention: head_dim {self.d} must be a multiple of 16, at most 256")
         if self.window < 0:
             raise ConfigError("attention: window must be >= 0")
-        self.w_qkv = self.w_q = self.w_o = self.q_norm = self.k_norm = None
+        self.qkv_bias, self.o_bias = bool(spec.get("qkv_bias", False)), bool(spec.get("o_bias", False))
+        self.w_qkv = self.w_q = self.w_o = self.q_norm = self.k_norm = self.b_qkv = self.b_o = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, nq, nkv, d = self.hidden_size, self.nq, self.nkv, self.d
@@ -50,6 +53,11 @@ class Attention(Mixer):
         if self.head_norm_eps is not None:
             specs["q_norm.weight"] = WeightSpec((d,), init="norm", std=0.1)
             specs["k_norm.weight"] = WeightSpec((d,), init="norm", std=0.1)
+        if self.qkv_bias:
+            specs.update({"q_proj.bias": WeightSpec((nq * d,)), "k_proj.bias": WeightSpec((nkv * d,)),
+                          "v_proj.bias": WeightSpec((nkv * d,))})
+        if self.o_bias:
+            specs["o_proj.bias"] = WeightSpec((h,))
         return specs
 
     def load(self, tensors, dtype):
@@ -62,6 +70,10 @@ class Attention(Mixer):
         # or (tile-packed weight) the whole product, whose k and v are then dropped
         self.w_q = w_qkv[: self.nq * self.d] if self.w_qkv is w_qkv else None
         self.w_o = prepare_weight(tensors["o_proj.weight"], dtype)
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors[f"{p}_proj.bias"].float() for p in "qkv"]).contiguous()
+        if self.o_bias:
+            self.b_o = tensors["o_proj.bias"]
         if self.head_norm_eps is not None:
             self.q_norm, self.k_norm = tensors["q_norm.weight"], tensors["k_norm.weight"]
             if self.q_norm.dtype != self.k_norm.dtype:
@@ -82,18 +94,19 @@ class Attention(Mixer):
         common = dict(nq=self.nq, head_dim=self.d, page_size=group.page_size, q_norm_w=self.q_norm, eps=eps, cos=cos, sin=sin,
                       positions=ctx.positions, status=ctx.status)
         if writes_cache:
-            qkv = linear(ctx, x, self.w_qkv, allow_partial=True)   # summed inside qkv_post
+            qkv = linear(ctx, x, self.w_qkv, allow_partial=True, bias=self.b_qkv)   # summed inside qkv_post
             q = ops.qkv_post(qkv, cache.k, cache.v, nkv=self.nkv, k_norm_w=self.k_norm,
                              slot_mapping=group.slot_mapping, **common)
         elif self.w_q is not None:
-            q = ops.qkv_post(linear(ctx, x, self.w_q), None, None, nkv=0, k_norm_w=None,
+            bias = None if self.b_qkv is None else self.b_qkv[: self.nq * self.d]
+            q = ops.qkv_post(linear(ctx, x, self.w_q, bias=bias), None, None, nkv=0, k_norm_w=None,
                              slot_mapping=None, **common)
         else:
-            q = ops.qkv_post(linear(ctx, x, self.w_qkv, allow_partial=True), None, None, nkv=self.nkv,
+            q = ops.qkv_post(linear(ctx, x, self.w_qkv, allow_partial=True, bias=self.b_qkv), None, None, nkv=self.nkv,
                              k_norm_w=self.k_norm, slot_mapping=None, **common)
         attn = ops.attention(ctx, q, cache.k, cache.v, group, nq=self.nq, nkv=self.nkv, head_dim=self.d,
                              scale=self.scale, window=self.window)
-        return linear(ctx, attn, self.w_o, allow_partial=True)       # summed by the norm that follows
+        return linear(ctx, attn, self.w_o, allow_partial=True, bias=self.b_o)   # summed by the norm that follows
 
 
 register_part("mixer", "attention", Attention, replace=True)

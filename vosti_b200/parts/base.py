@@ -11,6 +11,14 @@ them in `load`, and computes in `forward`. No part knows which model it is in.
                    of fixed size (`state_spec`).
 * FeedForward:     forward(ctx, x) -> y
 * Arrangement:     how a block wires mixer, feed-forward and norms around the residual.
+* Embedding:       forward(ctx, tokens, feedback) -> hidden rows; `table()` for a tied head
+* Head:            forward(ctx, x) -> float32 logits
+
+A part whose `forward` reads the step's host-side copies (`ctx.host_q_lens`,
+`ctx.host_kv_lens`, `ctx.host_state_slots`), or lets the host decide anything from a step's
+values, sets `capture_safe = False`: a CUDA graph would replay the launches of the step it
+was recorded in. The engine replays decode steps as graphs only for models all of whose
+parts are capture-safe.
 
 The reference has the same roles as closed Rust records
 (src/boundary/dense_swiglu_decoder.rs:18-24, 96-106).
@@ -48,6 +56,8 @@ class StateSpec:
 
 
 class Part:
+    capture_safe = True     # False: this part's launches depend on host-side values of the step
+
     def __init__(self, spec: PartSpec, hidden_size: int):
         self.spec = spec
         self.hidden_size = hidden_size
@@ -102,14 +112,46 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids to rows of the hidden width. `feedback` = (source, values) names tokens to take
+    from a device array instead (see ops.embedding)."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int):
+        super().__init__(spec, hidden_size)
+        self.vocab_size = vocab_size
+
+    def forward(self, ctx, tokens, feedback=None):
+        raise NotImplementedError
+
+    def table(self) -> Optional[torch.Tensor]:
+        """The [vocab, hidden] tensor a tied output head multiplies with, or None if this
+        embedding has no such table."""
+        return None
+
+
+class Head(Part):
+    """Final hidden rows to float32 logits [rows, vocab]. `load` gets `tied`, the embedding's
+    table, when the model ties them (then `weight_specs` must not ask for a matrix)."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int, tied: bool):
+        super().__init__(spec, hidden_size)
+        self.vocab_size, self.tied = vocab_size, tied
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, tied: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+    def forward(self, ctx, x):
+        raise NotImplementedError
+
+
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
-    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {},
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {}, "embedding": {}, "head": {},
 }
 
 
 def register_part(role: str, kind: str, factory: Callable, *, replace: bool = False) -> None:
     """Register `factory` for parts of `role` ('norm', 'position', 'mixer', 'feed_forward',
-    'arrangement') with the given kind."""
+    'arrangement', 'embedding', 'head') with the given kind."""
     if role not in _REGISTRIES:
         raise ConfigError(f"unknown part role '{role}'; roles: {sorted(_REGISTRIES)}")
     if kind in _REGISTRIES[role] and not replace:
@@ -139,10 +181,19 @@ def build_position(spec: Optional[PartSpec], hidden_size: int, head_dim: int) ->
 
 
 def build_mixer(spec: PartSpec, hidden_size: int, position_spec: Optional[PartSpec]) -> Mixer:
+    """The mixer with its position encoding, which is built for the mixer's `head_dim` parameter
+    or, for a mixer without heads, for the hidden width."""
     factory = part_factory("mixer", spec.kind)
-    head_dim = spec.get("head_dim", 0)
-    position = build_position(position_spec, hidden_size, head_dim) if head_dim else None
-    return factory(spec, hidden_size, position)
+    width = spec.get("head_dim", 0) or hidden_size
+    return factory(spec, hidden_size, build_position(position_spec, hidden_size, width))
+
+
+def build_embedding(spec: PartSpec, hidden_size: int, vocab_size: int) -> Embedding:
+    return part_factory("embedding", spec.kind)(spec, hidden_size, vocab_size)
+
+
+def build_head(spec: PartSpec, hidden_size: int, vocab_size: int, tied: bool) -> Head:
+    return part_factory("head", spec.kind)(spec, hidden_size, vocab_size, tied)
 
 
 def build_feed_forward(spec: Optional[PartSpec], hidden_size: int) -> Optional[FeedForward]:

@@ -33,11 +33,19 @@ def prepare_weight(w: torch.Tensor, serving_dtype: torch.dtype):
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
-           row_index: Optional[torch.Tensor] = None, allow_partial: bool = False):
-    """y = x @ w.T. With `allow_partial` the result may come back as an `ops.PartialSum` (the
-    K splits not yet summed) for a consumer that adds them itself; the caller must hand it to
-    such a consumer, or to `ops.materialize`, before any other product runs."""
+           row_index: Optional[torch.Tensor] = None, allow_partial: bool = False,
+           bias: Optional[torch.Tensor] = None):
+    """y = x @ w.T (+ bias). With `allow_partial` the result may come back as an `ops.PartialSum`
+    (the K splits not yet summed) for a consumer that adds them itself; the caller must hand it
+    to such a consumer, or to `ops.materialize`, before any other product runs. With a `bias`
+    (a vector of w's row count, float32 or bfloat16) the product is taken in float32, the bias
+    is added there and the sum is rounded once; such a result is never partial."""
     x = ops.materialize(x)
+    if bias is not None:
+        if bias.dim() != 1 or bias.shape[0] != w.shape[0]:
+            raise ops.KernelError(f"linear: bias has shape {tuple(bias.shape)}, the weight has {w.shape[0]} rows")
+        product = linear(ctx, x, w, out_dtype=torch.float32, row_index=row_index)
+        return ops.affine_rows(product, bias=bias, out_dtype=out_dtype or x.dtype)
     if isinstance(w, ops.PackedWeight) and x.dtype != torch.bfloat16:
         raise ops.KernelError("a tile-packed weight serves bfloat16 activations only")
     if uses_tensor_cores(x.dtype, w):
