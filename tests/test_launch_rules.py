@@ -40,8 +40,19 @@ def test_decode_segment_length(lib):
     # many tokens: one segment per request as long as it fits; few tokens: cut finely
     assert lib.vosti_attention_decode_segment_keys(64, nq, nkv, d, 2560) == 2560
     assert lib.vosti_attention_decode_segment_keys(1, nq, nkv, d, 2560) == 128
-    # the choice is a function of the launch's shape, never of a request's place in it
-    assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 2560) == lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 2560)
+    # a pinned length overrides the cost model for every shape of launch, and taking the pin
+    # away gives the launches their own choice back
+    shapes = [(c, n) for c in (1, 8, 64) for n in (600, 2560, 9000)]
+    free = [lib.vosti_attention_decode_segment_keys(c, nq, nkv, d, n) for c, n in shapes]
+    assert len(set(free)) > 1
+    assert lib.vosti_set_decode_segment(576) == 0
+    try:
+        assert {lib.vosti_attention_decode_segment_keys(c, nq, nkv, d, n) for c, n in shapes} == {576}
+        assert lib.vosti_set_decode_segment(100) != 0            # not a multiple of 64: refused, the pin stays
+        assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 2560) == 576
+    finally:
+        assert lib.vosti_set_decode_segment(0) == 0
+    assert [lib.vosti_attention_decode_segment_keys(c, nq, nkv, d, n) for c, n in shapes] == free
 
 
 def test_no_product_is_split_when_one_order_of_arithmetic_is_asked_for(lib):
@@ -53,3 +64,24 @@ def test_no_product_is_split_when_one_order_of_arithmetic_is_asked_for(lib):
     finally:
         lib.vosti_set_fixed_order(0)
     assert lib.vosti_gemm_tc_splits(8, 4096, 12288) > 1
+
+
+def test_weight_bytes_of_a_decode_step_in_closed_form():
+    """What bench.py counts as the weights a decode step must read: every tensor the model
+    expects except the embedding table (read by rows), two bytes each. For the 8B sizes that is
+    13.892 GB of layers + the final norm + 1.245 GB of output head."""
+    import importlib.util
+    import math
+    import os
+    from vosti_b200.config import model_spec_from_config
+    from vosti_b200.models import expected_weights
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    spec = importlib.util.spec_from_file_location("bench_for_test", path)
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for size, (_, config) in bench.SIZES.items():
+        names = expected_weights(model_spec_from_config(config))
+        total = sum(2 * math.prod(w.shape) for name, w in names.items() if name != "model.embed_tokens.weight")
+        assert bench.closed_form_weight_bytes(config) == total, size
+    layers = bench.closed_form_weight_bytes(bench.SIZES["8b"][1]) - 2 * 151936 * 4096
+    assert abs(layers - 13.892e9) < 2e6 and 2 * 151936 * 4096 == 1_244_659_712

@@ -5,8 +5,10 @@ serving process that gave all free GPU memory to its cache pool at start-up, or 
 device memory belongs to another allocator. For them `vosti_gemm_tc_split_static` keeps the
 split-K partial sums in a device array inside the library instead of a workspace the caller
 allocates. This test calls it through its exported C symbol, twice in a row with different
-sizes and data, and checks each result against the ordinary entry point; it also checks that
-sizes beyond the array are refused. It runs last (file name) so that a run that stops at the
+sizes and data (one for each width of token tile the kernel has), and checks each result
+against the ordinary entry point; it also checks that sizes beyond the array are refused and
+that, after the warm-up call the header asks for, a call leaves the free device memory as it
+found it. It runs last (file name) so that a run that stops at the
 first failure has already run every other test, and it passes alone in a fresh process too.
 """
 import ctypes
@@ -46,7 +48,8 @@ def test_static_scratch_product_matches_the_ordinary_entry_point():
     torch.manual_seed(0)
     # two calls in a row: the second reuses the array the first one filled
     for tokens, features, k, out_dtype in [(8, 4096, 4096, torch.bfloat16), (70, 1024, 12288, torch.float32),
-                                           (1, 6144, 4096, torch.bfloat16)]:
+                                           (1, 6144, 4096, torch.bfloat16), (40, 2048, 8192, torch.bfloat16),
+                                           (64, 1536, 4096, torch.float32)]:
         assert lib.vosti_gemm_tc_splits(tokens, features, k) > 1           # the scratch is really used
         x = torch.randn(tokens, k, device=device).bfloat16()
         w = (torch.randn(features, k, device=device) / math.sqrt(k)).bfloat16()
@@ -57,6 +60,42 @@ def test_static_scratch_product_matches_the_ordinary_entry_point():
         exact = x.double() @ w.double().T
         assert torch.allclose(got.double(), exact, atol=2e-2, rtol=2e-2)
     torch.cuda.synchronize()
+
+
+def test_static_scratch_calls_leave_device_memory_alone():
+    """After one warm-up call on the device, calls neither take nor give back device memory:
+    the driver's count of free bytes and torch's own count of what it holds stay the same
+    across them (inputs and outputs are made before the counts are read)."""
+    from vosti_b200 import ops
+    device = torch.device("cuda:0")
+    ops.require_device(device)
+    lib = _library()
+    cases = []
+    for tokens, features, k in [(8, 4096, 4096), (48, 1024, 8192), (100, 1024, 4096)]:
+        x = torch.randn(tokens, k, device=device).bfloat16()
+        w = (torch.randn(features, k, device=device) / math.sqrt(k)).bfloat16()
+        y = torch.empty((tokens, features), dtype=torch.bfloat16, device=device)
+        cases.append((x, w, y))
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(x, w, y):
+        return lib.vosti_gemm_tc_split_static(
+            ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+            x.shape[0], w.shape[0], x.shape[1], 0, ctypes.c_void_p(status.data_ptr()), stream)
+
+    for case in cases:                     # the warm-up calls: every tile width's kernel is loaded and set up
+        assert call(*case) == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(device)
+    held_before = torch.cuda.memory_reserved(device)
+    for _ in range(3):
+        for case in cases:
+            assert call(*case) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(device)
+    assert free_after == free_before and torch.cuda.memory_reserved(device) == held_before
+    assert status.item() == 0
 
 
 def test_static_scratch_refuses_sizes_beyond_the_array():

@@ -16,8 +16,15 @@
 //    (splits = vosti_gemm_tc_splits(tokens, features, k)); anything else is refused with
 //    VOSTI_BAD_ARGUMENT and a message in vosti_last_error().
 //  * It calls no cudaMalloc, cudaFree or allocating library routine.
-//  * The first call on a device looks up the array's device address (once per device, with
-//    that device current). Make that first call before any stream capture begins.
+//  * The first call on a device is a set-up call: it looks up the array's device address (once
+//    per device, with that device current) and raises the kernel's shared-memory limit; under
+//    CUDA's default lazy module loading it is also the moment the driver places the kernel's
+//    code and the 8 MiB array in device memory. The kernel exists in three widths of token
+//    tile (1..32, 33..64 and 65..128 tokens), each loaded at its first use. So make one warm-up
+//    call per device for each of those ranges you will use, while device memory is still
+//    available, before the process hands its free memory away and before any stream capture
+//    begins; every later call changes the amount of free device memory by nothing. Two threads making the first call on one device at once both
+//    store the same address, which is harmless.
 //  * All calls share the one array and it keeps the last call's contents. Nothing has to
 //    start at zero: every partial sum the reduction reads is written by the same call. Two
 //    calls that overlap on the GPU (different streams without ordering between them) race
