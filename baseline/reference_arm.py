@@ -53,7 +53,10 @@ class ReferenceModel:
     def __init__(self, profile: str, layers: int, token_capacity: int, seed: int = 0):
         import torch
         root = install()
-        sys.path.insert(0, os.path.join(root, "python"))
+        # the checkout's root (for `kernels.triton_kernels`) and its python/ folder (for `vosti_kernels`)
+        for folder in (root, os.path.join(root, "python")):
+            if folder not in sys.path:
+                sys.path.insert(0, folder)
         import vosti_kernels as vk
         from vosti_kernels.graph_overlay import CudaGraphOverlay
         from vosti_kernels.model_families.qwen3 import runtime as qwen3_runtime

@@ -284,6 +284,8 @@ def reference_main(args) -> int:
         }
         print(json.dumps(line))
     except Exception as error:  # the arm must report, not crash: the driver reads this line
+        import traceback
+        traceback.print_exc(file=sys.stderr)
         text = " ".join(f"{type(error).__name__}: {error}".split())
         print(json.dumps({"impl": "reference", "unavailable": text[:600]}))
     return 0
