@@ -618,3 +618,95 @@ print("pairs ok")
     env = dict(os.environ, VOSTI_GEMM_PAIR=pairs, PYTHONPATH=str(root))
     done = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0 and "pairs ok" in done.stdout, done.stderr[-2000:]
+
+
+# ---------------------------------------------------------------- the real vocabulary
+REAL_VOCAB = 151936      # the family's vocabulary: 1,187 feature tiles of 128, no power of two
+
+
+def test_head_product_sampling_and_embedding_at_the_real_vocabulary(dev, status):
+    """The output head on the tensor cores (float32 epilogue) and on the CUDA cores, the
+    sampler and the embedding at 151,936 rows, each against a float64 reference."""
+    from vosti_b200 import ops
+    hidden = 1024
+    gen = torch.Generator(device=dev).manual_seed(5)
+    w = (torch.randn(REAL_VOCAB, hidden, device=dev, generator=gen) / math.sqrt(hidden)).bfloat16()
+    x = torch.randn(9, hidden, device=dev, generator=gen).bfloat16()
+    want = torch.cat([x.double() @ w[i:i + 16384].double().T for i in range(0, REAL_VOCAB, 16384)], dim=1)
+    # a logit that must win although it sits in the last, partial feature tile
+    last = REAL_VOCAB - 3
+    for packed in (False, True):
+        weight = ops.PackedWeight(w) if packed else w
+        logits = ops.gemm_tc(x, weight, status, out_dtype=torch.float32)
+        assert logits.shape == (9, REAL_VOCAB)
+        assert torch.allclose(logits.double(), want, atol=3e-4, rtol=3e-4), (logits.double() - want).abs().max()
+    narrow = ops.gemm_simt(x.float()[:3], w.float()[:, :], status, out_dtype=torch.float32)
+    assert torch.allclose(narrow.double(), want[:3], atol=1e-4, rtol=1e-4)
+    assert ops.sample(logits).tolist() == want.argmax(-1).tolist() or \
+        all(float(want[r].max() - want[r, t]) < 1e-3 for r, t in enumerate(ops.sample(logits).tolist()))
+    logits[4, last] = 100.0
+    logits[5, 0] = logits[5, last] = 90.0                       # a tie across the whole width: the lowest index
+    got = ops.sample(logits).tolist()
+    assert got[4] == last and got[5] == 0
+    temps = torch.tensor([0.0, 0.8, 1.0, 0.5, 0.7, 0.7, 1.5, 0.9, 1.1], device=dev)
+    seeds = torch.arange(9, dtype=torch.int64, device=dev) + 100
+    for index in (0, 1, 2):
+        counters = torch.full((9,), index, dtype=torch.int64, device=dev)
+        drawn = ops.sample(logits, temps, seeds, counters).tolist()
+        assert drawn[0] == got[0] and drawn[4] == last          # greedy row; a row with one overwhelming logit
+        for row in (1, 2, 3, 6, 7, 8):
+            t = float(temps[row])
+            weights = torch.exp((logits[row].double() - logits[row].double().max()) / t)
+            cdf = torch.cumsum(weights, 0).cpu()
+            u = plain.uniform(int(seeds[row]), index) * float(cdf[-1])
+            low = float(cdf[drawn[row] - 1]) if drawn[row] > 0 else 0.0
+            slack = 2e-5 * float(cdf[-1])
+            assert low - slack <= u <= float(cdf[drawn[row]]) + slack, (row, index)
+    ids = torch.tensor([0, last, REAL_VOCAB - 1, 77777, 151935 - 128], dtype=torch.int32, device=dev)
+    assert torch.equal(ops.embedding(ids, w, status), w[ids.long()])
+    assert status.item() == 0
+    ops.embedding(torch.tensor([REAL_VOCAB], dtype=torch.int32, device=dev), w, status)
+    assert status.item() == 1                                   # one past the end is reported, not read
+    status.zero_()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_affine_rows(dev, dtype):
+    """cap(x * scale + bias) from a float32 product, rounded once."""
+    from vosti_b200 import ops
+    x = torch.randn(7, 1531, device=dev) * 4
+    bias = torch.randn(1531, device=dev)
+    for scale, cap, b in [(1.0, 0.0, bias), (0.5, 3.0, None), (2.0, 5.0, bias.bfloat16()), (1.0, 0.0, None)]:
+        want = x.double() * scale + (0 if b is None else b.double())
+        if cap > 0:
+            want = cap * torch.tanh(want / cap)
+        got = ops.affine_rows(x.clone(), bias=b, scale=scale, softcap=cap, out_dtype=dtype)
+        assert got.dtype == dtype
+        if dtype == torch.float32:
+            assert torch.allclose(got.double(), want, atol=1e-5, rtol=1e-5)
+        else:
+            assert torch.equal(got, want.float().bfloat16()) or torch.allclose(got.double(), want, atol=4e-2, rtol=1e-2)
+    with pytest.raises(ops.KernelError):
+        ops.affine_rows(x.bfloat16())
+    with pytest.raises(ops.KernelError):
+        ops.affine_rows(x, bias=bias[:-1])
+
+
+def test_split_sums_wider_than_the_fused_norm_are_summed_first(dev, status):
+    """The norm that adds a product's K splits keeps a row in shared memory; a wider row is
+    summed by the reduction kernel first and normed by the plain kernel, instead of refused."""
+    from vosti_b200 import ops
+    width, splits = 24576 + 512, 3
+    pieces = torch.randn(splits, 4, width, device=dev)
+    residual = torch.randn(4, width, device=dev).bfloat16()
+    weight = (1 + 0.1 * torch.randn(width, device=dev)).bfloat16()
+    # (the product's own split rule never splits so wide a result; the sums are handed over by hand)
+    partial = ops.PartialSum(pieces, splits, 4, width, torch.bfloat16, status)
+    assert partial.width > ops.RMSNORM_PARTIAL_MAX_WIDTH
+    res = residual.clone()
+    out, new_res = ops.rmsnorm(partial, weight, 1e-6, residual=res, residual_out=res)
+    product = pieces.sum(0).bfloat16()
+    want_n, want_r = plain.add_rms_norm(product.float().cpu(), residual.float().cpu(), weight.float().cpu(), 1e-6)
+    assert torch.allclose(new_res.float().cpu(), want_r, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(out.float().cpu(), want_n, atol=3e-2, rtol=3e-2)
+    assert status.item() == 0
