@@ -710,3 +710,32 @@ def test_split_sums_wider_than_the_fused_norm_are_summed_first(dev, status):
     assert torch.allclose(new_res.float().cpu(), want_r, atol=3e-2, rtol=3e-2)
     assert torch.allclose(out.float().cpu(), want_n, atol=3e-2, rtol=3e-2)
     assert status.item() == 0
+
+
+def test_weights_requested_ahead_change_no_value(dev, status):
+    """The split-summing norm with a hint (it asks for the next product's weights to be brought
+    into L2 from blocks added to its launch) gives the bits it gives without one; a hint is
+    taken by one launch only; what is not a tile-packed weight is no hint."""
+    import ctypes
+    from vosti_b200 import ops
+    x = torch.randn(8, 4096, device=dev).bfloat16()
+    w = (torch.randn(4096, 4096, device=dev) / 64).bfloat16()
+    nxt = ops.PackedWeight((torch.randn(6144, 4096, device=dev) / 64).bfloat16())
+    gamma = (1 + 0.1 * torch.randn(4096, device=dev)).bfloat16()
+    residual = torch.randn(8, 4096, device=dev).bfloat16()
+    outs = []
+    for hint in (None, nxt, w, nxt):
+        partial = ops.gemm_tc(x, w, status, allow_partial=True)
+        assert isinstance(partial, ops.PartialSum)
+        res = residual.clone()
+        assert ops.hint_prefetch(hint) == (hint is nxt and ops.PREFETCH)
+        out, new_res = ops.rmsnorm(partial, gamma, 1e-6, residual=res, residual_out=res)
+        outs.append((out.clone(), new_res.clone()))
+    for out, res in outs[1:]:
+        assert torch.equal(out, outs[0][0]) and torch.equal(res, outs[0][1])
+    lib = ops.library()
+    assert lib.vosti_hint_prefetch(ctypes.c_void_p(nxt.data.data_ptr() + 8), ctypes.c_longlong(1 << 20)) != 0
+    assert b"16-byte" in lib.vosti_last_error()
+    assert lib.vosti_hint_prefetch(None, ctypes.c_longlong(0)) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0

@@ -120,6 +120,31 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 int vosti_pdl_enabled();
 
+// ---------------------------------------------------------------- weights requested ahead
+// A decode step alternates between products that stream weights from HBM and short kernels
+// (norms) during which HBM has little to do. The host may name the weight range the next product
+// will stream (vosti_hint_prefetch); the launcher of such a short kernel takes the hint and lets
+// blocks added to the launch ask for that range
+// to be brought into L2 (cp.async.bulk.prefetch.L2: no destination, no completion to wait for),
+// so that the product finds the start of its weights on the chip. Values never change by it.
+struct VostiPrefetch {
+  const char* ptr;       // 16-byte aligned, or null: nothing to ask for
+  long long bytes;       // a multiple of 16
+};
+VostiPrefetch vosti_take_prefetch();     // the pending hint, which is cleared (errors.cu)
+constexpr long long PREFETCH_PIECE = 16384;
+
+// Worker `worker` of `workers` requests its share of the range, one piece per instruction.
+__device__ __forceinline__ void l2_prefetch_share(VostiPrefetch p, long long worker, long long workers) {
+  if (p.ptr == nullptr) return;
+  const long long pieces = (p.bytes + PREFETCH_PIECE - 1) / PREFETCH_PIECE;
+  for (long long i = worker; i < pieces; i += workers) {
+    const long long at = i * PREFETCH_PIECE;
+    const unsigned size = (unsigned)(p.bytes - at < PREFETCH_PIECE ? p.bytes - at : PREFETCH_PIECE);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ptr + at), "r"(size) : "memory");
+  }
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t vosti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                 Args... args) {

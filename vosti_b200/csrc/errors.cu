@@ -47,3 +47,23 @@ int g_vosti_fixed_order = 0;
 
 VOSTI_API void vosti_set_fixed_order(int enabled) { g_vosti_fixed_order = enabled ? 1 : 0; }
 VOSTI_API int vosti_fixed_order() { return g_vosti_fixed_order; }
+
+// The weight range the next product will stream (see common.cuh): set by the host just before it
+// launches a kernel that can request it into L2, taken by that kernel's launcher. bytes 0 or a
+// null pointer clears the hint.
+static thread_local VostiPrefetch g_prefetch = {nullptr, 0};
+
+VOSTI_API int vosti_hint_prefetch(const void* ptr, long long bytes) {
+  g_prefetch = {nullptr, 0};
+  if (ptr == nullptr || bytes < 16) return VOSTI_OK;
+  VOSTI_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "hint_prefetch: the range must start on a 16-byte boundary");
+  g_prefetch.ptr = (const char*)ptr;
+  g_prefetch.bytes = bytes & ~15ll;
+  return VOSTI_OK;
+}
+
+VostiPrefetch vosti_take_prefetch() {
+  const VostiPrefetch taken = g_prefetch;
+  g_prefetch = {nullptr, 0};
+  return taken;
+}

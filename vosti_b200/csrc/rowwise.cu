@@ -157,15 +157,27 @@ VOSTI_API int vosti_rmsnorm(const void* x, const void* residual, const void* wei
   VOSTI_LAUNCH_CHECK();
 }
 
+constexpr int PREFETCH_LANES = 64;      // threads of a prefetch block that issue requests
+constexpr int PREFETCH_BLOCKS = 48;     // blocks added to a launch that carries a prefetch hint
+
 // The same norm fed by the float32 partial sums of a split-K product: x[t, i] is the sum of
 // `splits` planes of [rows, width] taken in split order; it is not rounded before the add.
 template <typename T, int BLOCK>
 __global__ void __launch_bounds__(BLOCK)
 rmsnorm_partial_kernel(const float* __restrict__ partial, int splits, int64_t plane, const T* __restrict__ residual,
                        const void* __restrict__ weight, int weight_is_f32, T* __restrict__ out,
-                       T* __restrict__ residual_out, int width, float eps) {
+                       T* __restrict__ residual_out, int rows, int width, float eps, VostiPrefetch ahead) {
   __shared__ float scratch[32];
   extern __shared__ float row_sum[];                       // the summed row, kept for the second pass
+  if ((int)blockIdx.x >= rows) {
+    // a block beyond the rows: it only asks for the next product's weights and leaves; it reads
+    // nothing another kernel writes, so it does not wait for the kernel before this one
+    pdl_launch_dependents();
+    if (threadIdx.x < PREFETCH_LANES)
+      l2_prefetch_share(ahead, (long long)((int)blockIdx.x - rows) * PREFETCH_LANES + threadIdx.x,
+                        (long long)((int)gridDim.x - rows) * PREFETCH_LANES);
+    return;
+  }
   // the norm weights do not depend on the kernel before this one: read them while it still runs
   constexpr int PRELOAD = 4;
   float w_pre[PRELOAD];
@@ -252,26 +264,28 @@ VOSTI_API int vosti_rmsnorm_partial(const float* partial, int splits, const void
   VOSTI_REQUIRE(rows >= 0 && width > 0 && splits >= 1, "rmsnorm_partial: bad sizes rows=%d width=%d splits=%d", rows, width, splits);
   VOSTI_REQUIRE(eps > 0.f, "rmsnorm_partial: eps must be positive");
   VOSTI_REQUIRE(width <= 24576, "rmsnorm_partial: width %d does not fit the row buffer", width);
+  const VostiPrefetch ahead = vosti_take_prefetch();
   if (rows == 0) return VOSTI_OK;
   VOSTI_REQUIRE(out != residual && out != residual_out, "rmsnorm_partial: out must not alias another operand");
   const int64_t plane = (int64_t)rows * width;
   const size_t smem = (size_t)width * sizeof(float);
+  const dim3 grid(rows + (ahead.ptr != nullptr ? PREFETCH_BLOCKS : 0));
   if (is_f32) {
     static bool configured = false;
     if (!configured) {
       cudaFuncSetAttribute(rmsnorm_partial_kernel<float, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 24576 * 4);
       configured = true;
     }
-    vosti_launch(rmsnorm_partial_kernel<float, 1024>, dim3(rows), dim3(1024), smem, stream, partial, splits, plane,
-                 (const float*)residual, weight, weight_is_f32, (float*)out, (float*)residual_out, width, eps);
+    vosti_launch(rmsnorm_partial_kernel<float, 1024>, grid, dim3(1024), smem, stream, partial, splits, plane,
+                 (const float*)residual, weight, weight_is_f32, (float*)out, (float*)residual_out, rows, width, eps, ahead);
   } else {
     static bool configured = false;
     if (!configured) {
       cudaFuncSetAttribute(rmsnorm_partial_kernel<bf16, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 24576 * 4);
       configured = true;
     }
-    vosti_launch(rmsnorm_partial_kernel<bf16, 1024>, dim3(rows), dim3(1024), smem, stream, partial, splits, plane,
-                 (const bf16*)residual, weight, weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
+    vosti_launch(rmsnorm_partial_kernel<bf16, 1024>, grid, dim3(1024), smem, stream, partial, splits, plane,
+                 (const bf16*)residual, weight, weight_is_f32, (bf16*)out, (bf16*)residual_out, rows, width, eps, ahead);
   }
   VOSTI_LAUNCH_CHECK();
 }

@@ -392,6 +392,34 @@ def gemm_tc(x: torch.Tensor, w, status: torch.Tensor, *, out_dtype: Optional[tor
     return out
 
 
+# Weights requested ahead (see csrc/common.cuh, VostiPrefetch): the norm before a product asks for
+# the start of the product's weights. VOSTI_PREFETCH=0 switches it off. Measured at the 8B sizes,
+# context 2,048: 3.65 instead of 3.76 ms per step at batch 8 with 32 MB per hint (8 MB: 3.71,
+# 96 MB: 3.90, slower than none). Also measured and not kept: asking for the output
+# projection's weights from the head kernel or from the tail of the decode attention (the step
+# got 2 % slower: the requests delay the attention's own loads by more than the projection
+# gains), and asking, per K split, for the k-blocks after those the product's CTAs request by
+# themselves (3.71 ms).
+import os as _os
+PREFETCH = _os.environ.get("VOSTI_PREFETCH", "1") != "0"
+PREFETCH_LIMIT = int(_os.environ.get("VOSTI_PREFETCH_MB", "32")) << 20    # bytes asked for at most per hint
+PREFETCH_MAX_TOKENS = 64         # steps with more tokens keep HBM busy anyway
+
+
+def hint_prefetch(w, limit: Optional[int] = None) -> bool:
+    """Name the weight the next product will stream, for the next kernel that can ask for its
+    first `limit` bytes to be brought into L2 while it runs (the split-summing norm). Only
+    tile-packed weights are taken (their first bytes are the first k-blocks of every feature
+    tile). `None` clears a hint nobody took. Returns whether a hint was set."""
+    lib = library()
+    if w is None or not PREFETCH or not isinstance(w, PackedWeight):
+        lib.vosti_hint_prefetch(None, ctypes.c_longlong(0))
+        return False
+    nbytes = min(w.data.numel() * w.data.element_size(), limit if limit is not None else PREFETCH_LIMIT)
+    _check(lib.vosti_hint_prefetch(_p(w.data), ctypes.c_longlong(nbytes)), "hint_prefetch", kernels=0)
+    return True
+
+
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
     """x[rows] for int32 row indices (the embedding kernel over an activation matrix)."""
     return embedding(rows, x, status)

@@ -83,6 +83,9 @@ class Attention(Mixer):
         if self.position is not None:
             self.position.setup(device, dtype)
 
+    def first_weight(self):
+        return self.w_qkv
+
     def cache_spec(self) -> PagedCacheSpec:
         return PagedCacheSpec(entries=2, heads=self.nkv, width=self.d, window=self.window)
 

@@ -71,6 +71,11 @@ class Part:
     def setup(self, device: torch.device, dtype: torch.dtype) -> None:
         """Build device tables that do not come from the checkpoint."""
 
+    def first_weight(self):
+        """The weight this part's first product streams, if the kernel before it may ask for it
+        to be brought into L2 ahead of time (ops.hint_prefetch), else None."""
+        return None
+
 
 class Norm(Part):
     def forward(self, ctx, x):

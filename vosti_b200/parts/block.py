@@ -46,16 +46,25 @@ class PreNormBlock:
             part.setup(device, dtype)
 
     def forward(self, ctx, hidden, residual, cache, writes_cache=True):
+        # In a step of few tokens a norm leaves HBM idle: it is told which weight the product
+        # after it will stream, so that it can ask for it ahead of time (ops.hint_prefetch).
+        few = ctx.num_tokens <= ops.PREFETCH_MAX_TOKENS
         if residual is None:
             residual = hidden = ops.materialize(hidden)
             normed = self.input_norm.forward(ctx, hidden)
         else:
+            hinted = few and ops.hint_prefetch(self.mixer.first_weight())
             normed, residual = self.input_norm.forward_add(ctx, hidden, residual)
+            if hinted:
+                ops.hint_prefetch(None)
         out = self.mixer.forward(ctx, normed, cache, writes_cache)
         # (a mixer or feed-forward may return its last product as unsummed K splits; the
         # norm that follows adds them, see ops.PartialSum)
         if self.feed_forward is not None:
+            hinted = few and ops.hint_prefetch(self.feed_forward.first_weight())
             normed, residual = self.post_norm.forward_add(ctx, out, residual)
+            if hinted:
+                ops.hint_prefetch(None)
             out = self.feed_forward.forward(ctx, normed)
         return out, residual
 

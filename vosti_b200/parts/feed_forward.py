@@ -48,6 +48,9 @@ class SwiGLU(FeedForward):
         else:
             self.w_gate_up = stacked.contiguous()
 
+    def first_weight(self):
+        return self.w_gate_up
+
     def forward(self, ctx, x):
         if self.fused:
             mlp = ops.gemm_tc(ops.materialize(x), self.w_gate_up, ctx.status, swiglu=True)

@@ -41,6 +41,9 @@ class LinearHead(Head):
             self.weight = prepare_weight(tensors["weight"], dtype)
         self.bias = tensors.get("bias")
 
+    def first_weight(self):
+        return self.weight
+
     def forward(self, ctx, x):
         logits = linear(ctx, x, self.weight, out_dtype=torch.float32)
         if self.bias is not None or self.scale != 1.0 or self.softcap > 0.0:
