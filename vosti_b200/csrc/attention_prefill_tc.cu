@@ -1,27 +1,33 @@
 // Paged causal attention for prompts and portions of prompts on the 5th-generation tensor
 // cores (tcgen05), head sizes 64 and 128, pages of a multiple of 16 tokens, bfloat16:
 //
-//   grid = (query tiles, kv heads, requests). A CTA takes 128 rows of one request and one kv
-//   head, where a row is a (query token, query head of the group) pair, so the query heads
-//   that share a kv head share its K and V tiles. Keys are walked in tiles of 64, aligned to
-//   the absolute key index. Roles, one warpgroup each:
-//     * two softmax warpgroups, one thread per row; the first takes the even tiles, the second
-//       the odd ones. A thread reads its row's scores from tensor memory, does the online
-//       softmax (base 2, float32) and writes P (rounded to bfloat16) to shared memory for the
-//       second MMA, which adds to the group's running product in tensor memory. The maximum
-//       the exponentials are taken against follows the true maximum lazily: only when it
-//       falls behind by more than 8 (P would pass 2^8) is it raised and the running product
-//       scaled down in tensor memory. At the end the two groups' (max, sum, product) are
-//       merged, normalised and stored.
+//   grid = (pairs of query tiles x kv heads, requests), the kv head running fastest, so that
+//   CTAs start in the order of their number of key tiles, longest first, across all heads (the
+//   tail of the launch is then made of the shortest ones). A CTA takes two tiles of 128 rows of
+//   one request and one kv head, where a row is a (query token, query head of the group) pair, so
+//   the query heads that share a kv head share its K and V tiles, and so do the two row tiles.
+//   Keys are walked in tiles of 64, aligned to the absolute key index. Roles, one warpgroup each:
+//     * two softmax warpgroups, one thread per row, one row tile each. A thread reads its row's
+//       scores from tensor memory, does the online softmax (base 2, float32) and writes P
+//       (rounded to bfloat16) to one of its group's two buffers in shared memory for the second
+//       MMA, which adds to the group's running product in tensor memory; with two buffers the
+//       exponentials of a tile overlap the product of the tile before. The maximum the
+//       exponentials are taken against follows the true maximum lazily: only when it falls
+//       behind by more than 8 (P would pass 2^8) is it raised and the running product scaled
+//       down in tensor memory. At the end each thread normalises and stores its row.
 //     * four loader warps: each brings 16 keys of a tile, one TMA box per 64 features of K
-//       and of V straight from the page, into the tensor cores' 128-byte-swizzled layout
-//       (four stages). The query rows come as one 4-D box per 64 features.
+//       and of V straight from the page, into the tensor cores' 128-byte-swizzled layout. A tile
+//       serves both row tiles, so a stage lasts twice as long as a row tile's step and three
+//       stages cover the latency of the copies. The query rows come as one 4-D box per 64
+//       features and row tile.
 //     * four threads (one per warp) issue the MMAs: S = Q K^T (M 128, N 64) into the score
-//       buffer of the tile's group in tensor memory, and P V (M 128, N = head size, V read as
-//       an MN-major operand straight from its [key][feature] rows) accumulating in the group's
-//       product buffer; scores and products, even and odd tiles have a thread each. The scores of a
-//       group's next tile are issued as soon as it has read the last ones.
+//       buffer of the row tile in tensor memory, and P V (M 128, N = head size, V read as
+//       an MN-major operand straight from its [key][feature] rows) accumulating in the row
+//       tile's product buffer; scores and products of each row tile have a thread each. The
+//       scores of a row tile's next key tile are issued as soon as its group has read the last.
 //   Registers move from the loader and MMA warpgroups to the softmax ones (setmaxnreg).
+//   A row's keys are always taken in the same tiles and the same order, by one thread, whatever
+//   the portion and the batch around it: its result does not depend on how the work is cut.
 //
 // Semantics as in attention_prefill.cu (bottom-right causal alignment, optional window,
 // kernels/triton_kernels/fattn_paged.py:176-252): out = acc / l, 0 if l = 0. A box brings
@@ -34,19 +40,19 @@
 
 namespace {
 
-constexpr int ROWS = 128;                 // packed rows per CTA: the MMA's M
+constexpr int ROWS = 128;                 // packed rows per row tile: the MMA's M
+constexpr int ROW_TILES = 2;              // row tiles per CTA, one per softmax warpgroup
 constexpr int KT = 64;                    // keys per tile
 constexpr int GROUP_KEYS = 16;            // keys per loader warp and TMA box
-constexpr int STAGES = 4;                 // K/V tiles in shared memory
 constexpr int THREADS = 512;              // softmax 0, softmax 1, loaders, MMA
 constexpr int MMA_WARP = 12;
 constexpr float LOG2E = 1.4426950408889634f;
 
+template <int D> __host__ __device__ constexpr int kv_stages() { return D == 128 ? 3 : 6; }   // K/V tiles in shared memory
+
 // Byte offset of 16-byte chunk `chunk` (of 8) of row `row` inside a [rows][128 bytes] block
 // with the 128-byte swizzle.
 __device__ __forceinline__ uint32_t swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
-// A barrier among the 256 softmax threads.
-__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -57,7 +63,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             int page_size, int page_shift, int num_pages, int nq, int nkv, float scale_log2,
                             int window, unsigned* status) {
   constexpr int NB = D / 64;                          // 64-element blocks of the head size
-  constexpr int Q_BYTES = NB * ROWS * 128;
+  constexpr int STAGES = kv_stages<D>();
+  constexpr int Q_BYTES = NB * ROWS * 128;            // one row tile of Q
   constexpr int K_BYTES = NB * KT * 128;              // one tile of K; V the same
   constexpr int STAGE_BYTES = 2 * K_BYTES;
   constexpr int P_BYTES = ROWS * 128;                 // [128 rows][64 keys] bfloat16
@@ -66,44 +73,54 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_s = smem;
-  uint8_t* kv_s = q_s + Q_BYTES;
-  uint8_t* p_s = kv_s + STAGES * STAGE_BYTES;
+  uint8_t* q_s = smem;                                // [row tile][NB][128 rows][128 B]
+  uint8_t* kv_s = q_s + ROW_TILES * Q_BYTES;
+  uint8_t* p_s = kv_s + STAGES * STAGE_BYTES;         // [row tile][2][128 rows][128 B]
   __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], edge_bar[KT / GROUP_KEYS];
-  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], pv_full[2];
+  __shared__ __align__(8) uint64_t s_full[ROW_TILES], s_empty[ROW_TILES], p_full[ROW_TILES][2], p_empty[ROW_TILES][2];
   __shared__ uint32_t tmem_base_holder;
   __shared__ volatile int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = row_list ? row_list[blockIdx.z] : blockIdx.z;
-  const int g = blockIdx.y;
+  const int b = row_list ? row_list[blockIdx.y] : blockIdx.y;
+  const int g = blockIdx.x % nkv, pair = blockIdx.x / nkv, pairs = gridDim.x / nkv;
   const int group = nq / nkv;
-  const int tokens_per_cta = ROWS / group, rows_used = tokens_per_cta * group;
+  const int tokens_per_tile = ROWS / group, rows_used = tokens_per_tile * group;
   pdl_wait();
   const int q_start = cu_q[b], q_len = cu_q[b + 1] - q_start, k_len = kv_len[b];
   const int shift = k_len - q_len;
-  const int token0 = (gridDim.x - 1 - blockIdx.x) * tokens_per_cta;   // the tiles with most keys start first
+  const int token0 = (pairs - 1 - pair) * ROW_TILES * tokens_per_tile;   // the pairs with most keys start first
   if (token0 >= q_len) return;
-  const int token_hi = min(q_len - 1, token0 + tokens_per_cta - 1);
-  const int key_end = shift + token_hi + 1;                            // exclusive
+  // keys a row tile sees: [its first row's window start, its last row's position]; the CTA walks
+  // the tiles from the first tile's first key to the last tile's last key, a row tile stops at
+  // its own end
   const int first_key = (window > 0 && shift + token0 - window + 1 > 0) ? shift + token0 - window + 1 : 0;
   const int tile_begin = (first_key / KT) * KT;
-  const int tiles = (key_end - tile_begin + KT - 1) / KT;
+  int tiles_of[ROW_TILES], key_end = 0;
+#pragma unroll
+  for (int w = 0; w < ROW_TILES; ++w) {
+    const int t0 = token0 + w * tokens_per_tile;
+    const int end = t0 < q_len ? shift + min(q_len - 1, t0 + tokens_per_tile - 1) + 1 : 0;    // exclusive
+    tiles_of[w] = end > tile_begin ? (end - tile_begin + KT - 1) / KT : 0;
+    key_end = max(key_end, end);
+  }
+  const int tiles = max(tiles_of[0], tiles_of[1]);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(smem_u32(&q_full), 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&kv_full[s]), KT / GROUP_KEYS);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), ROW_TILES);
     }
     for (int i = 0; i < KT / GROUP_KEYS; ++i) mbar_init(smem_u32(&edge_bar[i]), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < ROW_TILES; ++i) {
       mbar_init(smem_u32(&s_full[i]), 1);
       mbar_init(smem_u32(&s_empty[i]), 4);
-      mbar_init(smem_u32(&p_full[i]), 4);
-      mbar_init(smem_u32(&p_empty[i]), 1);
-      mbar_init(smem_u32(&pv_full[i]), 1);
+      for (int j = 0; j < 2; ++j) {
+        mbar_init(smem_u32(&p_full[i][j]), 4);
+        mbar_init(smem_u32(&p_empty[i][j]), 1);
+      }
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -117,12 +134,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   if (warp < 8) {
     // ------------------------------------------------------------ softmax and accumulation
     asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
-    const int wg = warp >> 2;                                    // takes tiles wg, wg + 2, ...
+    const int wg = warp >> 2;                                    // its row tile
     const int r = threadIdx.x & 127;                             // row of the tile and lane of tensor memory
-    const int token = token0 + r / group;
+    const int token = token0 + wg * tokens_per_tile + r / group;
     const bool valid = r < rows_used && token < q_len;
     const int pos = valid ? shift + token : -1;                  // -1: no key is visible, nothing is written
     const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int my_tiles = wg ? tiles_of[1] : tiles_of[0];
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     // m_run is the maximum the exponentials are taken against. It follows the true running
     // maximum lazily: only when a tile's maximum exceeds it by more than RESCALE (P would pass
@@ -130,13 +148,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr float RESCALE = 8.f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    uint8_t* p_dst = p_s + wg * P_BYTES;
     const uint32_t o_tmem = lane_base + PV_COL + wg * D;
 
-    int k = 0;
-    for (int j = wg; j < tiles && ok; j += 2, ++k) {
-      const int key0 = tile_begin + j * KT;
-      ok = mbar_wait(smem_u32(&s_full[wg]), k & 1, &abort_flag, status);
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int key0 = tile_begin + t * KT;
+      const int buf = t & 1;
+      ok = mbar_wait(smem_u32(&s_full[wg]), t & 1, &abort_flag, status);
       if (!ok) break;
       tc_fence_after();
       uint32_t raw[2][32];
@@ -172,27 +189,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         l_run *= alpha;
       }
       const float safe = m_run == -INFINITY ? 0.f : m_run;
-      // ---- the product of the tile before this one is complete by now (it was issued a softmax
-      // ago); the wait also keeps this thread in step with the barrier's phases. If any row of the
-      // warp raised its maximum, the warp scales its rows of the running product.
-      if (k >= 1) {
-        ok = mbar_wait(smem_u32(&pv_full[wg]), (k - 1) & 1, &abort_flag, status);
-        if (__any_sync(0xffffffffu, raise)) {
-          tc_fence_after();
+      // ---- this tile's buffer of P is free once the product of the tile before the last one is
+      // complete (p_empty of a buffer counts every second product, so a wait is always for the
+      // barrier's current or last phase). If any row of the warp raised its maximum, the warp
+      // also waits for the last product and scales its rows of the running product.
+      if (t >= 2) ok = mbar_wait(smem_u32(&p_empty[wg][buf]), ((t >> 1) - 1) & 1, &abort_flag, status);
+      if (t >= 1 && __any_sync(0xffffffffu, raise)) {
+        ok = ok && mbar_wait(smem_u32(&p_empty[wg][buf ^ 1]), ((t - 1) >> 1) & 1, &abort_flag, status);
+        tc_fence_after();
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t v[32];
-            tmem_load32(o_tmem + c0, v);
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t v[32];
+          tmem_load32(o_tmem + c0, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_store32(o_tmem + c0, v);
-          }
-          tmem_wait_stores();
-          tc_fence_before();
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_store32(o_tmem + c0, v);
         }
-        ok = ok && mbar_wait(smem_u32(&p_empty[wg]), (k - 1) & 1, &abort_flag, status);
+        tmem_wait_stores();
+        tc_fence_before();
       }
       // ---- P (rounded to bfloat16) into shared memory as the A operand of the second MMA
+      uint8_t* p_dst = p_s + (wg * 2 + buf) * P_BYTES;
       float part_sum[4] = {0.f, 0.f, 0.f, 0.f};         // four chains, combined in a fixed order
       if (!valid) {
       } else if (masked) {
@@ -226,53 +243,25 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       l_run += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&p_full[wg]));
+      if (lane == 0) mbar_arrive(smem_u32(&p_full[wg][buf]));
     }
-    if (ok && k > 0) ok = mbar_wait(smem_u32(&pv_full[wg]), (k - 1) & 1, &abort_flag, status);
+    // ---- the last product complete means every product of the row tile is: normalise and store
+    if (ok && my_tiles > 0)
+      ok = mbar_wait(smem_u32(&p_empty[wg][(my_tiles - 1) & 1]), ((my_tiles - 1) >> 1) & 1, &abort_flag, status);
     tc_fence_after();
-
-    // ---- merge the two groups (every MMA is complete once both have their last products),
-    // 32 columns at a time: the second group's rows go through shared memory
-    float* merge = reinterpret_cast<float*>(kv_s);                    // [128 rows][D + 2]
-    softmax_sync();
-    if (wg == 1) {
-      float* mine = merge + r * (D + 2);
-      mine[0] = m_run;
-      mine[1] = l_run;
-      if (k > 0) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t v[32];
-          tmem_load32(o_tmem + c0, v);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mine[2 + c0 + i] = __uint_as_float(v[i]);
-        }
-      }
-    }
-    softmax_sync();
-    if (wg == 0) {
-      const float* other = merge + r * (D + 2);
-      const float m_other = other[0];
-      const bool has_other = m_other != -INFINITY;                   // the second group saw a visible key
-      const float m = fmaxf(m_run, m_other);
-      const float w_mine = m_run == -INFINITY ? 0.f : fast_exp2(m_run - m);
-      const float w_other = has_other ? fast_exp2(m_other - m) : 0.f;
-      const float l = l_run * w_mine + other[1] * w_other;
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (my_tiles > 0) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* dst = out + ((int64_t)(q_start + token) * nq + g * group + r % group) * D;
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t v[32];
-        tmem_load32(o_tmem + c0, v);                                  // the first group always has a tile
+        tmem_load32(o_tmem + c0, v);                                  // (all lanes of the warp take part)
         if (ok && valid) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             float y[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float mine_v = __uint_as_float(v[8 * c + e]) * w_mine;
-              y[e] = (has_other ? mine_v + other[2 + c0 + 8 * c + e] * w_other : mine_v) * inv;
-            }
+            for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[8 * c + e]) * inv;
             *reinterpret_cast<uint4*>(dst + c0 + 8 * c) =
                 make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
           }
@@ -286,9 +275,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int w = warp - 8;                              // keys 16 w .. 16 w + 15 of every tile
     if (w == 0 && lane == 0) {
       // Q rows: row r is token r / group, head r % group: a box [tokens][heads of the group][64]
-      mbar_expect_tx(smem_u32(&q_full), (uint32_t)(NB * rows_used * 128));
-      for (int nb = 0; nb < NB; ++nb)
-        tma_load_4d(smem_u32(q_s + nb * (ROWS * 128)), &map_q, 0, g * group, q_start + token0, nb, smem_u32(&q_full));
+      // per row tile (rows past the end of the tensor come as zeros and still count as bytes)
+      mbar_expect_tx(smem_u32(&q_full), (uint32_t)(ROW_TILES * NB * rows_used * 128));
+      for (int rt = 0; rt < ROW_TILES; ++rt)
+        for (int nb = 0; nb < NB; ++nb)
+          tma_load_4d(smem_u32(q_s + rt * Q_BYTES + nb * (ROWS * 128)), &map_q, 0, g * group,
+                      q_start + token0 + rt * tokens_per_tile, nb, smem_u32(&q_full));
     }
     const int* table = block_table + (int64_t)b * max_pages;
     bool ok = true;
@@ -339,25 +331,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // ------------------------------------------------------------ MMA issue
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (lane == 0) {
-      // Four issuing threads, one per warp: scores of the even tiles, scores of the odd tiles,
-      // products of the even tiles, products of the odd tiles. One thread alone cannot issue
-      // a tile's twelve MMAs and wait on its barriers as fast as the tensor core retires them.
+      // Four issuing threads, one per warp: scores of row tile 0, scores of row tile 1, products of
+      // row tile 0, products of row tile 1. One thread alone cannot issue a tile's twelve MMAs and
+      // wait on its barriers as fast as the tensor core retires them.
       const int role = warp - MMA_WARP, wg = role & 1;
+      const int my_tiles = wg ? tiles_of[1] : tiles_of[0];
       constexpr uint32_t idesc_s = umma_instr_desc(ROWS, KT, false);
       constexpr uint32_t idesc_pv = umma_instr_desc(ROWS, D, true);
       // descriptors differ in their start address only: bits [0,14) in units of 16 bytes
-      const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s)), k_desc = smem_desc_sw128(smem_u32(kv_s));
-      const uint64_t p_desc = smem_desc_sw128(smem_u32(p_s) + wg * P_BYTES);
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s) + wg * Q_BYTES), k_desc = smem_desc_sw128(smem_u32(kv_s));
       const uint64_t v_desc = smem_desc_sw128_mn(smem_u32(kv_s) + K_BYTES, KT * 128);
       bool ok = true;
       if (role < 2) {
-        // S_t = Q K_t^T into the score buffer of the tile's group
+        // S_t = Q K_t^T into the score buffer of the row tile
         ok = mbar_wait(smem_u32(&q_full), 0, &abort_flag, status);
-        int k = 0;
-        for (int t = wg; t < tiles && ok; t += 2, ++k) {
+        for (int t = 0; t < my_tiles && ok; ++t) {
           const int stage = t % STAGES;
           ok = mbar_wait(smem_u32(&kv_full[stage]), (t / STAGES) & 1, &abort_flag, status);
-          if (ok && k >= 1) ok = mbar_wait(smem_u32(&s_empty[wg]), (k - 1) & 1, &abort_flag, status);
+          if (ok && t >= 1) ok = mbar_wait(smem_u32(&s_empty[wg]), (t - 1) & 1, &abort_flag, status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t kd = k_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
@@ -370,21 +361,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           umma_commit(smem_u32(&s_full[wg]));
         }
       } else {
-        // (P V) of tile t, 16 keys per MMA; V rows are [key][64 features] blocks: MN-major
-        int k = 0;
-        for (int t = wg; t < tiles && ok; t += 2, ++k) {
+        // (P V) of tile t, 16 keys per MMA; V rows are [key][64 features] blocks: MN-major.
+        // A stage is given back when both row tiles' products of it are complete; a row tile that
+        // ends before the other one still counts itself in for the remaining tiles, each time
+        // after the tile has arrived, so that it never runs a phase ahead.
+        for (int t = 0; t < tiles && ok; ++t) {
           const int stage = t % STAGES;
           ok = mbar_wait(smem_u32(&kv_full[stage]), (t / STAGES) & 1, &abort_flag, status);
-          if (ok) ok = mbar_wait(smem_u32(&p_full[wg]), k & 1, &abort_flag, status);
+          if (!ok) break;
+          if (t >= my_tiles) {
+            mbar_arrive(smem_u32(&kv_empty[stage]));
+            continue;
+          }
+          ok = mbar_wait(smem_u32(&p_full[wg][t & 1]), (t >> 1) & 1, &abort_flag, status);
           if (!ok) break;
           tc_fence_after();
           const uint64_t vd = v_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
+          const uint64_t p_desc = smem_desc_sw128(smem_u32(p_s) + (wg * 2 + (t & 1)) * P_BYTES);
 #pragma unroll
           for (int ks = 0; ks < KT / 16; ++ks)
             umma_bf16(tmem_base + PV_COL + wg * D, p_desc + (uint64_t)((ks * 32) >> 4),
-                      vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, (k | ks) ? 1u : 0u);
-          umma_commit(smem_u32(&pv_full[wg]));
-          umma_commit(smem_u32(&p_empty[wg]));
+                      vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, (t | ks) ? 1u : 0u);
+          umma_commit(smem_u32(&p_empty[wg][t & 1]));
           umma_commit(smem_u32(&kv_empty[stage]));
         }
       }
@@ -404,7 +402,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 template <int D>
 constexpr size_t prefill_tc_smem_bytes() {
-  return 1024 + (size_t)(D / 64) * ROWS * 128 + (size_t)STAGES * 2 * (D / 64) * KT * 128 + 2 * (size_t)ROWS * 128;
+  return 1024 + (size_t)ROW_TILES * (D / 64) * ROWS * 128 + (size_t)kv_stages<D>() * 2 * (D / 64) * KT * 128 +
+         (size_t)ROW_TILES * 2 * ROWS * 128;
 }
 
 }  // namespace
@@ -427,23 +426,23 @@ VOSTI_API int vosti_attention_prefill_tc(const void* q, const void* k_cache, con
                 "attention_prefill_tc: head_dim %d must be 64 or 128 and page_size %d a multiple of 16", d, page_size);
   VOSTI_REQUIRE(max_pages > 0 && num_pages > 0 && window >= 0 && tokens_total > 0, "attention_prefill_tc: bad geometry");
   VOSTI_REQUIRE(scale > 0.f, "attention_prefill_tc: the score scale must be positive");
-  VOSTI_REQUIRE(count <= 65535 && nkv <= 65535, "attention_prefill_tc: too many requests or heads for one launch");
+  VOSTI_REQUIRE(count <= 65535, "attention_prefill_tc: too many requests for one launch");
   if (count == 0 || max_q_len <= 0) return VOSTI_OK;
   const int group = nq / nkv;
-  const int tokens_per_cta = ROWS / group;
+  const int tokens_per_tile = ROWS / group, tokens_per_cta = ROW_TILES * tokens_per_tile;
   const int64_t cache_rows = (int64_t)num_pages * nkv * page_size;
   VOSTI_REQUIRE(cache_rows < (int64_t)1 << 31, "attention_prefill_tc: cache of %lld rows is too large", (long long)cache_rows);
   CUtensorMap map_q, map_k, map_v;
   {
     const cuuint64_t dims[4] = {64, (cuuint64_t)nq, (cuuint64_t)tokens_total, (cuuint64_t)(d / 64)};
     const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)nq * d * 2, 128};
-    const cuuint32_t box[4] = {64, (cuuint32_t)group, (cuuint32_t)tokens_per_cta, 1};
+    const cuuint32_t box[4] = {64, (cuuint32_t)group, (cuuint32_t)tokens_per_tile, 1};
     VOSTI_REQUIRE(encode_tensor_map_nd(&map_q, q, 4, dims, strides, box), "attention_prefill_tc: cuTensorMapEncodeTiled failed (q)");
   }
   VOSTI_REQUIRE(cached_tensor_map(k_cache, cache_rows, d, GROUP_KEYS, &map_k) &&
                     cached_tensor_map(v_cache, cache_rows, d, GROUP_KEYS, &map_v),
                 "attention_prefill_tc: cuTensorMapEncodeTiled failed (cache)");
-  dim3 grid((unsigned)((max_q_len + tokens_per_cta - 1) / tokens_per_cta), nkv, count);
+  dim3 grid((unsigned)((max_q_len + tokens_per_cta - 1) / tokens_per_cta) * nkv, count);
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
