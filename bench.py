@@ -394,7 +394,7 @@ def main() -> int:
         engine = Engine(spec=spec, tensors=tensors, dtype="bfloat16", device="cuda:0", num_blocks=num_blocks,
                         block_size=PAGE, max_num_seqs=32, max_num_batched_tokens=4096, enable_prefix_caching=True,
                         cuda_graphs=not args.no_cuda_graphs, batch_invariant=args.batch_invariant,
-                        async_scheduling=not args.sync_scheduling)
+                        async_scheduling=not args.sync_scheduling, consume_tensors=True)
         del tensors
         torch.cuda.empty_cache()
         mixed_run(engine, config, seed=4, requests=4)            # warm the kernels and the graphs' first shapes
@@ -418,12 +418,13 @@ def main() -> int:
         return 0
 
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    tokens_per_request = config["max_position_embeddings"]
+    tokens_per_request = CONTEXT + 2 * DECODE_STEPS + 128     # prompt, both timed regions, warm-up and slack
     num_blocks = max_batch * ((tokens_per_request + PAGE - 1) // PAGE) + 8
     engine = Engine(spec=spec, tensors=tensors, dtype="bfloat16", device="cuda:0", num_blocks=num_blocks,
                     block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=2 * CONTEXT,
                     enable_prefix_caching=False, cuda_graphs=not args.no_cuda_graphs,
-                    batch_invariant=args.batch_invariant, async_scheduling=not args.sync_scheduling)
+                    batch_invariant=args.batch_invariant, async_scheduling=not args.sync_scheduling,
+                    consume_tensors=True)
     del tensors
     torch.cuda.empty_cache()
     weight_bytes = engine.runner.model.weight_bytes()

@@ -51,7 +51,7 @@ class Engine:
                  max_num_batched_tokens: int = 4096, prefill_chunk_size: int = 0,
                  enable_prefix_caching: bool = True, step_trace: Optional[str] = None,
                  cuda_graphs: bool = True, batch_invariant=False, async_scheduling: bool = False, spec=None,
-                 tensors=None):
+                 tensors=None, consume_tensors: bool = False):
         """`num_blocks` pages of `block_size` tokens; `max_num_seqs` rows and
         `max_num_batched_tokens` tokens per step at most (the reference's VOSTI_NUM_BLOCKS,
         VOSTI_MAX_SEQS, VOSTI_MAX_BATCHED_TOKENS; its page size is fixed at 64).
@@ -71,7 +71,7 @@ class Engine:
             ops.set_invariance(batch_invariant)
         self.runner = ModelRunner(model, dtype=dtype, device=device, num_pages=num_blocks, page_size=block_size,
                                   max_requests=max_num_seqs, prefix_reuse=enable_prefix_caching, spec=spec,
-                                  tensors=tensors)
+                                  tensors=tensors, consume_tensors=consume_tensors)
         spec = self.runner.spec
         self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
             max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,

@@ -48,7 +48,12 @@ def parse_dtype(name) -> torch.dtype:
 class ModelRunner:
     def __init__(self, model_dir: Optional[str | Path] = None, *, dtype="bfloat16", device="cuda:0",
                  num_pages: int, page_size: int = 16, max_requests: int = 64, prefix_reuse: bool = False,
-                 spec: Optional[ModelSpec] = None, tensors: Optional[Dict[str, torch.Tensor]] = None):
+                 spec: Optional[ModelSpec] = None, tensors: Optional[Dict[str, torch.Tensor]] = None,
+                 consume_tensors: bool = False):
+        """`tensors` (name -> tensor, already on the device) stands in for a model folder.
+        With `consume_tensors` the dictionary is emptied once the parts have taken what they
+        keep, before the cache is allocated, so that weights the parts re-packed do not stay in
+        memory twice."""
         self.device = torch.device(device)
         self.dtype = parse_dtype(dtype)
         ops.require_device(self.device)
@@ -68,6 +73,9 @@ class ModelRunner:
             if self.dtype == torch.float32:
                 tensors = {k: (v.float() if v.is_floating_point() else v) for k, v in tensors.items()}
         self.model.load(tensors, self.dtype)
+        if consume_tensors:
+            tensors.clear()
+            torch.cuda.empty_cache()
         cache_specs = [b.mixer.cache_spec() for b in self.model.blocks]
         state_specs = [b.mixer.state_spec() for b in self.model.blocks]
         self.cache = CacheManager(cache_specs, state_specs, num_pages=num_pages, page_size=page_size,
