@@ -739,3 +739,35 @@ def test_weights_requested_ahead_change_no_value(dev, status):
     assert lib.vosti_hint_prefetch(None, ctypes.c_longlong(0)) == 0
     torch.cuda.synchronize()
     assert status.item() == 0
+
+
+def test_sampling_with_the_state_in_request_slots(dev, status):
+    """The sampler reads (temperature, seed, index) from each row's slot, draws what the array
+    form draws for the same state, advances the index in the slot and notes the position; a slot
+    outside the table is reported and sampled greedily."""
+    from vosti_b200 import ops
+    from vosti_b200.sampling import sampler_state_words
+    vocab, rows, num_slots = 1531, 5, 9
+    logits = torch.randn(rows, vocab, device=dev) * 2
+    slot_of = [7, 2, 0, 8, 4]
+    temps, seeds, start = [0.0, 0.7, 1.0, 1.3, 0.7], [3, 5, 2 ** 40 + 7, 11, 6], [0, 4, 9, 1, 30]
+    table = torch.zeros(num_slots, 4, dtype=torch.int64, device=dev)
+    for slot, t, s, i in zip(slot_of, temps, seeds, start):
+        table[slot] = torch.tensor(sampler_state_words(t, s, i), dtype=torch.int64)
+    untouched = table[[1, 3, 5, 6]].clone()
+    slots = torch.tensor(slot_of, dtype=torch.int32, device=dev)
+    positions = torch.tensor([40, 41, 42, 43, 44], dtype=torch.int32, device=dev)
+    for step in range(3):
+        got = ops.sample_slots(logits, slots, table, positions + step, status).tolist()
+        want = ops.sample(logits, torch.tensor(temps, device=dev), torch.tensor(seeds, dtype=torch.int64, device=dev),
+                          torch.tensor([i + step for i in start], dtype=torch.int64, device=dev)).tolist()
+        assert got == want
+        for row, slot in enumerate(slot_of):
+            assert table[slot, 2].item() == start[row] + step + 1 and table[slot, 3].item() == 40 + row + step
+            assert table[slot, 1].item() == seeds[row]
+    assert torch.equal(table[[1, 3, 5, 6]], untouched) and status.item() == 0
+    assert len({tuple(ops.sample_slots(logits[1:2], slots[1:2], table, None, status).tolist()) for _ in range(6)}) > 1
+    bad = torch.tensor([num_slots], dtype=torch.int32, device=dev)
+    assert ops.sample_slots(logits[:1], bad, table, None, status).tolist() == [int(logits[0].argmax())]
+    assert status.item() == 2
+    status.zero_()

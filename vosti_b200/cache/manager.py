@@ -136,6 +136,12 @@ class CacheManager:
             if spec is not None and device is not None:
                 self.layer_caches[layer].state = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype,
                                                              device=device)
+        # Beside the mixers' state, every request slot holds four 64-bit words for the engine: the
+        # sampler's state (temperature as float bits, seed, index of the next token) and the
+        # position of the last sampled token's input, written at admission and advanced on the
+        # device (src/exec/request_state.rs:213-226 keeps the same per request on the host).
+        self.request_state = (torch.zeros((max_requests, 4), dtype=torch.int64, device=device)
+                              if device is not None else None)
         self.has_state = any(s is not None for s in state_specs)
         # The accounting itself is C++. A published page stands for the keys of every layer;
         # with a windowed group or per-request state a prefix would need more than pages to

@@ -810,7 +810,7 @@ VH_API int vh_queue(void* host, int which, int64_t* out, int capacity) {   // 0:
     if (n < capacity) out[n++] = r->id;
   return (int)queue.size();
 }
-// rows_out: [capacity][4] = (start, count, sample, computed-after-plan is start) with ids in ids_out.
+// rows_out: [capacity][4] = (start, count, sample, state slot of the request), ids in ids_out.
 VH_API int vh_plan(void* host, int64_t* ids_out, int32_t* rows_out, int capacity, int64_t* preempted_out,
                    int32_t* n_preempted, int64_t* dropped_out, int32_t* n_dropped, int side_capacity) {
   std::vector<PlanRow> rows;
@@ -820,9 +820,11 @@ VH_API int vh_plan(void* host, int64_t* ids_out, int32_t* rows_out, int capacity
     return fail(VH_BAD_ARGUMENT, "plan does not fit the buffers given");
   for (size_t i = 0; i < rows.size(); ++i) {
     ids_out[i] = rows[i].id;
-    rows_out[3 * i] = rows[i].start;
-    rows_out[3 * i + 1] = rows[i].count;
-    rows_out[3 * i + 2] = rows[i].sample;
+    rows_out[4 * i] = rows[i].start;
+    rows_out[4 * i + 1] = rows[i].count;
+    rows_out[4 * i + 2] = rows[i].sample;
+    const Residency* res = ((Host*)host)->cache->find(rows[i].id);
+    rows_out[4 * i + 3] = res != nullptr ? res->slot : -1;
   }
   std::copy(preempted.begin(), preempted.end(), preempted_out);
   std::copy(dropped.begin(), dropped.end(), dropped_out);

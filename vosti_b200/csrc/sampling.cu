@@ -6,6 +6,12 @@
 //   from a counter-based generator keyed by (seed, index of the token being drawn).
 // A row's result depends on its own logits, seed and index only, so it is independent of
 // what else is in the batch.
+// The sampler's state (temperature, seed, index of the next token) comes either as arrays with
+// an entry per row, or from the per-request slots of fixed size the cache manager keeps: four
+// 64-bit words per slot (temperature as float bits, seed, index of the next token to draw,
+// position of the last sampled token's input), which the kernel reads by the row's slot and
+// advances itself, so a decode step brings no sampler state from the host. The reference models
+// its sampler as (state, logits) -> (state', token) (src/boundary/sampler.rs:7-19).
 #include "common.cuh"
 
 namespace {
@@ -23,7 +29,9 @@ __device__ __forceinline__ float uniform24(unsigned long long seed, unsigned lon
 
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, const float* __restrict__ temperature,
-              const long long* __restrict__ seeds, const long long* __restrict__ counters, int* __restrict__ out) {
+              const long long* __restrict__ seeds, const long long* __restrict__ counters, const int* __restrict__ slots,
+              long long* __restrict__ slot_table, int num_slots, const int* __restrict__ positions,
+              int* __restrict__ out, unsigned* status) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ float s_scan[THREADS + 1];
@@ -32,6 +40,28 @@ sample_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, c
   pdl_launch_dependents();
   const float* row = logits + (int64_t)blockIdx.x * row_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // the sampler state of this row: from its slot, or from the arrays
+  long long* state = nullptr;
+  float temp = temperature ? temperature[blockIdx.x] : 0.f;
+  unsigned long long seed = seeds ? (unsigned long long)seeds[blockIdx.x] : 0ull;
+  unsigned long long index = counters ? (unsigned long long)counters[blockIdx.x] : 0ull;
+  if (slots != nullptr) {
+    int slot = slots[blockIdx.x];
+    if (slot < 0 || slot >= num_slots) {
+      if (tid == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+      temp = 0.f;
+    } else {
+      state = slot_table + 4ll * slot;
+      temp = __int_as_float((int)(state[0] & 0xffffffffll));
+      seed = (unsigned long long)state[1];
+      index = (unsigned long long)state[2];
+    }
+  }
+  __syncthreads();                       // every thread has read the state before thread 0 advances it
+  if (state != nullptr && tid == 0) {
+    state[2] = (long long)(index + 1ull);
+    if (positions != nullptr) state[3] = positions[blockIdx.x];
+  }
 
   // ---- maximum and its lowest index (needed by both modes)
   float best = -INFINITY;
@@ -88,7 +118,6 @@ sample_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, c
       best_i = s_idx[w];
     }
   }
-  const float temp = temperature ? temperature[blockIdx.x] : 0.f;
   if (!(temp > 0.f)) {
     if (tid == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
     return;
@@ -115,7 +144,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, c
   }
   __syncthreads();
   const float total = s_scan[THREADS];
-  const float u = uniform24((unsigned long long)seeds[blockIdx.x], (unsigned long long)counters[blockIdx.x]);
+  const float u = uniform24(seed, index);
   const float target = u * total;
   const float before = s_scan[tid];
   if (target >= before && target < s_scan[tid + 1]) {
@@ -142,6 +171,21 @@ VOSTI_API int vosti_sample(const float* logits, int rows, int vocab, int64_t row
                 "sample: temperature sampling needs seeds and counters");
   if (rows == 0) return VOSTI_OK;
   vosti_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, row_stride, temperature, seeds,
-               counters, out);
+               counters, (const int*)nullptr, (long long*)nullptr, 0, (const int*)nullptr, out, (unsigned*)nullptr);
+  VOSTI_LAUNCH_CHECK();
+}
+
+// The same with the sampler state in per-request slots: slots int32[rows] names each row's slot,
+// slot_table int64[num_slots][4] = (temperature as float bits, seed, index of the next token,
+// position); the kernel advances the index and, if `positions` (int32[rows]) is given, writes the
+// row's position. A slot outside the table sets a fault bit and the row is sampled greedily.
+VOSTI_API int vosti_sample_slots(const float* logits, int rows, int vocab, int64_t row_stride, const int* slots,
+                                 long long* slot_table, int num_slots, const int* positions, int* out,
+                                 unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample_slots: bad sizes rows=%d vocab=%d", rows, vocab);
+  VOSTI_REQUIRE(slots != nullptr && slot_table != nullptr && num_slots > 0, "sample_slots: the slots or their table are missing");
+  if (rows == 0) return VOSTI_OK;
+  vosti_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, row_stride, (const float*)nullptr,
+               (const long long*)nullptr, (const long long*)nullptr, slots, slot_table, num_slots, positions, out, status);
   VOSTI_LAUNCH_CHECK();
 }

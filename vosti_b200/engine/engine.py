@@ -12,7 +12,10 @@ The surface is the reference's Rust API as its example drives it: `Engine::init`
 `try_add_request`, `step` -> emitted tokens (src/exec/engine.rs:2515, 2664, 2795;
 examples/support/engine_serving.rs:211-219). One step is plan -> forward -> sample ->
 publish completed pages -> commit (src/exec/engine.rs:2781-2782), with one device-to-host
-copy for the sampled tokens and the device fault word. With `async_scheduling` the order
+copy for the sampled tokens and the device fault word. A request's sampler state
+(temperature, seed, index of the next token) is written to its slot of fixed size on the
+device when it takes the slot and advanced there by the sampling kernel
+(src/boundary/sampler.rs:7-19: (state, logits) -> (state', token)). With `async_scheduling` the order
 becomes plan -> launch the next step -> read the last step's tokens, and the commit is split
 in two around the plan (`Scheduler.commit_ahead`, `Scheduler.resolve`).
 """
@@ -25,7 +28,7 @@ from typing import Dict, Iterable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..sampling import sample_rows, sampling_arrays
+from ..sampling import sample_from_slots, sampler_state_words
 from .batch import StepEntry
 from .request import AdmissionStatus, Request
 from .runner import DeviceFault, ModelRunner, _FAULTS
@@ -85,6 +88,7 @@ class Engine:
         self._host_results = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._events = [torch.cuda.Event() for _ in range(2)]
         self._host_turn = 0
+        self._slot_tenant: Dict[int, object] = {}      # request whose sampler state a slot holds
         self.step_trace = open(step_trace, "a") if step_trace else None
         self.step_index = 0
         self.last_plan: Optional[StepPlan] = None
@@ -171,7 +175,7 @@ class Engine:
         result to the host. `before` is the step launched earlier whose tokens the host has not
         read: a row whose last token is one of them names its place in that step's result."""
         runner = self.runner
-        entries, temps, seeds, counters, feedback = [], [], [], [], []
+        entries, feedback, slots, positions = [], [], [], []
         slot_before = {}
         if before is not None:
             slot = 0
@@ -179,6 +183,7 @@ class Engine:
                 if row.sample:
                     slot_before[row.request.request_id] = slot
                     slot += 1
+        table = runner.cache.request_state
         for row in plan.rows:
             request = row.request
             tokens = request.token_range(row.start, row.count)
@@ -189,25 +194,30 @@ class Engine:
                 tokens[-1], source[-1] = 0, slot_before[request.request_id]
             feedback.extend(source)
             entries.append(StepEntry(request.request_id, tokens, [row.count - 1] if row.sample else []))
+            # the sampler's state lives in the request's slot: written when the request takes the
+            # slot (admission, re-admission after a preemption), advanced there by the kernel
+            if self._slot_tenant.get(row.slot) != request.request_id:
+                self._slot_tenant[row.slot] = request.request_id
+                words = torch.tensor(sampler_state_words(request.temperature, request.seed, len(request.generated)),
+                                     dtype=torch.int64).pin_memory()
+                table[row.slot].copy_(words, non_blocking=True)
             if row.sample:
-                temps.append(request.temperature)
-                seeds.append(request.seed)
-                counters.append(len(request.generated))
-        arrays = sampling_arrays(temps, seeds, counters)
-        extras = None if arrays is None else {"temperature": arrays[0], "seeds": arrays[1], "counters": arrays[2]}
+                slots.append(row.slot)
+                positions.append(row.start + row.count - 1)
+        count = len(slots)
+        extras = {"sample_slots": np.asarray(slots, dtype=np.int32),
+                  "sample_positions": np.asarray(positions, dtype=np.int32)} if count else {}
         if self.async_scheduling:
-            extras = dict(extras or {})
             extras["feedback"] = np.asarray(feedback, dtype=np.int32)
-        count = len(temps)
         if self.graphs is not None and all(row.count == 1 and row.sample for row in plan.rows):
             self.graphs.step(entries, extras, longest=max(row.start for row in plan.rows) + 1)
         else:
-            ctx = runner.prepare(entries, extras=extras)
+            ctx = runner.prepare(entries, extras=extras or None)
             logits = runner.run(ctx)
             if logits is not None:
                 ex = ctx.extras
-                sample_rows(logits, ex.get("temperature"), ex.get("seeds"), ex.get("counters"),
-                            out=runner.result[1:1 + count])
+                sample_from_slots(logits, ex["sample_slots"], table, ex["sample_positions"], runner.status,
+                                  out=runner.result[1:1 + count])
         self._host_turn ^= 1
         host = self._host_results[self._host_turn]
         host[:1 + count].copy_(runner.result[:1 + count], non_blocking=True)

@@ -3,9 +3,10 @@
 A decode step launches a few hundred small kernels; issuing them one by one from the host
 takes longer than the GPU needs to run them. Steps in which every request brings exactly
 one token are therefore captured once per shape and replayed: the shape is (requests,
-sampling arrays present, block-table width bucket, key-length bucket), and everything else
-a kernel needs (tokens, positions, slots, block tables, sampler state) is read from the
-step's staging buffer, whose address and layout are the same for every step of a shape.
+per-step arrays present, block-table width bucket, key-length bucket), and everything else
+a kernel needs (tokens, positions, slots, block tables) is read from the step's staging
+buffer, whose address and layout are the same for every step of a shape; the sampler's
+state is read from, and advanced in, the requests' slots.
 The reference has the same remedy for its per-primitive host overhead
 (python/vosti_kernels/graph_overlay.py; src/exec/engine.rs:1990-2027).
 
@@ -21,7 +22,7 @@ from typing import Dict, Optional, Sequence
 import torch
 
 from .. import ops
-from ..sampling import sample_rows
+from ..sampling import sample_from_slots
 from .batch import StepEntry
 
 PAGES_BUCKET = 32      # block-table width is rounded up to this many pages
@@ -48,8 +49,8 @@ class DecodeGraphs:
         runner = self.runner
         logits = runner.run(ctx)
         ex = ctx.extras
-        sample_rows(logits, ex.get("temperature"), ex.get("seeds"), ex.get("counters"),
-                    out=runner.result[1:1 + count])
+        sample_from_slots(logits, ex["sample_slots"], runner.cache.request_state, ex["sample_positions"],
+                          runner.status, out=runner.result[1:1 + count])
 
     def step(self, entries: Sequence[StepEntry], extras: Optional[dict], longest: Optional[int] = None) -> None:
         """Run a decode-only step; the sampled tokens are left in runner.result[1:1+B]."""

@@ -67,6 +67,7 @@ class PlanRow:
     start: int                 # position of the row's first token
     count: int                 # tokens the row computes
     sample: bool               # the row reaches the end of the known tokens
+    slot: int = -1             # the request's slot of per-request state in this step
 
 
 @dataclass
@@ -102,7 +103,7 @@ class Scheduler:
         capacity = max(config.max_num_seqs, cache.max_requests, 1) + 8
         self._capacity = capacity
         self._ids = (ctypes.c_int64 * capacity)()
-        self._rows = (ctypes.c_int32 * (3 * capacity))()
+        self._rows = (ctypes.c_int32 * (4 * capacity))()
         self._side = (ctypes.c_int64 * 4096)()
         self._side2 = (ctypes.c_int64 * 4096)()
 
@@ -203,8 +204,8 @@ class Scheduler:
         rows = self._rows
         for i in range(n):
             request = self._requests[names[self._ids[i]]]
-            request.computed = rows[3 * i]
-            plan.rows.append(PlanRow(request, rows[3 * i], rows[3 * i + 1], bool(rows[3 * i + 2])))
+            request.computed = rows[4 * i]
+            plan.rows.append(PlanRow(request, rows[4 * i], rows[4 * i + 1], bool(rows[4 * i + 2]), rows[4 * i + 3]))
         return plan
 
     # ------------------------------------------------------------ commit

@@ -247,6 +247,26 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
     return out
 
 
+def sample_slots(logits: torch.Tensor, slots: torch.Tensor, table: torch.Tensor, positions: Optional[torch.Tensor],
+                 status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tokens from float32 logits with each row's sampler state read from, and advanced in, its
+    per-request slot: `slots` int32[rows], `table` int64[slots, 4] = (temperature as float bits,
+    seed, index of the next token, position)."""
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 [rows, vocab] with unit inner stride")
+    _contig(slots, table, positions)
+    if slots.dtype != torch.int32 or slots.numel() < logits.shape[0] or table.dtype != torch.int64 or table.shape[-1] != 4:
+        raise KernelError("sample_slots: slots must be int32 with an entry per row, the table int64 [slots, 4]")
+    if out is None:
+        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    elif out.dtype != torch.int32 or out.numel() < logits.shape[0] or not out.is_contiguous():
+        raise KernelError("sample: out must be a contiguous int32 tensor with a slot per row")
+    _check(library().vosti_sample_slots(_p(logits), logits.shape[0], logits.shape[1], ctypes.c_int64(logits.stride(0)),
+                                        _p(slots), _p(table), table.shape[0], _p(positions), _p(out), _p(status),
+                                        _stream()), "sample_slots")
+    return out
+
+
 def gemm_tc_supported(n: int, k: int) -> bool:
     """Whether the tensor-core product takes a [n, k] bfloat16 weight."""
     return bool(library().vosti_gemm_tc_supported(int(n), int(k)))

@@ -44,6 +44,22 @@ def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None
     return ops.sample(logits, temperature, seeds, counters, out=out)
 
 
+def sampler_state_words(temperature: float, seed: int, index: int, position: int = 0):
+    """The four 64-bit words of a request's sampler state as its slot keeps them: temperature
+    as float32 bits, seed, index of the next token to draw, position (written by the kernel)."""
+    bits = int(np.float32(temperature).view(np.uint32))
+    signed = lambda v: int(np.uint64(v & _MASK).view(np.int64))
+    return [bits, signed(seed), signed(index), int(position)]
+
+
+def sample_from_slots(logits: torch.Tensor, slots: torch.Tensor, table: torch.Tensor,
+                      positions: Optional[torch.Tensor], status: Optional[torch.Tensor],
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row; each row's (temperature, seed, index) is read from its request's slot
+    of `table`, and the index is advanced there."""
+    return ops.sample_slots(logits, slots, table, positions, status, out=out)
+
+
 def sampling_arrays(temperatures: Sequence[float], seeds: Sequence[int], counters: Sequence[int]):
     """Host arrays in the layout the kernel reads; None if every row is greedy."""
     if not any(t > 0.0 for t in temperatures):
