@@ -167,3 +167,37 @@ def test_replay_with_other_page_sizes(name, page, dtype, model_dirs, plain_model
     replayer.run_line({"step": 10 ** 6 + 2, "entries": [{"id": "over", "tokens": [3], "want": [0]}], "end": ["over"]})
     replayer.runner.cache.check()
     assert pool.available() == pool.num_pages
+
+
+def test_two_engines_of_one_process_may_differ_in_their_invariance_mode(model_dirs):
+    """An engine applies its own mode before each of its steps: stepped in turns with an engine in
+    the default mode, an engine with one order of arithmetic still gives every request the bits
+    (here: the tokens at temperature 0.9, which any changed bit of a logit would soon change) it
+    gives that request alone, prompts cut into portions and decoded in a batch of three."""
+    from vosti_b200 import Engine, ops
+    path, config, page = model_dirs["c"]
+    prompts = [R.random_tokens(config["vocab_size"], n, seed=900 + n) for n in (70, 33, 120)]
+    try:
+        fixed = Engine(path, dtype="bfloat16", num_blocks=128, block_size=page, max_num_seqs=3, max_num_batched_tokens=48,
+                       batch_invariant="full")
+        plain_mode = Engine(path, dtype="bfloat16", num_blocks=128, block_size=page, max_num_seqs=3)
+        assert ops.INVARIANCE == "off"                        # the engine made last set the mode last
+        for i, p in enumerate(prompts):
+            fixed.add_request(i, p, 40, None, True, temperature=0.9, seed=i)
+            plain_mode.add_request(i, p, 40, None, True, temperature=0.9, seed=i)
+        together = {i: [] for i in range(3)}
+        while fixed.has_unfinished() or plain_mode.has_unfinished():
+            busy = fixed.has_unfinished()
+            for rid, token in fixed.step().items():
+                together[rid].append(token)
+            assert not busy or ops.INVARIANCE == "full"
+            busy = plain_mode.has_unfinished()
+            plain_mode.step()
+            assert not busy or ops.INVARIANCE == "off"
+        for i, p in enumerate(prompts):
+            alone = Engine(path, dtype="bfloat16", num_blocks=128, block_size=page, max_num_seqs=1, batch_invariant="full")
+            plain_mode.add_request(100 + i, p, 3, None, True)
+            plain_mode.step()                                   # the other engine keeps running in between
+            assert alone.generate([p], max_tokens=40, temperature=0.9, seeds=[i]) == [together[i]]
+    finally:
+        ops.set_invariance("off")

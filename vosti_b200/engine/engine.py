@@ -58,7 +58,8 @@ class Engine:
         """`num_blocks` pages of `block_size` tokens; `max_num_seqs` rows and
         `max_num_batched_tokens` tokens per step at most (the reference's VOSTI_NUM_BLOCKS,
         VOSTI_MAX_SEQS, VOSTI_MAX_BATCHED_TOKENS; its page size is fixed at 64).
-        `batch_invariant` (a setting of the whole process, bfloat16 only; ops.set_invariance):
+        `batch_invariant` (bfloat16 only; ops.set_invariance, which this engine applies again
+        before each of its steps, so two engines of one process may run in different modes):
         True or "full" computes every token in one order of arithmetic, so that its bits do not
         depend on how prompts are cut into portions, on reused prefixes or on the batch around
         it, at the price of slower decoding; "decode" only pins the decode attention's segment
@@ -70,8 +71,7 @@ class Engine:
         `cuda_graphs`: decode steps are recorded once per shape and replayed; it is switched
         off by itself for a model with a part that declares `capture_safe = False`."""
         from .. import ops
-        if _is_bfloat16(dtype):
-            ops.set_invariance(batch_invariant)
+        self.invariance = ops.set_invariance(batch_invariant) if _is_bfloat16(dtype) else None
         self.runner = ModelRunner(model, dtype=dtype, device=device, num_pages=num_blocks, page_size=block_size,
                                   max_requests=max_num_seqs, prefix_reuse=enable_prefix_caching, spec=spec,
                                   tensors=tensors, consume_tensors=consume_tensors)
@@ -175,6 +175,9 @@ class Engine:
         result to the host. `before` is the step launched earlier whose tokens the host has not
         read: a row whose last token is one of them names its place in that step's result."""
         runner = self.runner
+        if self.invariance is not None:
+            from .. import ops
+            ops.set_invariance(self.invariance)       # another engine of the process may have set its own
         entries, feedback, slots, positions = [], [], [], []
         slot_before = {}
         if before is not None:

@@ -469,8 +469,13 @@ def set_decode_segment(keys: int) -> None:
     _check(library().vosti_set_decode_segment(int(keys)), "set_decode_segment", kernels=0)
 
 
+INVARIANCE = "off"          # the mode set last
+
+
 def set_invariance(mode) -> str:
-    """Choose what a token's bfloat16 bits may depend on, for this process.
+    """Choose what a token's bfloat16 bits may depend on, for the launches that follow (the
+    kernel library keeps the mode; an engine sets its own mode again before each of its steps,
+    so engines of one process may differ).
     False, None, "off": every launch picks the fastest cut for its shape.
     "decode": the decode attention's segment length is pinned, so a decode step of up to 64
     rows gives a row the same bits whatever the batch around it is; prompts cut differently
@@ -480,8 +485,11 @@ def set_invariance(mode) -> str:
     name = {False: "off", None: "off", True: "full", "0": "off", "1": "full", "": "off"}.get(mode, mode)
     if name not in ("off", "decode", "full"):
         raise ValueError(f"batch invariance is 'off', 'decode' or 'full', not {mode!r}")
-    set_fixed_order(name == "full")
-    set_decode_segment(BATCH_INVARIANT_SEGMENT if name == "decode" else 0)
+    global INVARIANCE
+    if name != INVARIANCE:
+        set_fixed_order(name == "full")
+        set_decode_segment(BATCH_INVARIANT_SEGMENT if name == "decode" else 0)
+        INVARIANCE = name
     return name
 
 
