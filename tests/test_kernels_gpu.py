@@ -771,3 +771,68 @@ def test_sampling_with_the_state_in_request_slots(dev, status):
     assert ops.sample_slots(logits[:1], bad, table, None, status).tolist() == [int(logits[0].argmax())]
     assert status.item() == 2
     status.zero_()
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window,use_norm,use_rope", [(32, 8, 128, 16, 0, True, True), (6, 3, 48, 16, 0, True, True),
+                                                                     (4, 1, 16, 8, 0, False, True), (8, 8, 64, 32, 0, True, False),
+                                                                     (10, 2, 128, 16, 700, True, True)])
+def test_fused_decode_attention_gives_the_bits_of_its_two_kernels(dev, status, nq, nkv, d, page, window, use_norm, use_rope):
+    """Head norm, rotation, cache store and attention in one kernel against the head kernel
+    followed by the decode attention, from the same partial sums: the same bits in the output and
+    in the caches, for requests of very different lengths, and close to the plain attention."""
+    from vosti_b200 import ops
+    gen = torch.Generator(device=dev).manual_seed(nq * 131 + d)
+    lengths = [1, 17, 300, 1024, 1500, 2047, 33, 640]                  # keys of each request after the step
+    B, heads, splits = len(lengths), nq + 2 * nkv, 5
+    pages_of = [-(-n // page) for n in lengths]
+    num_pages = sum(pages_of) + 3
+    order = torch.randperm(num_pages - 1, generator=torch.Generator().manual_seed(1)).tolist()
+    table = torch.zeros(B, max(pages_of), dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(pages_of):
+        table[b, :n] = torch.tensor(order[at:at + n], dtype=torch.int32)
+        at += n
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32)
+    slots = torch.tensor([int(table[b, (n - 1) // page]) * page + (n - 1) % page for b, n in enumerate(lengths)], dtype=torch.int32)
+    k0 = torch.randn(num_pages, nkv, page, d, device=dev, generator=gen).bfloat16()
+    v0 = torch.randn(num_pages, nkv, page, d, device=dev, generator=gen).bfloat16()
+    partial = torch.randn(splits, B, heads * d, device=dev, generator=gen) * 0.6
+    qw = (1 + 0.1 * torch.randn(d, device=dev, generator=gen)).bfloat16() if use_norm else None
+    kw = (1 + 0.1 * torch.randn(d, device=dev, generator=gen)).bfloat16() if use_norm else None
+    cos = sin = None
+    if use_rope:
+        cos, sin = (t.to(dev).contiguous() for t in plain.rope_tables(torch.arange(2100), d, 1e4))
+    table, positions, slots = table.to(dev), positions.to(dev), slots.to(dev)
+    request_of = torch.arange(B, dtype=torch.int32, device=dev)
+    make = lambda: ops.PartialSum(partial, splits, B, heads * d, torch.bfloat16, status)
+    common = dict(page_size=page, nq=nq, nkv=nkv, head_dim=d, scale=d ** -0.5, window=window, status=status)
+    # the two kernels
+    k1, v1 = k0.clone(), v0.clone()
+    q = ops.qkv_post(make(), k1, v1, nq=nq, nkv=nkv, head_dim=d, page_size=page, q_norm_w=qw, k_norm_w=kw, eps=1e-6, cos=cos,
+                     sin=sin, positions=positions, slot_mapping=slots, status=status)
+    want = torch.empty_like(q)
+    ops.attention_decode(q, k1, v1, want, token_list=None, count=B, positions=positions, request_of=request_of,
+                         block_table=table, max_kv_len=2048, **common)
+    # the one kernel
+    k2, v2 = k0.clone(), v0.clone()
+    got = ops.attention_decode_fused(make(), k2, v2, positions=positions, request_of=request_of, block_table=table,
+                                     slot_mapping=slots, max_kv_len=2048, q_norm_w=qw, k_norm_w=kw, eps=1e-6, cos=cos, sin=sin,
+                                     **common)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.equal(k1, k2) and torch.equal(v1, v2) and not torch.equal(k1, k0)
+    assert torch.equal(got, want)
+    # and the plain attention of the last request's token over its keys (no window: every key)
+    if window == 0:
+        b = B - 1
+        n = lengths[b]
+        rows = [int(table[b, i // page]) * page + i % page for i in range(n)]
+        keys = k2.permute(0, 2, 1, 3).reshape(-1, nkv, d)[rows].float().cpu()
+        values = v2.permute(0, 2, 1, 3).reshape(-1, nkv, d)[rows].float().cpu()
+        qb = q[b].float().cpu().view(nq, d)
+        ref = torch.zeros(nq, d)
+        for h in range(nq):
+            g = h * nkv // nq
+            p = torch.softmax((keys[:, g] @ qb[h]) * d ** -0.5, 0)
+            ref[h] = p @ values[:, g]
+        assert torch.allclose(got[b].float().cpu().view(nq, d), ref, atol=2e-2, rtol=2e-2)

@@ -22,6 +22,16 @@
 // scale * log2(e), causal up to the token's own position, optional window, P rounded to
 // bfloat16 before P.V (:246), out = acc / l (0 if l = 0).
 //
+// Fused form for steps in which every request brings one token: the kernel takes the QKV
+// projection's unsummed K-split partial sums instead of finished query rows. The producer sums
+// the splits of its item's query heads in split order, applies the per-head norm and the
+// rotation (the arithmetic of qkv_post.cu, operation by operation: head_post.cuh) and puts the
+// rows where the copies would have put them; for the item whose segment holds the token's own
+// position it does the same for the token's key and copies its value, stores both in the cache
+// for the steps to come and hands them to the consumers, which write them over the tile's row
+// for that position after the tile has landed (the cache row a box brings there is not yet the
+// new one). One kernel and one boundary less per layer.
+//
 // A box of 16 keys is read whole when pages hold a multiple of 16 tokens; the V rows of keys
 // beyond the token's position (or before its window) are overwritten with zeros in shared
 // memory and their scores masked, so what unused cache slots hold never reaches the
@@ -29,6 +39,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "head_post.cuh"
 #include "mma_util.cuh"
 #include "tensor_map.cuh"
 
@@ -133,22 +144,42 @@ __device__ __forceinline__ void merge_segments(const float* __restrict__ base, b
 }
 
 struct ItemMeta {
-  int t, pos, item, g, seg, kstart, request, pad;    // t < 0: no more items
+  int t, pos, item, g, seg, kstart, request, fresh;  // t < 0: no more items; fresh: the token's own key and value come with it
 };
 
-// DMAX bounds the head size; with EXACT the head size is DMAX itself.
-template <int DMAX, bool EXACT>
-__global__ void __launch_bounds__(THREADS)
+// What the fused form needs beside the attention's own arguments (partial == null: not fused).
+struct FusedProjection {
+  const float* partial;        // [splits][tokens][(nq + 2 nkv) d] float32
+  int splits;
+  long long plane;             // tokens * (nq + 2 nkv) * d
+  const void* q_norm_w;        // [d] or null: no head norm
+  const void* k_norm_w;
+  int norm_w_is_f32;
+  float eps;
+  const float* cos_table;      // [max_positions][d / 2] float32 or null: no rotation
+  const float* sin_table;
+  int max_positions;
+  const int* slot_mapping;     // [tokens] cache slot of each token's key and value, -1: none
+  long long num_slots;
+  bf16* k_cache;
+  bf16* v_cache;
+};
+
+// DMAX bounds the head size; with EXACT the head size is DMAX itself. FUSED: the query rows and
+// the token's own key and value are made here from the projection's partial sums (`fused`).
+template <int DMAX, bool EXACT, bool FUSED>
+__global__ void __launch_bounds__(THREADS, DMAX <= 128 ? 2 : 1)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const bf16* __restrict__ q, float* __restrict__ partial, bf16* __restrict__ out,
                         int* __restrict__ arrivals, const int* __restrict__ token_list,
                         const int* __restrict__ positions, const int* __restrict__ request_of,
                         const int* __restrict__ block_table, int max_pages, int page_size, int page_shift,
                         int num_pages, int whole_pages, int whole_rows, int count, int nq, int nkv, int d_runtime,
-                        int segment_keys, int max_segments, float scale_log2, int window, unsigned* status) {
+                        int segment_keys, int max_segments, float scale_log2, int window, unsigned* status,
+                        const FusedProjection fused) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[CONSUMERS][RING];
-  __shared__ __align__(8) uint64_t q_full[Q_BUFFERS], q_empty[Q_BUFFERS], meta_bar[Q_BUFFERS];
+  __shared__ __align__(8) uint64_t q_full[Q_BUFFERS], q_empty[Q_BUFFERS], meta_bar[Q_BUFFERS], fresh_bar[Q_BUFFERS];
   __shared__ ItemMeta item_meta[Q_BUFFERS];
   __shared__ ItemMeta consumer_meta;       // the consumers' common copy: they all take the same decisions
   __shared__ int tile_rows[Q_BUFFERS][MAX_SEGMENT_PAGES];   // cache row of each tile's first key (whole pages)
@@ -165,13 +196,16 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   uint8_t* ring_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_base = ring_base + CONSUMERS * RING * slot_bytes;                         // [Q_BUFFERS][16][q_pitch]
   float* merge = reinterpret_cast<float*>(q_base + Q_BUFFERS * 16 * q_pitch);         // [CONSUMERS][group][rec]
+  bf16* fresh_kv = reinterpret_cast<bf16*>(merge + CONSUMERS * group * rec);           // [Q_BUFFERS][2][d]: the token's own key, value
 
   if (threadIdx.x == 0) {
     abandoned = 0;
     for (int w = 0; w < CONSUMERS; ++w)
       for (int r = 0; r < RING; ++r) mb_init(smem_addr(&full_bar[w][r]), 1);
     for (int b = 0; b < Q_BUFFERS; ++b) {
-      mb_init(smem_addr(&q_full[b]), 1);
+      // fused: every consumer warp makes its share of the query rows and counts itself in
+      mb_init(smem_addr(&q_full[b]), FUSED ? CONSUMERS : 1);
+      mb_init(smem_addr(&fresh_bar[b]), 1);
       mb_init(smem_addr(&q_empty[b]), CONSUMERS);
       mb_init(smem_addr(&meta_bar[b]), 1);
     }
@@ -265,15 +299,47 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
           pdl_wait();
           waited = true;
         }
-        if (lane == 0) {
-          // the description first: the consumers request their tiles while the query rows travel
-          item_meta[qb] = ItemMeta{t, pos, item, g, seg, kstart, req, 0};
-          mb_arrive(smem_addr(&meta_bar[qb]));
-          mb_expect_tx(smem_addr(&q_full[qb]), (uint32_t)(group * d * 2));
-          // the item's query rows are contiguous in q: the heads of one group
-          for (int row = 0; row < group; ++row)
-            bulk_copy_g2s(smem_addr(q_base + (qb * 16 + row) * q_pitch), q + ((int64_t)t * nq + g * group + row) * d,
-                          (uint32_t)(d * 2), smem_addr(&q_full[qb]));
+        if (!FUSED) {
+          if (lane == 0) {
+            // the description first: the consumers request their tiles while the query rows travel
+            item_meta[qb] = ItemMeta{t, pos, item, g, seg, kstart, req, 0};
+            mb_arrive(smem_addr(&meta_bar[qb]));
+            mb_expect_tx(smem_addr(&q_full[qb]), (uint32_t)(group * d * 2));
+            // the item's query rows are contiguous in q: the heads of one group
+            for (int row = 0; row < group; ++row)
+              bulk_copy_g2s(smem_addr(q_base + (qb * 16 + row) * q_pitch), q + ((int64_t)t * nq + g * group + row) * d,
+                            (uint32_t)(d * 2), smem_addr(&q_full[qb]));
+          }
+        } else {
+          // ---- fused: the consumers make the query rows from the projection's partial sums; in the
+          // segment of the token's own position the producer makes the token's key and value
+          int64_t slot = -1;
+          if (pos / segment_keys == seg && fused.slot_mapping != nullptr) {
+            slot = fused.slot_mapping[t];
+            if (slot >= fused.num_slots || slot < -1) {
+              if (lane == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+              slot = -1;
+            }
+          }
+          if (lane == 0) {
+            item_meta[qb] = ItemMeta{t, pos, item, g, seg, kstart, req, slot >= 0 ? 1 : 0};
+            mb_arrive(smem_addr(&meta_bar[qb]));
+          }
+          if (slot >= 0) {
+            int rope_pos = pos;
+            if (fused.cos_table != nullptr && (pos < 0 || pos >= fused.max_positions)) rope_pos = 0;   // (the consumers report it)
+            const float* token_partial = fused.partial + (int64_t)t * (nq + 2 * nkv) * d;
+            // cache row of the slot: [pages, kv heads, page_size, d]
+            const int64_t cache_row = ((slot / page_size) * nkv + g) * page_size + slot % page_size;
+            bf16* mine = fresh_kv + (int64_t)qb * 2 * d;
+            head_from_partial<bf16, (DMAX + 63) / 64>(token_partial + (int64_t)(nq + g) * d, fused.splits, fused.plane, d, lane, fused.k_norm_w,
+                              fused.norm_w_is_f32, fused.eps, fused.cos_table, fused.sin_table, rope_pos, mine,
+                              fused.k_cache + cache_row * d);
+            head_from_partial<bf16, (DMAX + 63) / 64>(token_partial + (int64_t)(nq + nkv + g) * d, fused.splits, fused.plane, d, lane, nullptr, 0,
+                              fused.eps, nullptr, nullptr, 0, mine + d, fused.v_cache + cache_row * d);
+            __syncwarp();
+            if (lane == 0) mb_arrive(smem_addr(&fresh_bar[qb]));     // key and value are in shared memory
+          }
         }
         ++q_issued;
       }
@@ -302,6 +368,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const uint32_t v_lane = v_row * 128, v_xor = (uint32_t)((v_half ^ (v_row & 7)) << 4);
   pdl_wait();
   uint32_t seen = 0, n_issued = 0, q_seen = 0;       // tiles consumed and requested by this warp, items seen
+  uint32_t fresh_seen[Q_BUFFERS] = {0, 0};           // items with a fresh key and value seen so far, per buffer
   int ahead = 0;                                     // tiles of the next item already requested
   bool pending = false;                              // an item whose partials are written but not counted in
   int p_item = 0, p_g = 0, p_t = 0, p_first = 0, p_last = 0;
@@ -406,6 +473,21 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     ItemMeta next_meta = ItemMeta{-1, 0, 0, 0, 0, 0, 0, 0};
     int next_first = 0, next_tiles = 0;
 
+    if (FUSED) {
+      // ---- fused: this warp's share of the item's query rows, from the projection's partial sums
+      int rope_pos = pos;
+      if (fused.cos_table != nullptr && (pos < 0 || pos >= fused.max_positions)) {
+        if (ctid == 0) raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
+        rope_pos = 0;
+      }
+      const float* token_partial = fused.partial + (int64_t)meta.t * (nq + 2 * nkv) * d;
+      for (int row = cw; row < group; row += CONSUMERS)
+        head_from_partial<bf16, (DMAX + 63) / 64>(token_partial + (int64_t)(g * group + row) * d, fused.splits, fused.plane, d, lane, fused.q_norm_w,
+                          fused.norm_w_is_f32, fused.eps, fused.cos_table, fused.sin_table, rope_pos,
+                          reinterpret_cast<bf16*>(q_base + (qb * 16 + row) * q_pitch), (bf16*)nullptr);
+      __syncwarp();
+      if (lane == 0) mb_arrive(smem_addr(&q_full[qb]));
+    }
     // ---- Q fragments of this item into registers (up to head size 128)
     wait_or_abandon(smem_addr(&q_full[qb]), (q_seen / Q_BUFFERS) & 1, status, &abandoned);
     const uint8_t* q_s = q_base + qb * 16 * q_pitch;
@@ -430,6 +512,21 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       const uint32_t vs = ks + nb * BLOCK_BYTES;
       const int key0 = first_tile + tile * TILE;
       bool edge = false;
+      if (FUSED && meta.fresh && pos >= key0 && pos < key0 + TILE) {
+        // the token's own key and value, made by the producer: over the row the box brought
+        wait_or_abandon(smem_addr(&fresh_bar[qb]), fresh_seen[qb] & 1, status, &abandoned);
+        const int r = pos - key0;
+        const uint4* src = reinterpret_cast<const uint4*>(fresh_kv + (int64_t)qb * 2 * d);
+        uint8_t* tile = ring_base + (cw * RING + slot) * slot_bytes;
+        const int chunks = d >> 3;                     // 16-byte pieces of a row
+        for (int i = lane; i < 2 * chunks; i += 32) {
+          const int c = i % chunks;                    // piece of the key (i < chunks) or of the value
+          uint8_t* block = tile + ((i < chunks ? 0 : nb) + (c >> 3)) * BLOCK_BYTES;
+          *reinterpret_cast<uint4*>(block + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = src[i];
+        }
+        edge = true;                                   // written by threads: fence before the slot is refilled
+        __syncwarp();
+      }
       if (whole_pages && (key0 < kstart || key0 + TILE - 1 > pos)) {
         // a box brought keys that are masked: their V rows must not reach the MMA (0 * NaN)
         edge = true;
@@ -524,6 +621,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
     // the description (and with head sizes above 128 the Q rows) of this item is not needed any more
     __syncwarp();
+    if (FUSED && meta.fresh) ++fresh_seen[qb];                // (whether or not this warp had the tile of the token's position)
     if (lane == 0) mb_arrive(smem_addr(&q_empty[qb]));
     ++q_seen;
 
@@ -595,7 +693,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 size_t decode_smem_bytes(int d, int group) {
   const size_t nb = (d + BOX_COLS - 1) / BOX_COLS;
   return 1024 + (size_t)CONSUMERS * RING * 2 * nb * BLOCK_BYTES + (size_t)Q_BUFFERS * 16 * ((size_t)d * 2 + 16) +
-         (size_t)CONSUMERS * group * (d + 2) * sizeof(float);
+         (size_t)CONSUMERS * group * (d + 2) * sizeof(float) + (size_t)Q_BUFFERS * 2 * d * 2;
 }
 
 int sm_count() {
@@ -673,11 +771,12 @@ VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int nkv, int
 // q, out: bf16 [tokens_total, nq, d]; the kernel serves `count` tokens: those listed in
 // token_list (int32[count]) or tokens 0..count-1. scratch holds the partial records of the
 // launch (vosti_attention_decode_scratch elements) and may be reused by the next launch.
-VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* scratch,
-                                     int64_t scratch_elems, int* arrivals, const int* token_list, int count, int tokens_total,
-                                     const int* positions, const int* request_of, const int* block_table, int max_pages,
-                                     int page_size, int num_pages, int nq, int nkv, int d, int max_kv_len, float scale,
-                                     int window, unsigned* status, cudaStream_t stream) {
+namespace {
+int launch_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* scratch,
+                  int64_t scratch_elems, int* arrivals, const int* token_list, int count, int tokens_total,
+                  const int* positions, const int* request_of, const int* block_table, int max_pages,
+                  int page_size, int num_pages, int nq, int nkv, int d, int max_kv_len, float scale,
+                  int window, unsigned* status, cudaStream_t stream, const FusedProjection& fused) {
   VOSTI_REQUIRE(count >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention_decode: bad head counts nq=%d nkv=%d", nq, nkv);
   VOSTI_REQUIRE(nq / nkv <= 16, "attention_decode: at most 16 query heads per kv head, got %d", nq / nkv);
   VOSTI_REQUIRE(d > 0 && d % 16 == 0 && d <= 256, "attention_decode: head_dim %d must be a multiple of 16 and <= 256", d);
@@ -709,18 +808,23 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
-#define LAUNCH_DECODE(DMAX, EXACT)                                                                                  \
+#define LAUNCH_DECODE_AS(DMAX, EXACT, FUSED)                                                                        \
   do {                                                                                                              \
     static bool configured = false;                                                                                 \
     if (!configured) {                                                                                              \
-      cudaFuncSetAttribute(attention_decode_kernel<DMAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+      cudaFuncSetAttribute(attention_decode_kernel<DMAX, EXACT, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)decode_smem_bytes(DMAX, 16));                                                       \
       configured = true;                                                                                            \
     }                                                                                                               \
-    vosti_launch(attention_decode_kernel<DMAX, EXACT>, grid, dim3(THREADS), smem, stream, map_k, map_v,             \
+    vosti_launch(attention_decode_kernel<DMAX, EXACT, FUSED>, grid, dim3(THREADS), smem, stream, map_k, map_v,      \
         (const bf16*)q, scratch, (bf16*)out, arrivals, token_list, positions, request_of,                          \
         block_table, max_pages, page_size, page_shift, num_pages, whole_pages, whole_rows, count, nq, nkv, d, segment_keys,     \
-        segments, scale * LOG2E, window, status);                                                                   \
+        segments, scale * LOG2E, window, status, fused);                                                            \
+  } while (0)
+#define LAUNCH_DECODE(DMAX, EXACT)                                                                                  \
+  do {                                                                                                              \
+    if (fused.partial != nullptr) LAUNCH_DECODE_AS(DMAX, EXACT, true);                                              \
+    else LAUNCH_DECODE_AS(DMAX, EXACT, false);                                                                      \
   } while (0)
   if (d == 64) LAUNCH_DECODE(64, true);
   else if (d == 128) LAUNCH_DECODE(128, true);
@@ -729,5 +833,55 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
   else if (d < 128) LAUNCH_DECODE(128, false);
   else LAUNCH_DECODE(256, false);
 #undef LAUNCH_DECODE
+#undef LAUNCH_DECODE_AS
   VOSTI_LAUNCH_CHECK();
+}
+}  // namespace
+
+VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* scratch,
+                                     int64_t scratch_elems, int* arrivals, const int* token_list, int count, int tokens_total,
+                                     const int* positions, const int* request_of, const int* block_table, int max_pages,
+                                     int page_size, int num_pages, int nq, int nkv, int d, int max_kv_len, float scale,
+                                     int window, unsigned* status, cudaStream_t stream) {
+  FusedProjection none = {};
+  return launch_decode(q, k_cache, v_cache, out, scratch, scratch_elems, arrivals, token_list, count, tokens_total, positions,
+                       request_of, block_table, max_pages, page_size, num_pages, nq, nkv, d, max_kv_len, scale, window,
+                       status, stream, none);
+}
+
+// The fused form: `partial` holds the QKV projection's K-split partial sums of the step's tokens
+// ([splits][tokens][(nq + 2 nkv) d] float32, every request bringing one token, token i being row i);
+// the kernel sums them, applies head norm and rotation, stores the new keys and values in the
+// caches at slot_mapping and attends. q_norm_w / k_norm_w null: no head norm; cos / sin null: no
+// rotation (float32 tables [max_positions][d / 2]). Head sizes up to 512 in steps of 16 as the
+// unfused kernel; d must be even.
+VOSTI_API int vosti_attention_decode_fused(const float* partial, int splits, void* k_cache, void* v_cache, void* out,
+                                           float* scratch, int64_t scratch_elems, int* arrivals, int count,
+                                           const int* positions, const int* request_of, const int* block_table,
+                                           int max_pages, int page_size, int num_pages, int nq, int nkv, int d,
+                                           int max_kv_len, float scale, int window, const void* q_norm_w,
+                                           const void* k_norm_w, int norm_w_is_f32, float eps, const float* cos_table,
+                                           const float* sin_table, int max_positions, const int* slot_mapping,
+                                           unsigned* status, cudaStream_t stream) {
+  VOSTI_REQUIRE(partial != nullptr && splits >= 1, "attention_decode_fused: the partial sums are missing");
+  VOSTI_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "attention_decode_fused: cos and sin go together");
+  VOSTI_REQUIRE(d % 2 == 0 && d / 2 <= 32 * HEAD_MAX_PAIRS, "attention_decode_fused: head_dim %d is too large", d);
+  FusedProjection fused = {};
+  fused.partial = partial;
+  fused.splits = splits;
+  fused.plane = (long long)count * (nq + 2 * nkv) * d;
+  fused.q_norm_w = q_norm_w;
+  fused.k_norm_w = k_norm_w;
+  fused.norm_w_is_f32 = norm_w_is_f32;
+  fused.eps = eps;
+  fused.cos_table = cos_table;
+  fused.sin_table = sin_table;
+  fused.max_positions = max_positions;
+  fused.slot_mapping = slot_mapping;
+  fused.num_slots = (long long)num_pages * page_size;
+  fused.k_cache = (bf16*)k_cache;
+  fused.v_cache = (bf16*)v_cache;
+  return launch_decode(nullptr, k_cache, v_cache, out, scratch, scratch_elems, arrivals, nullptr, count, count, positions,
+                       request_of, block_table, max_pages, page_size, num_pages, nq, nkv, d, max_kv_len, scale, window,
+                       status, stream, fused);
 }

@@ -8,9 +8,10 @@
 // The reference rounds to bf16 between the norm and the rotation; this kernel keeps
 // float32 there and rounds once at the store.
 #include "common.cuh"
+#include "head_post.cuh"
 
 namespace {
-constexpr int MAX_PAIRS_PER_LANE = 8;  // head_dim <= 512
+constexpr int MAX_PAIRS_PER_LANE = HEAD_MAX_PAIRS;  // head_dim <= 512
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -71,6 +72,13 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
       const int g = is_k ? h - nq : h - nq - nkv;
       // caches are [pages, kv heads, page_size, d]: a head's tokens of a page are contiguous
       dst = (is_k ? k_cache : v_cache) + (((slot / page_size) * nkv + g) * page_size + slot % page_size) * d;
+    }
+    if (partial != nullptr) {
+      // from the projection's partial sums: the arithmetic the fused decode attention shares
+      const bool rotated = is_q || is_k;
+      head_from_partial<T>(psrc, splits, plane, d, lane, is_q ? q_norm_w : (is_k ? k_norm_w : nullptr), norm_w_is_f32, eps,
+                           rotated ? cos_table : nullptr, rotated ? sin_table : nullptr, pos, dst, (T*)nullptr);
+      continue;
     }
     if (!is_q && !is_k) {  // value head: plain copy
       for (int i = lane; i < d; i += 32) dst[i] = partial == nullptr ? src[i] : from_f32<T>(load(i));

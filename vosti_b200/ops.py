@@ -511,6 +511,45 @@ def attention_decode(q, k_cache, v_cache, out, *, token_list, count, positions, 
         "attention_decode")
 
 
+DECODE_FUSION = _os.environ.get("VOSTI_DECODE_FUSION", "1") != "0"
+
+
+def attention_decode_fused(qkv: "PartialSum", k_cache, v_cache, *, positions, request_of, block_table, slot_mapping,
+                           page_size, nq, nkv, head_dim, max_kv_len, scale, window, q_norm_w, k_norm_w, eps, cos, sin,
+                           status) -> torch.Tensor:
+    """Head norm, rotation, cache store and single-query attention in one kernel, for a step in
+    which every request brings one token: `qkv` is the QKV projection's unsummed split-K result
+    (row i = token i = request i). Returns the attention output [tokens, nq * head_dim]."""
+    qkv.check()
+    lib = library()
+    count = qkv.rows
+    if qkv.width != (nq + 2 * nkv) * head_dim or qkv.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_fused: the projection does not match the head counts or is not bfloat16")
+    _contig(k_cache, v_cache, positions, request_of, block_table, slot_mapping, q_norm_w, k_norm_w, cos, sin)
+    norm_flag = 0
+    if q_norm_w is not None:
+        norm_flag = _is_f32(q_norm_w)
+        if k_norm_w is not None and _is_f32(k_norm_w) != norm_flag:
+            raise KernelError("attention_decode_fused: q and k norm weights must share a dtype")
+    elif k_norm_w is not None:
+        norm_flag = _is_f32(k_norm_w)
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != head_dim // 2):
+        raise KernelError("attention_decode_fused: rotation tables must be float32 [positions, head_dim/2]")
+    out = torch.empty((count, nq * head_dim), dtype=torch.bfloat16, device=qkv.partial.device)
+    lib.vosti_attention_decode_scratch.restype = ctypes.c_int64
+    elems = lib.vosti_attention_decode_scratch(count, nq, nkv, head_dim, max_kv_len)
+    scratch = _workspace(out.device, elems)
+    arrivals = _counters(out.device, count * nkv)
+    num_pages = k_cache.numel() // (page_size * nkv * head_dim)
+    _check(lib.vosti_attention_decode_fused(
+        _p(qkv.partial), qkv.splits, _p(k_cache), _p(v_cache), _p(out), _p(scratch), ctypes.c_int64(scratch.numel()),
+        _p(arrivals), count, _p(positions), _p(request_of), _p(block_table), block_table.shape[1], page_size, num_pages,
+        nq, nkv, head_dim, max_kv_len, ctypes.c_float(scale), window, _p(q_norm_w), _p(k_norm_w), norm_flag,
+        ctypes.c_float(eps), _p(cos), _p(sin), 0 if cos is None else cos.shape[0], _p(slot_mapping), _p(status),
+        _stream()), "attention_decode_fused")
+    return out
+
+
 def attention_prefill(q, k_cache, v_cache, out, *, row_list, count, cu_q, kv_len, block_table, page_size, nq, nkv,
                       head_dim, max_q_len, scale, window, status, kernel: Optional[str] = None) -> None:
     """Attention of whole portions for `count` requests (bfloat16). Head sizes 64 and 128 with

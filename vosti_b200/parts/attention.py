@@ -98,6 +98,18 @@ class Attention(Mixer):
                       positions=ctx.positions, status=ctx.status)
         if writes_cache:
             qkv = linear(ctx, x, self.w_qkv, allow_partial=True, bias=self.b_qkv)   # summed inside qkv_post
+            if (ops.DECODE_FUSION and isinstance(qkv, ops.PartialSum) and qkv.dtype == torch.bfloat16
+                    and ctx.num_short_tokens == ctx.num_tokens == ctx.num_requests and ctx.short_tokens is None
+                    and self.nq // self.nkv <= 16 and cache.k.dtype == torch.bfloat16):
+                # every request brings one token: head norm, rotation, cache store and attention in
+                # one kernel, straight from the projection's partial sums
+                attn = ops.attention_decode_fused(
+                    qkv, cache.k, cache.v, positions=ctx.positions, request_of=ctx.request_of,
+                    block_table=group.block_table, slot_mapping=group.slot_mapping, page_size=group.page_size,
+                    nq=self.nq, nkv=self.nkv, head_dim=self.d, max_kv_len=ctx.max_kv_len, scale=self.scale,
+                    window=self.window, q_norm_w=self.q_norm, k_norm_w=self.k_norm, eps=eps, cos=cos, sin=sin,
+                    status=ctx.status)
+                return linear(ctx, attn, self.w_o, allow_partial=True, bias=self.b_o)
             q = ops.qkv_post(qkv, cache.k, cache.v, nkv=self.nkv, k_norm_w=self.k_norm,
                              slot_mapping=group.slot_mapping, **common)
         elif self.w_q is not None:
