@@ -51,8 +51,12 @@ def test_position_part_tables():
     cos, sin = rope.rotation_tables()
     want_c, want_s = plain.rope_tables(torch.arange(300), 48, 50000.0)
     assert cos.dtype == torch.float32 and torch.equal(cos.cpu(), want_c) and torch.equal(sin.cpu(), want_s)
-    with pytest.raises(Exception):
-        build_position(PartSpec.make("rope", theta=1e4, rotary_dim=24, max_positions=8), 80, 48)
+    for bad in (25, 64, 0 - 2):
+        with pytest.raises(Exception):
+            build_position(PartSpec.make("rope", theta=1e4, rotary_dim=bad, max_positions=8), 80, 48)
+    part = build_position(PartSpec.make("rope", theta=1e4, rotary_dim=24, max_positions=8, interleaved=True), 80, 48)
+    part.setup(torch.device(DEV), torch.bfloat16)
+    assert part.rotary_dim == 24 and part.interleaved and part.rotation_tables()[0].shape == (8, 12)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -332,3 +336,51 @@ def test_windowed_layer_beside_a_full_one_has_pages_of_its_own(dtype):
     full_pool, window_pool = (g.pool for g in small.cache.groups)
     assert full_pool.held() == 15 and window_pool.held() <= 3
     small.check_status()
+
+
+def rotate_reference(x, positions, rotary_dim, theta, interleaved):
+    """x: [T, heads, d]; the first rotary_dim elements of every head rotated by angle position *
+    theta^(-2i/rotary_dim), pairs (i, i + rotary_dim/2) or (2i, 2i + 1); the rest unchanged."""
+    cos, sin = plain.rope_tables(positions, rotary_dim, theta)
+    c, s = cos[:, None, :].double(), sin[:, None, :].double()
+    out = x.double().clone()
+    half = rotary_dim // 2
+    ia = torch.arange(half) * 2 if interleaved else torch.arange(half)
+    ib = ia + 1 if interleaved else ia + half
+    a, b = x.double()[..., ia], x.double()[..., ib]
+    out[..., ia] = a * c - b * s
+    out[..., ib] = b * c + a * s
+    return out.float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rotary_dim,interleaved", [(16, False), (32, True), (8, True)])
+def test_partial_and_interleaved_rotations_through_the_attention_part(dtype, rotary_dim, interleaved):
+    """A rotation of only the first elements of a head, or of neighbouring pairs, as a parameter of
+    the built-in position encoding: the attention part fed in portions and single tokens equals a
+    plain attention over queries and keys rotated by the formula."""
+    nq, nkv, d, hidden = 4, 2, 32, 80
+    spec = PartSpec.make("attention", num_heads=nq, num_kv_heads=nkv, head_dim=d, head_norm_eps=1e-5, window=0, scale=d ** -0.5)
+    mixer = build_mixer(spec, hidden, PartSpec.make("rope", theta=3e4, rotary_dim=rotary_dim, max_positions=128,
+                                                    interleaved=interleaved))
+    W = load(mixer, 7, dtype, scale=4.0)
+    harness = Harness([mixer.cache_spec()], [None], dtype, num_pages=16, page_size=8)
+    T = 45
+    x = torch.randn(T, hidden).to(dtype)
+    outs, at = [], 0
+    for size in (9, 1, 1, 30, 2, 1, 1):
+        ctx = harness.context([StepEntry("s", [0] * size)])
+        outs.append(mixer.forward(ctx, x[at:at + size].to(DEV), harness.cache.layer_caches[0]).float().cpu())
+        at += size
+    xf = x.float()
+    q = plain.head_rms_norm((xf @ W["q_proj.weight"].T).view(T, nq, d), W["q_norm.weight"], 1e-5)
+    k = plain.head_rms_norm((xf @ W["k_proj.weight"].T).view(T, nkv, d), W["k_norm.weight"], 1e-5)
+    v = (xf @ W["v_proj.weight"].T).view(T, nkv, d)
+    positions = torch.arange(T)
+    q, k = (rotate_reference(t, positions, rotary_dim, 3e4, interleaved) for t in (q, k))
+    want = plain.causal_attention(q, k, v, d ** -0.5).reshape(T, nq * d) @ W["o_proj.weight"].T
+    assert torch.allclose(torch.cat(outs), want, **tol(dtype))
+    full = plain.attention_block(xf, positions, {("p." + n): t for n, t in W.items()}, "p.",
+                                 dict(num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d, rms_norm_eps=1e-5, rope_theta=3e4))
+    assert (full - want).abs().max() > 0.05                      # not the whole-head half-split rotation
+    assert harness.status.item() == 0

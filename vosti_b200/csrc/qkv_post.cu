@@ -246,6 +246,72 @@ qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf1
     }
   }
 }
+
+// The same pass for rotations that are not the half-split rotation of the whole head: only the
+// first `rotary_dim` elements of a head are rotated (pairs (i, i + rotary_dim/2)), or the pairs
+// are neighbours (2i, 2i + 1) ("interleaved"); the rest of the head passes through after the
+// norm. One block per (token, head), the head in shared memory: slow and plain, for
+// architectures whose position encoding asks for it (Qwen3 does not).
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_post_general_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, int splits, int64_t plane,
+                        T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                        const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_w_is_f32, float eps,
+                        const float* __restrict__ cos_table, const float* __restrict__ sin_table, int max_positions,
+                        const int* __restrict__ positions, const int* __restrict__ slot_mapping, int64_t num_slots,
+                        int page_size, int nq, int nkv, int d, int rotary_dim, int interleaved, unsigned* status) {
+  __shared__ float scratch[32];
+  extern __shared__ float head[];                      // d floats
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int heads = nq + 2 * nkv;
+  const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+  pdl_wait();
+  pdl_launch_dependents();
+  int pos = positions ? positions[t] : 0;
+  if (cos_table && (pos < 0 || pos >= max_positions)) {
+    if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
+    pos = 0;
+  }
+  T* dst;
+  if (is_q) {
+    dst = q_out + ((int64_t)t * nq + h) * d;
+  } else {
+    int64_t slot = slot_mapping ? slot_mapping[t] : -1;
+    if (slot >= num_slots || slot < -1) {
+      if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
+      slot = -1;
+    }
+    if (slot < 0) return;
+    const int g = is_k ? h - nq : h - nq - nkv;
+    dst = (is_k ? k_cache : v_cache) + (((slot / page_size) * nkv + g) * page_size + slot % page_size) * d;
+  }
+  const int64_t at = ((int64_t)t * heads + h) * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = 0.f;
+    if (partial == nullptr) v = to_f32(qkv[at + i]);
+    else for (int s = 0; s < splits; ++s) v += partial[s * plane + at + i];
+    head[i] = v;
+    ss += v * v;
+  }
+  const void* w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+  const float total = block_sum(ss, scratch);          // (also: the head is complete in shared memory)
+  if (w != nullptr) {
+    const float rrms = rsqrtf(total / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) head[i] = head[i] * rrms * load_flex(w, norm_w_is_f32, i);
+    __syncthreads();
+  }
+  const bool rotated = (is_q || is_k) && cos_table != nullptr;
+  const int rd = rotated ? rotary_dim : 0, half = rd >> 1;
+  for (int p = threadIdx.x; p < half; p += blockDim.x) {
+    const int ia = interleaved ? 2 * p : p, ib = interleaved ? 2 * p + 1 : p + half;
+    const float c = cos_table[(int64_t)pos * half + p], sn = sin_table[(int64_t)pos * half + p];
+    const float a = head[ia], b = head[ib];
+    dst[ia] = from_f32<T>(a * c - b * sn);
+    dst[ib] = from_f32<T>(b * c + a * sn);
+  }
+  for (int i = rd + threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(head[i]);
+}
 }  // namespace
 
 // qkv: [tokens, (nq + 2*nkv) * d], or null with `partial`: float32 [splits, tokens, (nq + 2*nkv) * d],
@@ -254,13 +320,16 @@ qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf1
 // slot s is (page s / page_size, offset s % page_size).
 // nkv == 0: the input holds query heads only and nothing is stored.
 // q_norm_w / k_norm_w null: no head norm. cos/sin null: no rotation; else float32
-// tables [max_positions, d/2].
+// tables [max_positions, rotary_dim/2]: the first rotary_dim elements of q and k heads are rotated,
+// pairs (i, i + rotary_dim/2) or, with `interleaved`, (2i, 2i + 1).
 VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, void* q_out, void* k_cache, void* v_cache, const void* q_norm_w,
                              const void* k_norm_w, int norm_w_is_f32, float eps, const float* cos_table,
                              const float* sin_table, int max_positions, const int* positions,
                              const int* slot_mapping, int64_t num_slots, int page_size, int tokens, int nq, int nkv, int d,
-                             int is_f32, unsigned* status, cudaStream_t stream) {
+                             int rotary_dim, int interleaved, int is_f32, unsigned* status, cudaStream_t stream) {
   VOSTI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && d > 0, "qkv_post: bad sizes");
+  VOSTI_REQUIRE(cos_table == nullptr || (rotary_dim > 0 && rotary_dim <= d && rotary_dim % 2 == 0),
+                "qkv_post: rotary_dim %d must be even and between 2 and head_dim %d", rotary_dim, d);
   VOSTI_REQUIRE(nkv == 0 || page_size > 0, "qkv_post: page_size must be positive");
   VOSTI_REQUIRE((qkv != nullptr) != (partial != nullptr), "qkv_post: give the projection or its partial sums");
   VOSTI_REQUIRE(partial == nullptr || splits >= 1, "qkv_post: bad split count");
@@ -271,6 +340,20 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
   VOSTI_REQUIRE(cos_table == nullptr || positions != nullptr, "qkv_post: rotation needs positions");
   if (tokens == 0) return VOSTI_OK;
   const int heads = nq + 2 * nkv;
+  if (cos_table != nullptr && (rotary_dim != d || interleaved)) {
+    VOSTI_REQUIRE(heads <= 65535, "qkv_post: too many heads for one launch");
+    const dim3 grid(tokens, heads);
+    const size_t smem = (size_t)d * sizeof(float);
+    if (is_f32)
+      vosti_launch(qkv_post_general_kernel<float>, grid, dim3(128), smem, stream, (const float*)qkv, partial, splits, plane,
+                   (float*)q_out, (float*)k_cache, (float*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table,
+                   max_positions, positions, slot_mapping, num_slots, page_size, nq, nkv, d, rotary_dim, interleaved, status);
+    else
+      vosti_launch(qkv_post_general_kernel<bf16>, grid, dim3(128), smem, stream, (const bf16*)qkv, partial, splits, plane,
+                   (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table,
+                   max_positions, positions, slot_mapping, num_slots, page_size, nq, nkv, d, rotary_dim, interleaved, status);
+    VOSTI_LAUNCH_CHECK();
+  }
   if (!is_f32 && partial == nullptr && tokens >= 64 && !g_vosti_fixed_order && (d == 64 || d == 128 || d == 256)) {
     // many tokens: a block per token, vector accesses
 #define LAUNCH_QKV_POST_WIDE(VE)                                                                                   \

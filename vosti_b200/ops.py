@@ -179,9 +179,12 @@ def qkv_post(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Option
              nq: int, nkv: int, head_dim: int, page_size: int = 1, q_norm_w: Optional[torch.Tensor] = None,
              k_norm_w: Optional[torch.Tensor] = None, eps: float = 1.0, cos: Optional[torch.Tensor] = None,
              sin: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
-             slot_mapping: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+             slot_mapping: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+             rotary_dim: Optional[int] = None, interleaved: bool = False) -> torch.Tensor:
     """Head norm, rotation and cache store after the QKV projection; returns q [T, nq*d].
-    `qkv` may be the projection or the unsummed partial sums of its split-K product."""
+    `qkv` may be the projection or the unsummed partial sums of its split-K product. The
+    rotation takes the first `rotary_dim` elements of a head (default: all of it) in pairs
+    (i, i + rotary_dim/2), or (2i, 2i + 1) with `interleaved`; cos/sin are [positions, rotary_dim/2]."""
     partial, splits = None, 0
     if isinstance(qkv, PartialSum):
         qkv.check()
@@ -206,12 +209,14 @@ def qkv_post(qkv: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Option
     elif k_norm_w is not None:
         norm_flag = _is_f32(k_norm_w)
     max_positions = 0 if cos is None else cos.shape[0]
-    if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != head_dim // 2):
-        raise KernelError("qkv_post: rotation tables must be float32 [positions, head_dim/2]")
+    rotary_dim = head_dim if rotary_dim is None else int(rotary_dim)
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape):
+        raise KernelError("qkv_post: rotation tables must be float32 [positions, rotary_dim/2]")
     _check(library().vosti_qkv_post(
         _p(qkv), _p(partial), splits, _p(q_out), _p(k_cache), _p(v_cache), _p(q_norm_w), _p(k_norm_w), norm_flag,
         ctypes.c_float(eps), _p(cos), _p(sin), max_positions, _p(positions), _p(slot_mapping),
-        ctypes.c_int64(num_slots), page_size, tokens, nq, nkv, head_dim, flag, _p(status), _stream()), "qkv_post")
+        ctypes.c_int64(num_slots), page_size, tokens, nq, nkv, head_dim, rotary_dim, int(bool(interleaved)), flag,
+        _p(status), _stream()), "qkv_post")
     return q_out
 
 

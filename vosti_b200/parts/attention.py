@@ -94,13 +94,16 @@ class Attention(Mixer):
         tables = self.position.rotation_tables() if self.position is not None else None
         cos, sin = tables if tables is not None else (None, None)
         eps = self.head_norm_eps if self.head_norm_eps is not None else 1.0
+        rotary_dim = getattr(self.position, "rotary_dim", None) or self.d
+        interleaved = bool(getattr(self.position, "interleaved", False))
         common = dict(nq=self.nq, head_dim=self.d, page_size=group.page_size, q_norm_w=self.q_norm, eps=eps, cos=cos, sin=sin,
-                      positions=ctx.positions, status=ctx.status)
+                      positions=ctx.positions, status=ctx.status, rotary_dim=rotary_dim, interleaved=interleaved)
         if writes_cache:
             qkv = linear(ctx, x, self.w_qkv, allow_partial=True, bias=self.b_qkv)   # summed inside qkv_post
             if (ops.DECODE_FUSION and isinstance(qkv, ops.PartialSum) and qkv.dtype == torch.bfloat16
                     and ctx.num_short_tokens == ctx.num_tokens == ctx.num_requests and ctx.short_tokens is None
-                    and self.nq // self.nkv <= 16 and cache.k.dtype == torch.bfloat16):
+                    and self.nq // self.nkv <= 16 and cache.k.dtype == torch.bfloat16
+                    and (cos is None or (rotary_dim == self.d and not interleaved))):
                 # every request brings one token: head norm, rotation, cache store and attention in
                 # one kernel, straight from the projection's partial sums
                 attn = ops.attention_decode_fused(

@@ -91,9 +91,14 @@ class PositionEncoding(Part):
         super().__init__(spec, hidden_size)
         self.head_dim = head_dim
 
+    # A rotation takes the first `rotary_dim` elements of every q and k head (None: the whole
+    # head) in pairs (i, i + rotary_dim/2), or neighbours (2i, 2i + 1) if `interleaved`.
+    rotary_dim: Optional[int] = None
+    interleaved: bool = False
+
     def rotation_tables(self) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
-        """float32 cos and sin [max_positions, head_dim/2] for a half-split rotation of q
-        and k, or None if this encoding is not a rotation."""
+        """float32 cos and sin [max_positions, rotary_dim/2] for the rotation of q and k, or
+        None if this encoding is not a rotation."""
         return None
 
 
