@@ -384,3 +384,29 @@ def test_partial_and_interleaved_rotations_through_the_attention_part(dtype, rot
                                  dict(num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d, rms_norm_eps=1e-5, rope_theta=3e4))
     assert (full - want).abs().max() > 0.05                      # not the whole-head half-split rotation
     assert harness.status.item() == 0
+
+
+def test_a_part_can_ask_for_index_arrays_of_its_own_in_every_step():
+    """A step-layout provider registered from outside the framework: its arrays travel with the
+    step's one copy and reach the parts through the context, beside the attention's own lists."""
+    from vosti_b200.parts import register_step_layout
+    from vosti_b200.parts.base import step_layout_providers
+
+    def starts_and_longest(q_lens):
+        starts, at = [], 0
+        for n in q_lens:
+            starts.append(at)
+            at += n
+        return {"starts": starts, "nothing": []}, {"longest": max(q_lens)}
+
+    register_step_layout("toy_lists", starts_and_longest)
+    try:
+        harness = Harness([attention_layer().mixer and build_mixer(attention_layer().mixer, 32, attention_layer().position).cache_spec()],
+                          [None], torch.bfloat16)
+        ctx = harness.context([StepEntry("a", [1] * 7), StepEntry("b", [2]), StepEntry("c", [3] * 5)])
+        assert ctx.extras["toy_lists.starts"].tolist() == [0, 7, 8] and ctx.layout["toy_lists"] == {"longest": 7}
+        assert ctx.extras["toy_lists.nothing"].numel() == 0
+        assert ctx.layout["attention"] == {"num_short_tokens": 1, "num_long_rows": 2, "max_long_q_len": 7}
+        assert ctx.extras["attention.short_tokens"].tolist() == [7] and ctx.extras["attention.long_rows"].tolist() == [0, 2]
+    finally:
+        step_layout_providers().pop("toy_lists")

@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from .. import host, ops
+from ..parts.base import step_layout_providers
 
 
 @dataclass
@@ -66,13 +67,9 @@ class StepContext:
     # extras["feedback"] (int32 [T], -1 or an index) names tokens to take from this device array
     # instead of `tokens`: what the step before sampled and the host has not read yet
     feedback_values: Optional[torch.Tensor] = None
-    # attention work lists: tokens of requests that bring at most SHORT_ROW tokens (served
-    # one query at a time) and the requests that bring more (served as portions)
-    short_tokens: Optional[torch.Tensor] = None   # int32 token indices, None: every token
-    num_short_tokens: int = 0
-    long_rows: Optional[torch.Tensor] = None      # int32 request rows, None: every request
-    num_long_rows: int = 0
-    max_long_q_len: int = 0
+    # what the registered step-layout providers made of the step's shape, by provider name: host
+    # values here, their int32 arrays on the device in `extras` under "<name>.<array>"
+    layout: dict = field(default_factory=dict)
 
     def group(self, index: int) -> GroupView:
         return self.groups[index]
@@ -108,9 +105,6 @@ class StagingBuffer:
         if self.copied is None:
             self.copied = torch.cuda.Event()
         self.copied.record()
-
-
-SHORT_ROW = 4
 
 
 def _round_up(value: int, multiple: int) -> int:
@@ -151,21 +145,11 @@ def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], s
         total += _round_up(max(s, 1), 4)
     extras = dict(extras or {})
     single = T == B                    # a decode-only step: one token per request
-    short_tokens, long_rows, cursor = [], [], 0
-    if ops.FIXED_ORDER:
-        long_rows = range(B)           # every token's attention on the portion kernel
-    elif single:
-        short_tokens = range(B)
-    else:
-        for i, n in enumerate(q_lens):
-            if n <= SHORT_ROW:
-                short_tokens.extend(range(cursor, cursor + n))
-            else:
-                long_rows.append(i)
-            cursor += n
-    if short_tokens and long_rows:
-        extras["_short_tokens"] = np.asarray(short_tokens, dtype=np.int32)
-        extras["_long_rows"] = np.asarray(long_rows, dtype=np.int32)
+    layout = {}
+    for name, provider in step_layout_providers().items():
+        arrays, layout[name] = provider(q_lens)
+        for key, array in arrays.items():
+            extras[f"{name}.{key}"] = np.asarray(array, dtype=np.int32)
     extra_at = {}
     for name, array in extras.items():
         words = np.ascontiguousarray(array).view(np.int32)
@@ -215,6 +199,4 @@ def build_context(staging: StagingBuffer, cache, entries: Sequence[StepEntry], s
         dtype=dtype, device=staging.device, host_q_lens=q_lens, host_kv_lens=kv_lens,
         host_state_slots=state_slots, max_q_len=max(q_lens, default=0),
         max_kv_len=max(kv_bucket, max(kv_lens, default=0)), all_decode=all(n == 1 for n in q_lens), extras=extra_views,
-        short_tokens=extra_views.pop("_short_tokens", None), num_short_tokens=len(short_tokens),
-        long_rows=extra_views.pop("_long_rows", None), num_long_rows=len(long_rows),
-        max_long_q_len=max((q_lens[i] for i in long_rows), default=0))
+        layout=layout)

@@ -576,11 +576,39 @@ def attention_prefill(q, k_cache, v_cache, out, *, row_list, count, cu_q, kv_len
         _p(status), _stream()), "attention_prefill")
 
 
+SHORT_ROW = 4     # requests that bring at most this many tokens are served one query at a time
+
+
+def attention_step_layout(q_lens):
+    """How the attention kernels divide a step (registered with the step layout as "attention"):
+    the tokens of requests that bring at most SHORT_ROW tokens go to the split-key kernel one
+    query at a time, the requests that bring more to the portion kernel; with one order of
+    arithmetic asked for (set_fixed_order) everything goes to the portion kernel. Lists that
+    would name every token or every request are left out."""
+    B = len(q_lens)
+    short_tokens, long_rows, cursor = [], [], 0
+    if FIXED_ORDER:
+        long_rows = list(range(B))
+    elif sum(q_lens) == B:
+        short_tokens = list(range(B))
+    else:
+        for i, n in enumerate(q_lens):
+            if n <= SHORT_ROW:
+                short_tokens.extend(range(cursor, cursor + n))
+            else:
+                long_rows.append(i)
+            cursor += n
+    arrays = {"short_tokens": short_tokens, "long_rows": long_rows} if short_tokens and long_rows else {}
+    return arrays, {"num_short_tokens": len(short_tokens), "num_long_rows": len(long_rows),
+                    "max_long_q_len": max((q_lens[i] for i in long_rows), default=0)}
+
+
 def attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, *, nq: int, nkv: int,
               head_dim: int, scale: float, window: int) -> torch.Tensor:
     """Attention of every query row of the batch over its request's cached keys. float32
     runs on the CUDA cores; bfloat16 on the tensor cores, requests that bring a few tokens
-    one query at a time with split keys, longer portions tile by tile."""
+    one query at a time with split keys, longer portions tile by tile (the step's work lists:
+    attention_step_layout)."""
     if q.dtype != torch.bfloat16 or nq // nkv > 16:
         return attention_simt(q, k_cache, v_cache, positions=ctx.positions, request_of=ctx.request_of,
                               block_table=group.block_table, page_size=group.page_size, nq=nq, nkv=nkv,
@@ -589,10 +617,13 @@ def attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     out = torch.empty_like(q)
     common = dict(block_table=group.block_table, page_size=group.page_size, nq=nq, nkv=nkv, head_dim=head_dim,
                   scale=scale, window=window, status=ctx.status)
-    if ctx.num_short_tokens:
-        attention_decode(q, k_cache, v_cache, out, token_list=ctx.short_tokens, count=ctx.num_short_tokens,
-                         positions=ctx.positions, request_of=ctx.request_of, max_kv_len=ctx.max_kv_len, **common)
-    if ctx.num_long_rows:
-        attention_prefill(q, k_cache, v_cache, out, row_list=ctx.long_rows, count=ctx.num_long_rows, cu_q=ctx.cu_q,
-                          kv_len=ctx.kv_len, max_q_len=ctx.max_long_q_len, **common)
+    lists = ctx.layout["attention"]
+    if lists["num_short_tokens"]:
+        attention_decode(q, k_cache, v_cache, out, token_list=ctx.extras.get("attention.short_tokens"),
+                         count=lists["num_short_tokens"], positions=ctx.positions, request_of=ctx.request_of,
+                         max_kv_len=ctx.max_kv_len, **common)
+    if lists["num_long_rows"]:
+        attention_prefill(q, k_cache, v_cache, out, row_list=ctx.extras.get("attention.long_rows"),
+                          count=lists["num_long_rows"], cu_q=ctx.cu_q, kv_len=ctx.kv_len,
+                          max_q_len=lists["max_long_q_len"], **common)
     return out

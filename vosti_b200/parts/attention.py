@@ -20,7 +20,7 @@ import torch
 from .. import ops
 from ..config.schema import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
-from .base import Mixer, PagedCacheSpec, PositionEncoding, register_part
+from .base import Mixer, PagedCacheSpec, PositionEncoding, register_part, register_step_layout
 from .linear import linear, prepare_weight
 
 
@@ -101,7 +101,7 @@ class Attention(Mixer):
         if writes_cache:
             qkv = linear(ctx, x, self.w_qkv, allow_partial=True, bias=self.b_qkv)   # summed inside qkv_post
             if (ops.DECODE_FUSION and isinstance(qkv, ops.PartialSum) and qkv.dtype == torch.bfloat16
-                    and ctx.num_short_tokens == ctx.num_tokens == ctx.num_requests and ctx.short_tokens is None
+                    and ctx.layout["attention"]["num_short_tokens"] == ctx.num_tokens == ctx.num_requests
                     and self.nq // self.nkv <= 16 and cache.k.dtype == torch.bfloat16
                     and (cos is None or (rotary_dim == self.d and not interleaved))):
                 # every request brings one token: head norm, rotation, cache store and attention in
@@ -128,3 +128,5 @@ class Attention(Mixer):
 
 
 register_part("mixer", "attention", Attention, replace=True)
+# the attention kernels' work lists are made with every step's layout
+register_step_layout("attention", ops.attention_step_layout)

@@ -159,6 +159,22 @@ _REGISTRIES: Dict[str, Dict[str, Callable]] = {
 }
 
 
+# Step-layout providers: a kind of part that needs index arrays of its own for a step (the
+# attention kernels want the step's tokens sorted into work lists) registers a function,
+# q_lens -> (int32 arrays by name, host values by name). The step layout calls every provider for
+# every step; the arrays travel in the step's one host-to-device copy and appear in ctx.extras as
+# "<provider>.<array>", the host values in ctx.layout[provider]. The layout knows no provider by name.
+_STEP_LAYOUTS: Dict[str, Callable] = {}
+
+
+def register_step_layout(name: str, provider: Callable) -> None:
+    _STEP_LAYOUTS[name] = provider
+
+
+def step_layout_providers() -> Dict[str, Callable]:
+    return _STEP_LAYOUTS
+
+
 def register_part(role: str, kind: str, factory: Callable, *, replace: bool = False) -> None:
     """Register `factory` for parts of `role` ('norm', 'position', 'mixer', 'feed_forward',
     'arrangement', 'embedding', 'head') with the given kind."""
