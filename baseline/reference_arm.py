@@ -32,13 +32,16 @@ REF_ROOT = os.path.join(HERE, "_ref", "reference")
 PAGE = 64          # the reference's fixed page size (python/vosti_kernels/physical.py)
 
 
-def install(source: str = "/root/reference") -> str:
+def install(source: str = "") -> str:
     """Copy the parts of the reference checkout that run (python/, kernels/) under
-    baseline/_ref/reference, unmodified. Returns the root."""
+    baseline/_ref/reference, unmodified, from `source` or the folder VOSTI_REFERENCE_CHECKOUT
+    names. Returns the root; does nothing if the copy is there already."""
     if os.path.isdir(os.path.join(REF_ROOT, "python", "vosti_kernels")):
         return REF_ROOT
-    if not os.path.isdir(os.path.join(source, "python", "vosti_kernels")):
-        raise FileNotFoundError(f"no reference checkout at {source} and none installed under {REF_ROOT}")
+    source = source or os.environ.get("VOSTI_REFERENCE_CHECKOUT", "")
+    if not source or not os.path.isdir(os.path.join(source, "python", "vosti_kernels")):
+        raise FileNotFoundError(f"the reference is not installed under {REF_ROOT}; name its checkout in "
+                                f"VOSTI_REFERENCE_CHECKOUT and call baseline.reference_arm.install()")
     os.makedirs(REF_ROOT, exist_ok=True)
     for sub in ("python", "kernels"):
         shutil.copytree(os.path.join(source, sub), os.path.join(REF_ROOT, sub), dirs_exist_ok=True,
