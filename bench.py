@@ -167,7 +167,7 @@ def decode_run(engine, batch, steps, warmup, seed, sample_clocks=False, least_re
         if len(device_ms) == 1:
             repeats = repeats_for(steps, device_ms[0], least_repeats, max(1, DECODE_STEPS // steps))
     # the end-to-end regions stay inside the same key-length bucket of the decode graphs
-    room = 2560 - (context_start + repeats * steps) - 8
+    room = (CONTEXT // 512 + 1) * 512 - (context_start + repeats * steps) - 8
     wall_ms = []
     for _ in range(max(1, min(repeats, room // steps))):
         torch.cuda.synchronize()
@@ -348,6 +348,8 @@ def main() -> int:
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline; mixed: a continuous batch with Poisson arrivals and a shared prefix")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (both are reported)")
+    parser.add_argument("--context", type=int, default=2048,
+                        help="prompt length of the decode requests and of the prefill (the headline is 2048)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
@@ -364,6 +366,13 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    global CONTEXT
+    if args.context != CONTEXT:
+        if args.context < 64 or args.context % 64:
+            parser.error("--context must be a multiple of 64, at least 64")
+        CONTEXT = args.context
+        for _, config in SIZES.values():
+            config["max_position_embeddings"] = max(config["max_position_embeddings"], CONTEXT + 2048)
     if args.impl == "reference":
         return reference_main(args)
 
