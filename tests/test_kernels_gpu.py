@@ -836,3 +836,78 @@ def test_fused_decode_attention_gives_the_bits_of_its_two_kernels(dev, status, n
             p = torch.softmax((keys[:, g] @ qb[h]) * d ** -0.5, 0)
             ref[h] = p @ values[:, g]
         assert torch.allclose(got[b].float().cpu().view(nq, d), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window,segment", [(32, 8, 128, 16, 0, 576), (32, 8, 128, 16, 0, 192), (6, 3, 48, 16, 0, 128),
+                                                           (4, 2, 256, 64, 0, 256), (12, 4, 64, 32, 77, 128),
+                                                           (10, 2, 128, 48, 700, 384), (8, 8, 64, 16, 0, 1024)])
+def test_one_round_decode_attention_gives_the_bits_of_the_persistent_kernel(dev, status, nq, nkv, d, page, window, segment):
+    """With few tokens the decode attention runs as one CTA per (token, kv head, segment), the
+    segments of a token in a thread-block cluster that merges them through the first CTA's shared
+    memory; with many it walks over its items and merges through global memory. At the same segment
+    length both give the same bits, in the plain form and in the fused one, whatever the lengths
+    (one key, one segment, a window that hides the first segments); and the rule takes the
+    one-round kernel exactly where it says."""
+    from vosti_b200 import ops
+    lib = ops.library()
+    # few enough tokens for one round: clusters of more than 8 CTAs only serve up to 8 (token, kv head)
+    # pairs, and with head size 256 an SM holds one CTA, so that fewer clusters fit the GPU at once
+    lengths = [2047, 300, 1, 1500, 17, 1024, 33, 640, 2000, 129, 64, 65, 1999, 5, 1025, 511]
+    lens_k = lengths[: max(1, (8 if -(-2047 // segment) > 8 or d > 128 else 16) // nkv)]
+    lens_q = [1] * len(lens_k)
+    case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page)
+    scale = d ** -0.5
+    out = {}
+    ops.set_decode_segment(segment)
+    try:
+        for once in (True, False):
+            ops.set_decode_once(once)
+            out[once] = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, scale, window, "decode")
+            assert lib.vosti_attention_decode_last_kernel() == (2 if once else 1)
+        assert torch.equal(out[True], out[False])
+        want = reference_attention(case, scale, window)
+        assert torch.allclose(out[True].float().cpu(), want, atol=2e-2, rtol=2e-2)
+        # the fused form: the same partial sums through both kernels
+        B, heads, splits = len(lens_k), nq + 2 * nkv, 6
+        gen = torch.Generator(device=dev).manual_seed(d + nq)
+        partial = torch.randn(splits, B, heads * d, device=dev, generator=gen) * 0.6
+        qw = (1 + 0.1 * torch.randn(d, device=dev, generator=gen)).bfloat16()
+        kw = (1 + 0.1 * torch.randn(d, device=dev, generator=gen)).bfloat16()
+        cos, sin = (t.to(dev).contiguous() for t in plain.rope_tables(torch.arange(2100), d, 1e4))
+        table, positions = case["table"].to(dev), case["positions"].to(dev)
+        slots = torch.tensor([int(table[b, (n - 1) // page]) * page + (n - 1) % page for b, n in enumerate(lens_k)],
+                             dtype=torch.int32, device=dev)
+        fused, caches = {}, {}
+        for once in (True, False):
+            ops.set_decode_once(once)
+            k, v = dev_cache(case, "k_cache", dev, torch.bfloat16).clone(), dev_cache(case, "v_cache", dev, torch.bfloat16).clone()
+            k, v = torch.nan_to_num(k), torch.nan_to_num(v)
+            fused[once] = ops.attention_decode_fused(
+                ops.PartialSum(partial, splits, B, heads * d, torch.bfloat16, status), k, v, positions=positions,
+                request_of=case["request_of"].to(dev), block_table=table, slot_mapping=slots, page_size=page, nq=nq, nkv=nkv,
+                head_dim=d, max_kv_len=max(lens_k), scale=scale, window=window, q_norm_w=qw, k_norm_w=kw, eps=1e-6, cos=cos,
+                sin=sin, status=status)
+            caches[once] = (k, v)
+            assert lib.vosti_attention_decode_last_kernel() == (2 if once else 1)
+        assert torch.equal(fused[True], fused[False]) and torch.isfinite(fused[True]).all()
+        assert torch.equal(caches[True][0], caches[False][0]) and torch.equal(caches[True][1], caches[False][1])
+        assert status.item() == 0
+    finally:
+        ops.set_decode_once(True)
+        ops.set_decode_segment(0)
+
+
+def test_one_round_decode_attention_leaves_large_launches_and_odd_pages_to_the_persistent_kernel(dev, status):
+    """More (token, kv head) pairs than CTAs fit, pages of no multiple of 16 tokens, or a segment
+    longer than a warp's lanes can describe: the persistent kernel runs, and the results are right."""
+    from vosti_b200 import ops
+    lib = ops.library()
+    nq, nkv, d = 8, 2, 64
+    for page, lens_k in ((16, [200] * 200), (8, [300, 17, 64]), (16, [33000, 5, 70, 1, 900])):
+        lens_q = [1] * len(lens_k)
+        case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page)
+        out = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, d ** -0.5, 0, "decode")
+        assert lib.vosti_attention_decode_last_kernel() == 1, (page, len(lens_k))
+        want = reference_attention(case, d ** -0.5, 0)
+        assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    assert status.item() == 0

@@ -36,10 +36,26 @@ def test_decode_segment_length(lib):
             keys = lib.vosti_attention_decode_segment_keys(count, nq, nkv, d, longest)
             assert 128 <= keys <= 4096 and keys % 64 == 0
             segments = -(-longest // keys)
-            assert lib.vosti_attention_decode_scratch(count, nq, nkv, d, longest) == count * nq * segments * (d + 4)
+            assert lib.vosti_attention_decode_scratch(count, nq, nkv, d, longest) >= count * nq * segments * (d + 4)
     # many tokens: one segment per request as long as it fits; few tokens: cut finely
     assert lib.vosti_attention_decode_segment_keys(64, nq, nkv, d, 2560) == 2560
-    assert lib.vosti_attention_decode_segment_keys(1, nq, nkv, d, 2560) == 128
+    # few enough tokens for every (token, kv head) to have CTAs of its own in one round: as many
+    # segments as fit the GPU, at most 16 for up to 8 (token, kv head) pairs and 8 beyond, of equal
+    # length, a multiple of 64
+    assert lib.vosti_attention_decode_segment_keys(1, nq, nkv, d, 2560) == 192        # 8 pairs x 14 segments
+    assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 2560) == 640        # 64 pairs x 4
+    assert lib.vosti_attention_decode_segment_keys(4, nq, nkv, d, 2560) == 320        # 32 pairs x 8
+    assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 40000) > 4096 // 2  # too long for one round: the cost model
+    assert lib.vosti_set_decode_once(0) == 0
+    try:
+        # the persistent kernel's cost model alone
+        assert lib.vosti_attention_decode_segment_keys(1, nq, nkv, d, 2560) == 128
+        assert lib.vosti_attention_decode_segment_keys(64, nq, nkv, d, 2560) == 2560
+        for count in (1, 8, 64):
+            keys = lib.vosti_attention_decode_segment_keys(count, nq, nkv, d, 2560)
+            assert lib.vosti_attention_decode_scratch(count, nq, nkv, d, 2560) == count * nq * -(-2560 // keys) * (d + 4)
+    finally:
+        assert lib.vosti_set_decode_once(1) == 0
     # a pinned length overrides the cost model for every shape of launch, and taking the pin
     # away gives the launches their own choice back
     shapes = [(c, n) for c in (1, 8, 64) for n in (600, 2560, 9000)]

@@ -37,6 +37,8 @@
 // memory and their scores masked, so what unused cache slots hold never reaches the
 // arithmetic. Other page sizes read row by row, masked keys not at all.
 #include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "head_post.cuh"
@@ -81,18 +83,37 @@ __host__ __device__ inline int record_floats(int d) { return d + 4; }
 // runs this. `base` points at the head's records, `dst` at its output row. A lane owns the
 // columns 4 * lane .. 4 * lane + 3 (and 128 further on for head sizes above 128); the loads of
 // up to BATCH segments are in flight together.
+// GLOBAL: the records were written by other CTAs to global memory (read past L1); else they lie in
+// this CTA's shared memory.
+template <bool GLOBAL>
 __device__ __forceinline__ void merge_segments(const float* __restrict__ base, bf16* __restrict__ dst, int first,
                                                int last, int d) {
+  auto load2 = [](const float* p) { return GLOBAL ? __ldcg(reinterpret_cast<const float2*>(p)) : *reinterpret_cast<const float2*>(p); };
+  auto load4 = [](const float* p) { return GLOBAL ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p); };
   const int lane = threadIdx.x & 31;
   const int rec = record_floats(d);
   constexpr int BATCH = 8;
+  const bool second = 4 * lane + 128 < d;               // this lane also owns columns beyond 128
+  const bool owner = 4 * lane < d;
+  float4 v[BATCH][2];
+  // segments s0 + j0 .. s0 + j0 + BATCH - 1 (clamped to the n of this round) of the accumulator
+  auto load_batch = [&](int s0, int j0, int n) {
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) {
+      const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 4;
+      v[b][0] = owner ? load4(row + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[b][1] = second ? load4(row + 4 * lane + 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  // the first accumulators are requested together with the (max, sum) pairs: one trip to memory
+  // instead of two when there are few segments
+  load_batch(first, 0, min(32, last - first + 1));
   // pass 1: every segment's (max, sum), the first 32 segments' kept for the second pass
   float2 ml_first = make_float2(-INFINITY, 0.f);
   float m = -INFINITY;
   for (int s0 = first; s0 <= last; s0 += 32) {
     const int s = s0 + lane;
-    const float2 ml = s <= last ? __ldcg(reinterpret_cast<const float2*>(base + (int64_t)s * rec))   // other CTAs wrote these: read past L1
-                                : make_float2(-INFINITY, 0.f);
+    const float2 ml = s <= last ? load2(base + (int64_t)s * rec) : make_float2(-INFINITY, 0.f);
     if (s0 == first) ml_first = ml;
     m = fmaxf(m, ml.x);
   }
@@ -100,13 +121,11 @@ __device__ __forceinline__ void merge_segments(const float* __restrict__ base, b
   // pass 2: weights, sum and accumulator
   float l = 0.f;
   float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-  const bool second = 4 * lane + 128 < d;               // this lane also owns columns beyond 128
-  const bool owner = 4 * lane < d;
   for (int s0 = first; s0 <= last; s0 += 32) {
     const int mine = s0 + lane;
     float w_mine = 0.f, l_mine = 0.f;
     if (mine <= last) {
-      const float2 ml = s0 == first ? ml_first : __ldcg(reinterpret_cast<const float2*>(base + (int64_t)mine * rec));
+      const float2 ml = s0 == first ? ml_first : load2(base + (int64_t)mine * rec);
       if (ml.x != -INFINITY) {
         w_mine = fast_exp2(ml.x - m);
         l_mine = ml.y * w_mine;
@@ -114,13 +133,7 @@ __device__ __forceinline__ void merge_segments(const float* __restrict__ base, b
     }
     const int n = min(32, last - s0 + 1);
     for (int j0 = 0; j0 < n; j0 += BATCH) {
-      float4 v[BATCH][2];
-#pragma unroll
-      for (int b = 0; b < BATCH; ++b) {
-        const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 4;
-        v[b][0] = owner ? __ldcg(reinterpret_cast<const float4*>(row + 4 * lane)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        v[b][1] = second ? __ldcg(reinterpret_cast<const float4*>(row + 4 * lane + 128)) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      if (s0 != first || j0 != 0) load_batch(s0, j0, n);
 #pragma unroll
       for (int b = 0; b < BATCH; ++b) {
         const bool live = j0 + b < n;
@@ -141,6 +154,85 @@ __device__ __forceinline__ void merge_segments(const float* __restrict__ base, b
     *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(pack_bf16(acc[0].x * inv, acc[0].y * inv), pack_bf16(acc[0].z * inv, acc[0].w * inv));
   if (second)
     *reinterpret_cast<uint2*>(dst + 4 * lane + 128) = make_uint2(pack_bf16(acc[1].x * inv, acc[1].y * inv), pack_bf16(acc[1].z * inv, acc[1].w * inv));
+}
+
+// One tile of 16 keys for one warp: S = Q K^T on the tensor cores, the online softmax of the
+// warp's 16 rows (base 2, float32; masked keys count as -inf), O = O * alpha + P V with P rounded
+// to bfloat16. ks / vs: shared-memory addresses of the tile's K and V blocks (128-byte swizzle).
+template <int DMAX, bool Q_IN_REGISTERS>
+__device__ __forceinline__ void attend_tile(uint32_t ks, uint32_t vs, const uint32_t (&qa)[Q_IN_REGISTERS ? DMAX / 16 : 1][4],
+                                            const uint8_t* q_s, int q_pitch, int d, int key0, int kstart, int pos,
+                                            float scale_log2, bool upper_rows_live, uint32_t k_lane, uint32_t k_xor,
+                                            uint32_t v_lane, uint32_t v_xor, float (&m_row)[2], float (&l_row)[2],
+                                            float (&o)[DMAX / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  // ---- S = Q K^T for 16 keys: two 8-key column tiles
+  float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+  for (int kk = 0; kk < DMAX / 16; ++kk) {
+    if (kk * 16 < d) {
+      uint32_t a[4], b[4];
+      if (Q_IN_REGISTERS) {
+        a[0] = qa[Q_IN_REGISTERS ? kk : 0][0]; a[1] = qa[Q_IN_REGISTERS ? kk : 0][1];
+        a[2] = qa[Q_IN_REGISTERS ? kk : 0][2]; a[3] = qa[Q_IN_REGISTERS ? kk : 0][3];
+      } else {
+        ldmatrix_x4(a, smem_addr(q_s + (lane & 15) * q_pitch + (kk * 16 + (lane >> 4) * 8) * 2));
+      }
+      // B: matrices (keys 0-7, k lo), (keys 0-7, k hi), (keys 8-15, k lo), (keys 8-15, k hi)
+      ldmatrix_x4(b, ks + (kk >> 2) * BLOCK_BYTES + k_lane + ((uint32_t)((kk & 3) << 5) ^ k_xor));
+      mma_bf16(s[0], a, b[0], b[1]);
+      mma_bf16(s[1], a, b[2], b[3]);
+    }
+  }
+  // ---- online softmax (rows lane/4 and lane/4 + 8)
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+      const bool visible = key >= kstart && key <= pos;
+      s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+      tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
+    }
+  float alpha[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (r == 1 && !upper_rows_live) {              // padding rows: no exponentials (warp-uniform)
+      alpha[r] = 1.f;
+      s[0][2] = s[0][3] = s[1][2] = s[1][3] = 0.f;
+      continue;
+    }
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+    const float m_new = fmaxf(m_row[r], tile_max[r]);
+    const float safe = m_new == -INFINITY ? 0.f : m_new;
+    alpha[r] = fast_exp2(m_row[r] - safe);
+    m_row[r] = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      s[nt][2 * r] = fast_exp2(s[nt][2 * r] - safe);
+      s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - safe);
+      sum += s[nt][2 * r] + s[nt][2 * r + 1];
+    }
+    l_row[r] = l_row[r] * alpha[r] + sum;          // per-thread share; reduced over the quad at the end
+  }
+  uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                   pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+  // ---- O = O * alpha + P V
+#pragma unroll
+  for (int nt = 0; nt < DMAX / 16; ++nt) {
+    if (nt * 16 < d) {
+      o[2 * nt][0] *= alpha[0]; o[2 * nt][1] *= alpha[0]; o[2 * nt][2] *= alpha[1]; o[2 * nt][3] *= alpha[1];
+      o[2 * nt + 1][0] *= alpha[0]; o[2 * nt + 1][1] *= alpha[0]; o[2 * nt + 1][2] *= alpha[1]; o[2 * nt + 1][3] *= alpha[1];
+      uint32_t b[4];
+      // transposed: matrices (keys 0-7, cols lo), (keys 8-15, cols lo), (keys 0-7, cols hi), (keys 8-15, cols hi)
+      ldmatrix_x4_trans(b, vs + (nt >> 2) * BLOCK_BYTES + v_lane + ((uint32_t)((nt & 3) << 5) ^ v_xor));
+      mma_bf16(o[2 * nt], p, b[0], b[1]);
+      mma_bf16(o[2 * nt + 1], p, b[2], b[3]);
+    }
+  }
 }
 
 struct ItemMeta {
@@ -295,7 +387,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
           }
           __syncwarp();
         }
-        if (!waited) {
+        // The description rests on what the host wrote before the step. The query rows (and in the
+        // fused form the partial sums) come from the kernel before this one.
+        if (!FUSED && !waited) {
           pdl_wait();
           waited = true;
         }
@@ -326,6 +420,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             mb_arrive(smem_addr(&meta_bar[qb]));
           }
           if (slot >= 0) {
+            if (!waited) {
+              pdl_wait();
+              waited = true;
+            }
             int rope_pos = pos;
             if (fused.cos_table != nullptr && (pos < 0 || pos >= fused.max_positions)) rope_pos = 0;   // (the consumers report it)
             const float* token_partial = fused.partial + (int64_t)t * (nq + 2 * nkv) * d;
@@ -366,7 +464,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_half = lane >> 4;
   const uint32_t k_lane = k_row * 128, k_xor = (uint32_t)((k_half ^ (k_row & 7)) << 4);
   const uint32_t v_lane = v_row * 128, v_xor = (uint32_t)((v_half ^ (v_row & 7)) << 4);
-  pdl_wait();
+  // Unfused, the newest cache rows and the query rows come from the kernel before this one. Fused,
+  // that kernel is the projection: the cache rows a tile brings were written in earlier steps (the
+  // token's own row is replaced in shared memory), so tiles are requested at once and the warp waits
+  // only before it reads the partial sums.
+  bool waited = !FUSED;
+  if (!FUSED) pdl_wait();
   uint32_t seen = 0, n_issued = 0, q_seen = 0;       // tiles consumed and requested by this warp, items seen
   uint32_t fresh_seen[Q_BUFFERS] = {0, 0};           // items with a fresh key and value seen so far, per buffer
   int ahead = 0;                                     // tiles of the next item already requested
@@ -444,7 +547,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       __threadfence();
       for (int row = cw; row < group; row += CONSUMERS) {
         const int h = p_g * group + row;
-        merge_segments(partial + ((int64_t)p_item * nq + h) * max_segments * record_floats(d), out + ((int64_t)p_t * nq + h) * d,
+        merge_segments<true>(partial + ((int64_t)p_item * nq + h) * max_segments * record_floats(d), out + ((int64_t)p_t * nq + h) * d,
                        p_first, p_last, d);
       }
     }
@@ -479,6 +582,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       if (fused.cos_table != nullptr && (pos < 0 || pos >= fused.max_positions)) {
         if (ctid == 0) raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
         rope_pos = 0;
+      }
+      if (!waited) {
+        pdl_wait();
+        waited = true;
       }
       const float* token_partial = fused.partial + (int64_t)meta.t * (nq + 2 * nkv) * d;
       for (int row = cw; row < group; row += CONSUMERS)
@@ -538,73 +645,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         __syncwarp();
       }
 
-      // ---- S = Q K^T for 16 keys: two 8-key column tiles
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-      for (int kk = 0; kk < DMAX / 16; ++kk) {
-        if (kk * 16 < d) {
-          uint32_t a[4], b[4];
-          if (Q_IN_REGISTERS) {
-            a[0] = qa[Q_IN_REGISTERS ? kk : 0][0]; a[1] = qa[Q_IN_REGISTERS ? kk : 0][1];
-            a[2] = qa[Q_IN_REGISTERS ? kk : 0][2]; a[3] = qa[Q_IN_REGISTERS ? kk : 0][3];
-          } else {
-            ldmatrix_x4(a, smem_addr(q_s + (lane & 15) * q_pitch + (kk * 16 + (lane >> 4) * 8) * 2));
-          }
-          // B: matrices (keys 0-7, k lo), (keys 0-7, k hi), (keys 8-15, k lo), (keys 8-15, k hi)
-          ldmatrix_x4(b, ks + (kk >> 2) * BLOCK_BYTES + k_lane + ((uint32_t)((kk & 3) << 5) ^ k_xor));
-          mma_bf16(s[0], a, b[0], b[1]);
-          mma_bf16(s[1], a, b[2], b[3]);
-        }
-      }
-      // ---- online softmax (rows lane/4 and lane/4 + 8)
-      float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-          const bool visible = key >= kstart && key <= pos;
-          s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
-          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
-        }
-      float alpha[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        if (r == 1 && !upper_rows_live) {              // padding rows: no exponentials (warp-uniform)
-          alpha[r] = 1.f;
-          s[0][2] = s[0][3] = s[1][2] = s[1][3] = 0.f;
-          continue;
-        }
-        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-        const float m_new = fmaxf(m_row[r], tile_max[r]);
-        const float safe = m_new == -INFINITY ? 0.f : m_new;
-        alpha[r] = fast_exp2(m_row[r] - safe);
-        m_row[r] = m_new;
-        float sum = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          s[nt][2 * r] = fast_exp2(s[nt][2 * r] - safe);
-          s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - safe);
-          sum += s[nt][2 * r] + s[nt][2 * r + 1];
-        }
-        l_row[r] = l_row[r] * alpha[r] + sum;          // per-thread share; reduced over the quad at the end
-      }
-      uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
-                       pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
-      // ---- O = O * alpha + P V
-#pragma unroll
-      for (int nt = 0; nt < DMAX / 16; ++nt) {
-        if (nt * 16 < d) {
-          o[2 * nt][0] *= alpha[0]; o[2 * nt][1] *= alpha[0]; o[2 * nt][2] *= alpha[1]; o[2 * nt][3] *= alpha[1];
-          o[2 * nt + 1][0] *= alpha[0]; o[2 * nt + 1][1] *= alpha[0]; o[2 * nt + 1][2] *= alpha[1]; o[2 * nt + 1][3] *= alpha[1];
-          uint32_t b[4];
-          // transposed: matrices (keys 0-7, cols lo), (keys 8-15, cols lo), (keys 0-7, cols hi), (keys 8-15, cols hi)
-          ldmatrix_x4_trans(b, vs + (nt >> 2) * BLOCK_BYTES + v_lane + ((uint32_t)((nt & 3) << 5) ^ v_xor));
-          mma_bf16(o[2 * nt], p, b[0], b[1]);
-          mma_bf16(o[2 * nt + 1], p, b[2], b[3]);
-        }
-      }
+      attend_tile<DMAX, Q_IN_REGISTERS>(ks, vs, qa, q_s, q_pitch, d, key0, kstart, pos, scale_log2, upper_rows_live, k_lane, k_xor,
+                                        v_lane, v_xor, m_row, l_row, o);
       __syncwarp();                                  // every lane is done with this slot: refill it
       if (edge) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       if (requested < tiles) {
@@ -681,6 +723,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     p_item = meta.item; p_g = g; p_t = meta.t;
     p_first = kstart / segment_keys; p_last = pos / segment_keys;
   }
+  if (!waited) pdl_wait();                           // (a CTA without items: the chain of completed kernels stays unbroken)
   if (pending) {
     consumer_sync();                                 // every consumer has written its share of the last item
     count_in();
@@ -688,6 +731,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     merge_if_last();
   }
 }
+
+#include "attention_decode_once.cuh"
 
 // Bytes of dynamic shared memory: ring, Q buffers, merge area, and room to align the ring.
 size_t decode_smem_bytes(int d, int group) {
@@ -713,16 +758,108 @@ int ctas_per_sm(int d, int group) {
   return by_smem >= 2 ? 2 : 1;                                       // registers allow two
 }
 
-// Keys per segment for a launch: items are spread over the persistent CTAs in rounds; a round
-// costs the segment's length plus a fixed share for starting and finishing an item.
-int g_pinned_segment = 0;           // vosti_set_decode_segment: 0 lets every launch choose
+// Shared memory of the one-round kernel with `segments` CTAs per cluster.
+size_t once_smem_bytes(int d, int group, int segments) {
+  const size_t nb = (d + BOX_COLS - 1) / BOX_COLS;
+  return 1024 + (size_t)CONSUMERS * RING * 2 * nb * BLOCK_BYTES + (size_t)16 * ((size_t)d * 2 + 16) +
+         (size_t)CONSUMERS * group * (d + 2) * sizeof(float) + (size_t)2 * d * 2 + 16 +
+         (size_t)segments * group * record_floats(d) * sizeof(float);
+}
 
-int choose_segment_keys(int count, int nkv, int d, int group, int max_kv_len) {
+constexpr size_t ONCE_SMEM_CAP = 227 * 1024 - 2048;   // dynamic bytes a CTA may ask for: an SM's, less the static arrays
+
+int once_ctas_per_sm(int d, int group, int segments) {
+  if (once_smem_bytes(d, group, segments) > ONCE_SMEM_CAP) return 0;
+  const size_t per_sm = 228 * 1024;
+  const size_t per_cta = once_smem_bytes(d, group, segments) + 2048;   // static arrays and the reserved kilobyte
+  const int by_smem = (int)(per_sm / per_cta);
+  return by_smem >= 2 ? (d <= 128 ? 2 : 1) : by_smem;                  // registers allow two up to head size 128
+}
+
+// Keys per segment for a launch. g_pinned_segment / VOSTI_DECODE_SEGMENT fix the length; else:
+//  * if every (token, kv head) can have CTAs of its own in one round, the one-round kernel runs
+//    with as many segments per (token, kv head) as fit the GPU (at most 16, a cluster), each of
+//    the same length, a multiple of 64;
+//  * else items are spread over the persistent CTAs in rounds; a round costs the segment's length
+//    plus a fixed share for starting and finishing an item.
+int g_pinned_segment = 0;           // vosti_set_decode_segment: 0 lets every launch choose
+thread_local int g_last_kernel = 0; // which kernel this thread's last launch took: 1 persistent, 2 one-round
+int g_once_enabled = -1;            // vosti_set_decode_once; -1: from VOSTI_DECODE_ONCE (default on)
+
+bool once_enabled() {
+  if (g_once_enabled < 0) {
+    const char* env = getenv("VOSTI_DECODE_ONCE");
+    g_once_enabled = (env != nullptr && env[0] == '0') ? 0 : 1;
+  }
+  return g_once_enabled != 0;
+}
+
+int forced_segment_keys() {
   if (g_pinned_segment > 0) return g_pinned_segment;
   if (const char* forced = getenv("VOSTI_DECODE_SEGMENT")) {
     const int keys = atoi(forced);
     if (keys >= SEGMENT_STEP && keys <= MAX_SEGMENT && keys % SEGMENT_STEP == 0) return keys;
   }
+  return 0;
+}
+
+// The one-round kernel's segment count for this launch, 0 if it does not take it. page_size 0:
+// not known (the rule is asked for a launch shape only): pages of a multiple of 16 are assumed.
+int once_segments(int count, int nkv, int d, int group, int max_kv_len, int page_size, int* keys_out) {
+  if (!once_enabled() || (page_size > 0 && page_size % TILE != 0) || count <= 0) return 0;
+  const int64_t pairs = (int64_t)count * nkv;
+  const int forced = forced_segment_keys();
+  // Clusters of more than 8 CTAs leave much of a GPC unused (two of them fill it), so that only a
+  // few fit the GPU at once: they are for the smallest launches.
+  const int limit = pairs <= 8 ? ONCE_MAX_SEGMENTS : 8;
+  for (int segments = limit; segments >= 1; --segments) {
+    const int per_sm = once_ctas_per_sm(d, group, segments);
+    if (per_sm < 1 || pairs * segments > (int64_t)sm_count() * per_sm) continue;
+    int keys = forced > 0 ? forced : ((max_kv_len + segments - 1) / segments + SEGMENT_STEP - 1) / SEGMENT_STEP * SEGMENT_STEP;
+    if (keys < MIN_SEGMENT && forced == 0) keys = MIN_SEGMENT;
+    if (keys > MAX_SEGMENT) return 0;                          // a warp's tiles would not fit its lanes
+    const int needed = (max_kv_len + keys - 1) / keys;
+    if (needed > segments) return 0;                           // (a pinned length that needs more CTAs than fit)
+    *keys_out = keys;
+    return needed;
+  }
+  return 0;
+}
+
+// How many clusters of `cluster` CTAs with `smem` bytes each the GPU can run at once (0: none, or
+// the size cannot be scheduled); asked once per (kernel, size, bytes).
+template <typename Kernel>
+int once_clusters_that_fit(Kernel kernel, int cluster, size_t smem) {
+  static std::unordered_map<uint64_t, int> known;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  const uint64_t key = ((uint64_t)smem << 8) | (uint64_t)cluster;
+  auto it = known.find(key);
+  if (it != known.end()) return it->second;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)cluster);
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = (unsigned)cluster;
+  attribute[0].val.clusterDim.y = attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
+    (void)cudaGetLastError();
+    clusters = 0;
+  }
+  known.emplace(key, clusters);
+  return clusters;
+}
+
+int choose_segment_keys(int count, int nkv, int d, int group, int max_kv_len, int page_size = 0) {
+  int keys = 0;
+  if (once_segments(count, nkv, d, group, max_kv_len, page_size, &keys) > 0) return keys;
+  const int forced = forced_segment_keys();
+  if (forced > 0) return forced;
   const int64_t ctas = (int64_t)sm_count() * ctas_per_sm(d, group);
   const int64_t pairs = (int64_t)count * nkv;
   const int item_overhead = 224;       // measured: starting and finishing an item costs about as much as 220 keys
@@ -753,16 +890,31 @@ VOSTI_API int vosti_set_decode_segment(int keys) {
   return VOSTI_OK;
 }
 
+// The one-round kernel on (1, the default) or off (0) for every later launch of this process.
+VOSTI_API int vosti_set_decode_once(int enabled) {
+  g_once_enabled = enabled ? 1 : 0;
+  return VOSTI_OK;
+}
+
+// Which kernel this thread's last decode-attention launch took: 1 the persistent one, 2 the
+// one-round one, 0 none yet (for tests of the rule above).
+VOSTI_API int vosti_attention_decode_last_kernel() { return g_last_kernel; }
+
 // Keys per segment, and so (max_kv_len + keys - 1) / keys partial records per token and
 // head, of a launch with `count` tokens and keys up to `max_kv_len`.
 VOSTI_API int vosti_attention_decode_segment_keys(int count, int nq, int nkv, int d, int max_kv_len) {
   return choose_segment_keys(count, nkv, d, nq / nkv, max_kv_len);
 }
 
-// float32 scratch elements needed: count * nq * segments * (d + 4).
+// float32 scratch elements a launch of this shape may need: count * nq * segments * (d + 4) for the
+// persistent kernel's records (the one-round kernel needs none; with pages of no multiple of 16
+// tokens the persistent kernel runs where the segment rule above names the one-round kernel's
+// length, so the larger of the two is returned).
 VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int nkv, int d, int max_kv_len) {
   const int keys = vosti_attention_decode_segment_keys(count, nq, nkv, d, max_kv_len);
-  return (int64_t)count * nq * ((max_kv_len + keys - 1) / keys) * record_floats(d);
+  const int other = choose_segment_keys(count, nkv, d, nq / nkv, max_kv_len, 1);      // page size 1: never the one-round kernel
+  const int shorter = keys < other ? keys : other;
+  return (int64_t)count * nq * ((max_kv_len + shorter - 1) / shorter) * record_floats(d);
 }
 
 // caches: bf16 [pages, kv heads, page_size, d] (a head's tokens of a page are contiguous),
@@ -784,11 +936,6 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, void*
   VOSTI_REQUIRE(max_kv_len > 0, "attention_decode: max_kv_len %d must be positive", max_kv_len);
   if (count == 0) return VOSTI_OK;
   const int group = nq / nkv;
-  const int segment_keys = choose_segment_keys(count, nkv, d, group, max_kv_len);
-  const int segments = (max_kv_len + segment_keys - 1) / segment_keys;
-  VOSTI_REQUIRE(arrivals != nullptr, "attention_decode: the arrival counters are missing");
-  VOSTI_REQUIRE(scratch != nullptr && scratch_elems >= (int64_t)count * nq * segments * record_floats(d),
-                "attention_decode: scratch too small");
   const int64_t cache_rows = (int64_t)num_pages * nkv * page_size;
   VOSTI_REQUIRE(cache_rows < (int64_t)1 << 31, "attention_decode: cache of %lld rows is too large", (long long)cache_rows);
   VOSTI_REQUIRE((reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0,
@@ -800,14 +947,66 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, void*
   VOSTI_REQUIRE(cached_tensor_map(k_cache, cache_rows, d, box_rows, &map_k) &&
                     cached_tensor_map(v_cache, cache_rows, d, box_rows, &map_v),
                 "attention_decode: cuTensorMapEncodeTiled failed");
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
+  {
+    // ---- one round: a cluster of CTAs per (token, kv head)
+    int once_keys = 0;
+    const int once = once_segments(count, nkv, d, group, max_kv_len, page_size, &once_keys);
+    if (once > 0) {
+      const size_t smem = once_smem_bytes(d, group, once);
+      const dim3 grid((unsigned)((int64_t)count * nkv * once));
+      bool launched = false;
+#define LAUNCH_ONCE_AS(DMAX, EXACT, FUSED)                                                                          \
+  do {                                                                                                              \
+    auto kernel = attention_decode_once_kernel<DMAX, EXACT, FUSED>;                                                 \
+    static bool configured = false;                                                                                 \
+    if (!configured) {                                                                                              \
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ONCE_SMEM_CAP);               \
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);                              \
+      configured = true;                                                                                            \
+    }                                                                                                               \
+    const int fit = once_clusters_that_fit(kernel, once, smem);                                                     \
+    if ((int64_t)fit * once >= (int64_t)grid.x && smem <= ONCE_SMEM_CAP) {                                         \
+      vosti_launch_clusters(kernel, grid, dim3(THREADS), (unsigned)once, smem, stream, map_k, map_v, (const bf16*)q, \
+                            (bf16*)out, token_list, positions, request_of, block_table, max_pages, page_size,       \
+                            page_shift, num_pages, whole_rows, nq, nkv, d, once_keys, scale * LOG2E, window, status, \
+                            fused);                                                                                 \
+      launched = true;                                                                                              \
+    }                                                                                                               \
+  } while (0)
+#define LAUNCH_ONCE(DMAX, EXACT)                                                                                    \
+  do {                                                                                                              \
+    if (fused.partial != nullptr) LAUNCH_ONCE_AS(DMAX, EXACT, true);                                                \
+    else LAUNCH_ONCE_AS(DMAX, EXACT, false);                                                                        \
+  } while (0)
+      if (d == 64) LAUNCH_ONCE(64, true);
+      else if (d == 128) LAUNCH_ONCE(128, true);
+      else if (d == 256) LAUNCH_ONCE(256, true);
+      else if (d < 64) LAUNCH_ONCE(64, false);
+      else if (d < 128) LAUNCH_ONCE(128, false);
+      else LAUNCH_ONCE(256, false);
+#undef LAUNCH_ONCE
+#undef LAUNCH_ONCE_AS
+      if (launched) {
+        g_last_kernel = 2;
+        VOSTI_LAUNCH_CHECK();
+      }
+    }
+  }
+  g_last_kernel = 1;
+  // ---- the persistent kernel (page size 1 in the rule: never the one-round kernel's length)
+  const int segment_keys = choose_segment_keys(count, nkv, d, group, max_kv_len, 1);
+  const int segments = (max_kv_len + segment_keys - 1) / segment_keys;
+  VOSTI_REQUIRE(arrivals != nullptr, "attention_decode: the arrival counters are missing");
+  VOSTI_REQUIRE(scratch != nullptr && scratch_elems >= (int64_t)count * nq * segments * record_floats(d),
+                "attention_decode: scratch too small");
   const size_t smem = decode_smem_bytes(d, group);
   const int64_t items = (int64_t)count * nkv * segments;
   VOSTI_REQUIRE(items < ((int64_t)1 << 30), "attention_decode: %lld work items are too many for one launch", (long long)items);
   const int64_t ctas = (int64_t)sm_count() * ctas_per_sm(d, group);
   dim3 grid((unsigned)(items < ctas ? items : ctas));
-  int page_shift = -1;
-  if ((page_size & (page_size - 1)) == 0)
-    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
 #define LAUNCH_DECODE_AS(DMAX, EXACT, FUSED)                                                                        \
   do {                                                                                                              \
     static bool configured = false;                                                                                 \
@@ -854,7 +1053,7 @@ VOSTI_API int vosti_attention_decode(const void* q, const void* k_cache, const v
 // the kernel sums them, applies head norm and rotation, stores the new keys and values in the
 // caches at slot_mapping and attends. q_norm_w / k_norm_w null: no head norm; cos / sin null: no
 // rotation (float32 tables [max_positions][d / 2]). Head sizes up to 512 in steps of 16 as the
-// unfused kernel; d must be even.
+// unfused kernel; d must be even. block_table has at least `count` rows (one per request).
 VOSTI_API int vosti_attention_decode_fused(const float* partial, int splits, void* k_cache, void* v_cache, void* out,
                                            float* scratch, int64_t scratch_elems, int* arrivals, int count,
                                            const int* positions, const int* request_of, const int* block_table,
@@ -885,3 +1084,4 @@ VOSTI_API int vosti_attention_decode_fused(const float* partial, int splits, voi
                        request_of, block_table, max_pages, page_size, num_pages, nq, nkv, d, max_kv_len, scale, window,
                        status, stream, fused);
 }
+

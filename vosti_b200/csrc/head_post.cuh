@@ -9,6 +9,19 @@
 
 constexpr int HEAD_MAX_PAIRS = 8;      // pairs (i, i + d/2) a lane holds: head_dim <= 512
 
+// Loads that are issued where they stand: the compiler neither moves them down to their first use
+// nor puts a use between them.
+__device__ __forceinline__ uint32_t issue_load_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.b32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t issue_load_u16(const unsigned short* p) {
+  unsigned short v;
+  asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return (uint32_t)v;
+}
+
 // One warp, one head: lane l holds the pairs i = l + 32 j, j < PAIRS (the caller chooses PAIRS so
 // that 64 PAIRS >= d; fewer pairs, fewer registers, the same arithmetic per element). `src` points
 // at the head's first element in split 0; split s lies s * plane further on. The result goes to
@@ -22,8 +35,35 @@ __device__ __forceinline__ void head_from_partial(const float* __restrict__ src,
   float x1[PAIRS], x2[PAIRS];
 #pragma unroll
   for (int j = 0; j < PAIRS; ++j) x1[j] = x2[j] = 0.f;
-  // the loads of up to four splits are issued together; the sums still run in split order
-  constexpr int FLIGHT = 4;
+  // Norm weights and rotation factors do not depend on the sums. They are requested first and
+  // looked at last (a weight stays raw bits until then), with loads that are issued where they stand,
+  // so that they and the partial sums make one trip to memory together instead of several in a row.
+  uint32_t w1[PAIRS], w2[PAIRS];
+  float cs[PAIRS], sn[PAIRS];
+#pragma unroll
+  for (int j = 0; j < PAIRS; ++j) {
+    const int i = lane + 32 * j;
+    const bool live = i < half;
+    w1[j] = w2[j] = 0u;
+    cs[j] = 1.f;
+    sn[j] = 0.f;
+    if (live && norm_w != nullptr) {
+      if (norm_w_is_f32) {
+        w1[j] = issue_load_u32(reinterpret_cast<const uint32_t*>(norm_w) + i);
+        w2[j] = issue_load_u32(reinterpret_cast<const uint32_t*>(norm_w) + i + half);
+      } else {
+        w1[j] = issue_load_u16(reinterpret_cast<const unsigned short*>(norm_w) + i);
+        w2[j] = issue_load_u16(reinterpret_cast<const unsigned short*>(norm_w) + i + half);
+      }
+    }
+    if (live && cos_table != nullptr) {
+      cs[j] = __uint_as_float(issue_load_u32(reinterpret_cast<const uint32_t*>(cos_table + (long long)pos * half + i)));
+      sn[j] = __uint_as_float(issue_load_u32(reinterpret_cast<const uint32_t*>(sin_table + (long long)pos * half + i)));
+    }
+  }
+  // the loads of up to four splits (eight where a lane holds few pairs) are issued together; the
+  // sums still run in split order
+  constexpr int FLIGHT = PAIRS <= 2 ? 8 : 4;
   for (int s0 = 0; s0 < splits; s0 += FLIGHT) {
     float v1[FLIGHT][PAIRS], v2[FLIGHT][PAIRS];
 #pragma unroll
@@ -32,8 +72,8 @@ __device__ __forceinline__ void head_from_partial(const float* __restrict__ src,
       for (int j = 0; j < PAIRS; ++j) {
         const int i = lane + 32 * j;
         const bool live = s0 + f < splits && i < half;
-        v1[f][j] = live ? src[(s0 + f) * plane + i] : 0.f;
-        v2[f][j] = live ? src[(s0 + f) * plane + i + half] : 0.f;
+        v1[f][j] = live ? __uint_as_float(issue_load_u32(reinterpret_cast<const uint32_t*>(src + (s0 + f) * plane + i))) : 0.f;
+        v2[f][j] = live ? __uint_as_float(issue_load_u32(reinterpret_cast<const uint32_t*>(src + (s0 + f) * plane + i + half))) : 0.f;
       }
 #pragma unroll
     for (int f = 0; f < FLIGHT; ++f)
@@ -58,12 +98,13 @@ __device__ __forceinline__ void head_from_partial(const float* __restrict__ src,
     if (i >= half) continue;
     float a = x1[j], b = x2[j];
     if (norm_w != nullptr) {
-      a = __fmul_rn(__fmul_rn(a, rrms), load_flex(norm_w, norm_w_is_f32, i));
-      b = __fmul_rn(__fmul_rn(b, rrms), load_flex(norm_w, norm_w_is_f32, i + half));
+      // (a bfloat16 weight is the upper half of its float32 value)
+      a = __fmul_rn(__fmul_rn(a, rrms), __uint_as_float(norm_w_is_f32 ? w1[j] : w1[j] << 16));
+      b = __fmul_rn(__fmul_rn(b, rrms), __uint_as_float(norm_w_is_f32 ? w2[j] : w2[j] << 16));
     }
     if (cos_table != nullptr) {
-      const float c = cos_table[(long long)pos * half + i], sn = sin_table[(long long)pos * half + i];
-      const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)), rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn));
+      const float c = cs[j], sn_j = sn[j];
+      const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn_j)), rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn_j));
       a = ra;
       b = rb;
     }

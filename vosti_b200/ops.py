@@ -467,6 +467,12 @@ def set_fixed_order(enabled: bool) -> None:
 BATCH_INVARIANT_SEGMENT = 576    # keys per decode-attention segment when the length is pinned
 
 
+def set_decode_once(enabled: bool) -> None:
+    """The decode attention's one-round kernel (a cluster of CTAs per token and kv head) on or off
+    for every later launch of this process; off, every launch takes the persistent kernel."""
+    _check(library().vosti_set_decode_once(1 if enabled else 0), "set_decode_once", kernels=0)
+
+
 def set_decode_segment(keys: int) -> None:
     """Pin the decode attention's segment length for this process (0: every launch chooses by
     its shape). Pinned, a token's attention does not depend on the size of its batch or on its
@@ -531,6 +537,8 @@ def attention_decode_fused(qkv: "PartialSum", k_cache, v_cache, *, positions, re
     if qkv.width != (nq + 2 * nkv) * head_dim or qkv.dtype != torch.bfloat16:
         raise KernelError("attention_decode_fused: the projection does not match the head counts or is not bfloat16")
     _contig(k_cache, v_cache, positions, request_of, block_table, slot_mapping, q_norm_w, k_norm_w, cos, sin)
+    if block_table.dim() != 2 or block_table.shape[0] < count:
+        raise KernelError("attention_decode_fused: the block table needs a row per request (one token each)")
     norm_flag = 0
     if q_norm_w is not None:
         norm_flag = _is_f32(q_norm_w)
