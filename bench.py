@@ -350,6 +350,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (both are reported)")
     parser.add_argument("--context", type=int, default=2048,
                         help="prompt length of the decode requests and of the prefill (the headline is 2048)")
+    parser.add_argument("--page", type=int, default=16, help="tokens per cache page")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
@@ -366,7 +367,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    global CONTEXT
+    global CONTEXT, PAGE
+    PAGE = args.page
     if args.context != CONTEXT:
         if args.context < 64 or args.context % 64:
             parser.error("--context must be a multiple of 64, at least 64")

@@ -897,17 +897,18 @@ def test_one_round_decode_attention_gives_the_bits_of_the_persistent_kernel(dev,
         ops.set_decode_segment(0)
 
 
-def test_one_round_decode_attention_leaves_large_launches_and_odd_pages_to_the_persistent_kernel(dev, status):
-    """More (token, kv head) pairs than CTAs fit, pages of no multiple of 16 tokens, or a segment
-    longer than a warp's lanes can describe: the persistent kernel runs, and the results are right."""
+def test_decode_attention_kernels_by_launch_shape(dev, status):
+    """Pages of no multiple of 16 tokens, or a context too long for 8 segments of 4096 keys: the
+    persistent kernel runs. More (token, kv head) pairs than CTAs fit the GPU at once: the kernel
+    with one CTA per item still runs, in waves. The results are right either way."""
     from vosti_b200 import ops
     lib = ops.library()
     nq, nkv, d = 8, 2, 64
-    for page, lens_k in ((16, [200] * 200), (8, [300, 17, 64]), (16, [33000, 5, 70, 1, 900])):
+    for page, lens_k, kernel in ((16, [200] * 400, 2), (8, [300, 17, 64], 1), (16, [33000, 5, 70, 1, 900], 1)):
         lens_q = [1] * len(lens_k)
         case = paged_case(dev, torch.bfloat16, lens_q, lens_k, nq, nkv, d, page)
         out = _run_tc_attention(dev, status, case, lens_q, lens_k, nq, nkv, d, page, d ** -0.5, 0, "decode")
-        assert lib.vosti_attention_decode_last_kernel() == 1, (page, len(lens_k))
+        assert lib.vosti_attention_decode_last_kernel() == kernel, (page, len(lens_k))
         want = reference_attention(case, d ** -0.5, 0)
         assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
     assert status.item() == 0

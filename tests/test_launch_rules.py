@@ -39,13 +39,19 @@ def test_decode_segment_length(lib):
             assert lib.vosti_attention_decode_scratch(count, nq, nkv, d, longest) >= count * nq * segments * (d + 4)
     # many tokens: one segment per request as long as it fits; few tokens: cut finely
     assert lib.vosti_attention_decode_segment_keys(64, nq, nkv, d, 2560) == 2560
-    # few enough tokens for every (token, kv head) to have CTAs of its own in one round: as many
-    # segments as fit the GPU, at most 16 for up to 8 (token, kv head) pairs and 8 beyond, of equal
-    # length, a multiple of 64
+    # one CTA per (token, kv head, segment): the segment count that makes waves x (keys + 350) smallest.
+    # While all CTAs fit the GPU at once (296 of them at these sizes) that is as many segments as fit,
+    # at most 16 for up to 8 (token, kv head) pairs and 8 beyond, of equal length, a multiple of 64
     assert lib.vosti_attention_decode_segment_keys(1, nq, nkv, d, 2560) == 192        # 8 pairs x 14 segments
     assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 2560) == 640        # 64 pairs x 4
     assert lib.vosti_attention_decode_segment_keys(4, nq, nkv, d, 2560) == 320        # 32 pairs x 8
-    assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 40000) > 4096 // 2  # too long for one round: the cost model
+    assert lib.vosti_attention_decode_segment_keys(16, nq, nkv, d, 2560) == 1280      # 128 pairs x 2
+    # in waves: 384 pairs are 2 waves of 2560 keys or 3 of 1280; 512 pairs are 2 waves of 2560 or 4 of 1280
+    assert lib.vosti_attention_decode_segment_keys(48, nq, nkv, d, 2560) == 1280
+    assert lib.vosti_attention_decode_segment_keys(64, nq, nkv, d, 2560) == 2560
+    assert lib.vosti_attention_decode_segment_keys(256, nq, nkv, d, 2560) == 2560
+    # too long for 8 segments of 4096 keys: the persistent kernel's cost model
+    assert lib.vosti_attention_decode_segment_keys(8, nq, nkv, d, 40000) > 4096 // 2
     assert lib.vosti_set_decode_once(0) == 0
     try:
         # the persistent kernel's cost model alone

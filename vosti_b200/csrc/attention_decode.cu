@@ -777,11 +777,12 @@ int once_ctas_per_sm(int d, int group, int segments) {
 }
 
 // Keys per segment for a launch. g_pinned_segment / VOSTI_DECODE_SEGMENT fix the length; else:
-//  * if every (token, kv head) can have CTAs of its own in one round, the one-round kernel runs
-//    with as many segments per (token, kv head) as fit the GPU (at most 16, a cluster), each of
-//    the same length, a multiple of 64;
-//  * else items are spread over the persistent CTAs in rounds; a round costs the segment's length
-//    plus a fixed share for starting and finishing an item.
+//  * with pages of a multiple of 16 tokens the kernel with one CTA per item runs, with 1 to 16
+//    segments per (token, kv head) (a cluster), each of the same length, a multiple of 64 up to
+//    4096 keys: the count that makes waves of CTAs x (keys + a CTA's fixed cost) smallest;
+//  * else (other page sizes, contexts too long for 8 segments of 4096 keys) items are spread over
+//    the persistent CTAs in rounds; a round costs the segment's length plus a fixed share for
+//    starting and finishing an item.
 int g_pinned_segment = 0;           // vosti_set_decode_segment: 0 lets every launch choose
 thread_local int g_last_kernel = 0; // which kernel this thread's last launch took: 1 persistent, 2 one-round
 int g_once_enabled = -1;            // vosti_set_decode_once; -1: from VOSTI_DECODE_ONCE (default on)
@@ -803,8 +804,9 @@ int forced_segment_keys() {
   return 0;
 }
 
-// The one-round kernel's segment count for this launch, 0 if it does not take it. page_size 0:
-// not known (the rule is asked for a launch shape only): pages of a multiple of 16 are assumed.
+// The segments per (token, kv head) with which the one-CTA-per-item kernel takes this launch, 0 if
+// it does not. page_size 0: not known (the rule is asked for a launch shape only): pages of a
+// multiple of 16 are assumed.
 int once_segments(int count, int nkv, int d, int group, int max_kv_len, int page_size, int* keys_out) {
   if (!once_enabled() || (page_size > 0 && page_size % TILE != 0) || count <= 0) return 0;
   const int64_t pairs = (int64_t)count * nkv;
@@ -812,18 +814,35 @@ int once_segments(int count, int nkv, int d, int group, int max_kv_len, int page
   // Clusters of more than 8 CTAs leave much of a GPC unused (two of them fill it), so that only a
   // few fit the GPU at once: they are for the smallest launches.
   const int limit = pairs <= 8 ? ONCE_MAX_SEGMENTS : 8;
+  // While all CTAs fit the GPU at once: as many segments as fit. Beyond that the CTAs run in waves,
+  // and a launch costs about its waves times a CTA's time: its keys plus what starting and finishing
+  // a CTA costs, about as much as 450 keys (fitted to batches of 20 to 256 requests of 2,048 keys:
+  // one segment for most, two where one would leave the second wave nearly empty).
+  const int cta_overhead = 450;
+  int best = 0;
+  int64_t best_cost = -1;
   for (int segments = limit; segments >= 1; --segments) {
-    const int per_sm = once_ctas_per_sm(d, group, segments);
-    if (per_sm < 1 || pairs * segments > (int64_t)sm_count() * per_sm) continue;
     int keys = forced > 0 ? forced : ((max_kv_len + segments - 1) / segments + SEGMENT_STEP - 1) / SEGMENT_STEP * SEGMENT_STEP;
     if (keys < MIN_SEGMENT && forced == 0) keys = MIN_SEGMENT;
-    if (keys > MAX_SEGMENT) return 0;                          // a warp's tiles would not fit its lanes
+    if (keys > MAX_SEGMENT) break;                             // a warp's tiles would not fit its lanes; fewer segments are longer still
     const int needed = (max_kv_len + keys - 1) / keys;
-    if (needed > segments) return 0;                           // (a pinned length that needs more CTAs than fit)
-    *keys_out = keys;
-    return needed;
+    if (needed > segments) break;                              // (a pinned length that needs more CTAs than a cluster has)
+    const int per_sm = once_ctas_per_sm(d, group, needed);
+    if (per_sm < 1) continue;
+    const int64_t capacity = (int64_t)sm_count() * per_sm;
+    if (pairs * needed <= capacity || forced > 0) {            // one wave (or a pinned length: the same plan for every launch)
+      *keys_out = keys;
+      return needed;
+    }
+    const int64_t waves = (pairs * needed + capacity - 1) / capacity;
+    const int64_t cost = waves * (keys + cta_overhead);
+    if (best_cost < 0 || cost <= best_cost) {                  // ties: fewer segments
+      best = needed;
+      best_cost = cost;
+      *keys_out = keys;
+    }
   }
-  return 0;
+  return best;
 }
 
 // How many clusters of `cluster` CTAs with `smem` bytes each the GPU can run at once (0: none, or
@@ -968,7 +987,13 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, void*
       configured = true;                                                                                            \
     }                                                                                                               \
     const int fit = once_clusters_that_fit(kernel, once, smem);                                                     \
-    if ((int64_t)fit * once >= (int64_t)grid.x && smem <= ONCE_SMEM_CAP) {                                         \
+    if (once == 1 && smem <= ONCE_SMEM_CAP) {                                                                       \
+      /* no cluster to form: an ordinary launch, whose CTAs are spread over all SMs first */                        \
+      vosti_launch(kernel, grid, dim3(THREADS), smem, stream, map_k, map_v, (const bf16*)q, (bf16*)out, token_list,  \
+                   positions, request_of, block_table, max_pages, page_size, page_shift, num_pages, whole_rows, nq,  \
+                   nkv, d, once_keys, scale * LOG2E, window, status, fused);                                         \
+      launched = true;                                                                                              \
+    } else if (fit >= 1 && smem <= ONCE_SMEM_CAP) {                                                                 \
       vosti_launch_clusters(kernel, grid, dim3(THREADS), (unsigned)once, smem, stream, map_k, map_v, (const bf16*)q, \
                             (bf16*)out, token_list, positions, request_of, block_table, max_pages, page_size,       \
                             page_shift, num_pages, whole_rows, nq, nkv, d, once_keys, scale * LOG2E, window, status, \

@@ -1,6 +1,6 @@
-// The decode attention for launches whose work fits the GPU in one round: one CTA per
-// (token, kv head, segment), the segments of a (token, kv head) forming a thread-block cluster.
-// Included by attention_decode.cu (it uses that file's tile arithmetic, merge and constants).
+// The decode attention with one CTA per (token, kv head, segment), the segments of a (token, kv
+// head) forming a thread-block cluster. Included by attention_decode.cu (it uses that file's tile
+// arithmetic, merge and constants).
 //
 // With few tokens the persistent kernel's time is mostly its ends: the producer describing the
 // item to the consumers, and at the far end three trips through global memory (the partial
@@ -11,9 +11,13 @@
 // cluster's first CTA (st.shared::cluster), which waits on an mbarrier the others arrive on and
 // merges the segments in segment order with the arithmetic of merge_segments. Same formulas,
 // same order of every sum as the persistent kernel at the same segment length: the same bits.
+// With many tokens the CTAs run in waves (two to an SM, a new one starting where one ends), which
+// measured faster than the persistent kernel's walk over its items at every batch size tried (48
+// to 256 requests of 2,048 keys).
 //
-// Needs pages of a multiple of 16 tokens. The fused form (query rows and the token's own key and
-// value from the projection's partial sums) is as in the persistent kernel.
+// Needs pages of a multiple of 16 tokens and segments of at most 4096 keys. The fused form (query
+// rows and the token's own key and value from the projection's partial sums) is as in the
+// persistent kernel.
 #pragma once
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
