@@ -812,8 +812,10 @@ int once_segments(int count, int nkv, int d, int group, int max_kv_len, int page
   const int64_t pairs = (int64_t)count * nkv;
   const int forced = forced_segment_keys();
   // Clusters of more than 8 CTAs leave much of a GPC unused (two of them fill it), so that only a
-  // few fit the GPU at once: they are for the smallest launches.
-  const int limit = pairs <= 8 ? ONCE_MAX_SEGMENTS : 8;
+  // few fit the GPU at once: they are for the smallest launches, and only where an SM holds two of
+  // their CTAs (with one, a cluster of 14 needs 14 SMs of one GPC: measured no faster than the
+  // persistent kernel, where 8 segments were 4 to 7 % faster).
+  const int limit = pairs <= 8 && once_ctas_per_sm(d, group, ONCE_MAX_SEGMENTS) >= 2 ? ONCE_MAX_SEGMENTS : 8;
   // While all CTAs fit the GPU at once: as many segments as fit. Beyond that the CTAs run in waves,
   // and a launch costs about its waves times a CTA's time: its keys plus what starting and finishing
   // a CTA costs, about as much as 450 keys (fitted to batches of 20 to 256 requests of 2,048 keys:
