@@ -36,225 +36,14 @@
 // beyond the token's position (or before its window) are overwritten with zeros in shared
 // memory and their scores masked, so what unused cache slots hold never reaches the
 // arithmetic. Other page sizes read row by row, masked keys not at all.
-#include <cstdlib>
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
-#include "head_post.cuh"
-#include "mma_util.cuh"
-#include "tensor_map.cuh"
+#include "attention_decode_common.cuh"
 
 namespace {
 
-constexpr int CONSUMERS = 4;                          // consumer warps; one producer warp beside them
-constexpr int THREADS = (CONSUMERS + 1) * 32;
-constexpr int TILE = 16;                              // keys per MMA step and per TMA box
-constexpr int RING = 2;                               // K/V tile buffers per consumer warp
-constexpr int Q_BUFFERS = 2;
-constexpr int SEGMENT_STEP = CONSUMERS * TILE;        // 64: segment lengths are multiples of this
-constexpr int MIN_SEGMENT = SEGMENT_STEP * RING;      // 128: both buffers of every warp in use
-constexpr int MAX_SEGMENT = 4096;
-constexpr int MAX_SEGMENT_PAGES = MAX_SEGMENT / TILE; // page ids the producer stages per item
-constexpr int BOX_COLS = 64;                          // 128 bytes: the swizzle width
-constexpr int BLOCK_BYTES = TILE * 128;               // one column block of a tile
-constexpr float LOG2E = 1.4426950408889634f;
-
-__device__ __forceinline__ void mb_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// A wait that ran out marks the CTA as abandoned: later waits return at once, so that a fault
-// costs one timeout and not one per tile, while every warp still walks through the same
-// barriers (the results are garbage then and the status word says so).
-__device__ __forceinline__ void wait_or_abandon(uint32_t bar, uint32_t parity, unsigned* status, volatile int* abandoned) {
-  if (*abandoned) return;
-  if (!mb_wait(bar, parity, status)) *abandoned = 1;
-}
-// A barrier among the consumer warps only (the producer never joins it).
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
-
-// Partial record of one (token, query head, segment) in global memory: [0] max (base-2
-// scores), [1] sum, [2..3] unused, [4 .. 4+d) accumulator, so that the accumulator is read as
-// 16-byte words. (In shared memory a record is [max, sum, accumulator]: d + 2 floats.)
-__host__ __device__ inline int record_floats(int d) { return d + 4; }
-
-// One warp combines the segments first..last of one (token, query head): lane s holds
-// segment s's max and weight; the sums run over segments in segment order, whichever CTA
-// runs this. `base` points at the head's records, `dst` at its output row. A lane owns the
-// columns 4 * lane .. 4 * lane + 3 (and 128 further on for head sizes above 128); the loads of
-// up to BATCH segments are in flight together.
-// GLOBAL: the records were written by other CTAs to global memory (read past L1); else they lie in
-// this CTA's shared memory.
-template <bool GLOBAL>
-__device__ __forceinline__ void merge_segments(const float* __restrict__ base, bf16* __restrict__ dst, int first,
-                                               int last, int d) {
-  auto load2 = [](const float* p) { return GLOBAL ? __ldcg(reinterpret_cast<const float2*>(p)) : *reinterpret_cast<const float2*>(p); };
-  auto load4 = [](const float* p) { return GLOBAL ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p); };
-  const int lane = threadIdx.x & 31;
-  const int rec = record_floats(d);
-  constexpr int BATCH = 8;
-  const bool second = 4 * lane + 128 < d;               // this lane also owns columns beyond 128
-  const bool owner = 4 * lane < d;
-  float4 v[BATCH][2];
-  // segments s0 + j0 .. s0 + j0 + BATCH - 1 (clamped to the n of this round) of the accumulator
-  auto load_batch = [&](int s0, int j0, int n) {
-#pragma unroll
-    for (int b = 0; b < BATCH; ++b) {
-      const float* row = base + (int64_t)(s0 + min(j0 + b, n - 1)) * rec + 4;
-      v[b][0] = owner ? load4(row + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-      v[b][1] = second ? load4(row + 4 * lane + 128) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-  };
-  // the first accumulators are requested together with the (max, sum) pairs: one trip to memory
-  // instead of two when there are few segments
-  load_batch(first, 0, min(32, last - first + 1));
-  // pass 1: every segment's (max, sum), the first 32 segments' kept for the second pass
-  float2 ml_first = make_float2(-INFINITY, 0.f);
-  float m = -INFINITY;
-  for (int s0 = first; s0 <= last; s0 += 32) {
-    const int s = s0 + lane;
-    const float2 ml = s <= last ? load2(base + (int64_t)s * rec) : make_float2(-INFINITY, 0.f);
-    if (s0 == first) ml_first = ml;
-    m = fmaxf(m, ml.x);
-  }
-  m = warp_max(m);
-  // pass 2: weights, sum and accumulator
-  float l = 0.f;
-  float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-  for (int s0 = first; s0 <= last; s0 += 32) {
-    const int mine = s0 + lane;
-    float w_mine = 0.f, l_mine = 0.f;
-    if (mine <= last) {
-      const float2 ml = s0 == first ? ml_first : load2(base + (int64_t)mine * rec);
-      if (ml.x != -INFINITY) {
-        w_mine = fast_exp2(ml.x - m);
-        l_mine = ml.y * w_mine;
-      }
-    }
-    const int n = min(32, last - s0 + 1);
-    for (int j0 = 0; j0 < n; j0 += BATCH) {
-      if (s0 != first || j0 != 0) load_batch(s0, j0, n);
-#pragma unroll
-      for (int b = 0; b < BATCH; ++b) {
-        const bool live = j0 + b < n;
-        const float w = live ? __shfl_sync(0xffffffffu, w_mine, (j0 + b) & 31) : 0.f;
-        l += live ? __shfl_sync(0xffffffffu, l_mine, (j0 + b) & 31) : 0.f;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          acc[i].x = fmaf(v[b][i].x, w, acc[i].x);
-          acc[i].y = fmaf(v[b][i].y, w, acc[i].y);
-          acc[i].z = fmaf(v[b][i].z, w, acc[i].z);
-          acc[i].w = fmaf(v[b][i].w, w, acc[i].w);
-        }
-      }
-    }
-  }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  if (owner)
-    *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(pack_bf16(acc[0].x * inv, acc[0].y * inv), pack_bf16(acc[0].z * inv, acc[0].w * inv));
-  if (second)
-    *reinterpret_cast<uint2*>(dst + 4 * lane + 128) = make_uint2(pack_bf16(acc[1].x * inv, acc[1].y * inv), pack_bf16(acc[1].z * inv, acc[1].w * inv));
-}
-
-// One tile of 16 keys for one warp: S = Q K^T on the tensor cores, the online softmax of the
-// warp's 16 rows (base 2, float32; masked keys count as -inf), O = O * alpha + P V with P rounded
-// to bfloat16. ks / vs: shared-memory addresses of the tile's K and V blocks (128-byte swizzle).
-template <int DMAX, bool Q_IN_REGISTERS>
-__device__ __forceinline__ void attend_tile(uint32_t ks, uint32_t vs, const uint32_t (&qa)[Q_IN_REGISTERS ? DMAX / 16 : 1][4],
-                                            const uint8_t* q_s, int q_pitch, int d, int key0, int kstart, int pos,
-                                            float scale_log2, bool upper_rows_live, uint32_t k_lane, uint32_t k_xor,
-                                            uint32_t v_lane, uint32_t v_xor, float (&m_row)[2], float (&l_row)[2],
-                                            float (&o)[DMAX / 8][4]) {
-  const int lane = threadIdx.x & 31;
-  // ---- S = Q K^T for 16 keys: two 8-key column tiles
-  float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-  for (int kk = 0; kk < DMAX / 16; ++kk) {
-    if (kk * 16 < d) {
-      uint32_t a[4], b[4];
-      if (Q_IN_REGISTERS) {
-        a[0] = qa[Q_IN_REGISTERS ? kk : 0][0]; a[1] = qa[Q_IN_REGISTERS ? kk : 0][1];
-        a[2] = qa[Q_IN_REGISTERS ? kk : 0][2]; a[3] = qa[Q_IN_REGISTERS ? kk : 0][3];
-      } else {
-        ldmatrix_x4(a, smem_addr(q_s + (lane & 15) * q_pitch + (kk * 16 + (lane >> 4) * 8) * 2));
-      }
-      // B: matrices (keys 0-7, k lo), (keys 0-7, k hi), (keys 8-15, k lo), (keys 8-15, k hi)
-      ldmatrix_x4(b, ks + (kk >> 2) * BLOCK_BYTES + k_lane + ((uint32_t)((kk & 3) << 5) ^ k_xor));
-      mma_bf16(s[0], a, b[0], b[1]);
-      mma_bf16(s[1], a, b[2], b[3]);
-    }
-  }
-  // ---- online softmax (rows lane/4 and lane/4 + 8)
-  float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-  for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-      const bool visible = key >= kstart && key <= pos;
-      s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
-      tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
-    }
-  float alpha[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (r == 1 && !upper_rows_live) {              // padding rows: no exponentials (warp-uniform)
-      alpha[r] = 1.f;
-      s[0][2] = s[0][3] = s[1][2] = s[1][3] = 0.f;
-      continue;
-    }
-    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-    const float m_new = fmaxf(m_row[r], tile_max[r]);
-    const float safe = m_new == -INFINITY ? 0.f : m_new;
-    alpha[r] = fast_exp2(m_row[r] - safe);
-    m_row[r] = m_new;
-    float sum = 0.f;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      s[nt][2 * r] = fast_exp2(s[nt][2 * r] - safe);
-      s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - safe);
-      sum += s[nt][2 * r] + s[nt][2 * r + 1];
-    }
-    l_row[r] = l_row[r] * alpha[r] + sum;          // per-thread share; reduced over the quad at the end
-  }
-  uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
-                   pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
-  // ---- O = O * alpha + P V
-#pragma unroll
-  for (int nt = 0; nt < DMAX / 16; ++nt) {
-    if (nt * 16 < d) {
-      o[2 * nt][0] *= alpha[0]; o[2 * nt][1] *= alpha[0]; o[2 * nt][2] *= alpha[1]; o[2 * nt][3] *= alpha[1];
-      o[2 * nt + 1][0] *= alpha[0]; o[2 * nt + 1][1] *= alpha[0]; o[2 * nt + 1][2] *= alpha[1]; o[2 * nt + 1][3] *= alpha[1];
-      uint32_t b[4];
-      // transposed: matrices (keys 0-7, cols lo), (keys 8-15, cols lo), (keys 0-7, cols hi), (keys 8-15, cols hi)
-      ldmatrix_x4_trans(b, vs + (nt >> 2) * BLOCK_BYTES + v_lane + ((uint32_t)((nt & 3) << 5) ^ v_xor));
-      mma_bf16(o[2 * nt], p, b[0], b[1]);
-      mma_bf16(o[2 * nt + 1], p, b[2], b[3]);
-    }
-  }
-}
+using namespace decode_attention;
 
 struct ItemMeta {
   int t, pos, item, g, seg, kstart, request, fresh;  // t < 0: no more items; fresh: the token's own key and value come with it
-};
-
-// What the fused form needs beside the attention's own arguments (partial == null: not fused).
-struct FusedProjection {
-  const float* partial;        // [splits][tokens][(nq + 2 nkv) d] float32
-  int splits;
-  long long plane;             // tokens * (nq + 2 nkv) * d
-  const void* q_norm_w;        // [d] or null: no head norm
-  const void* k_norm_w;
-  int norm_w_is_f32;
-  float eps;
-  const float* cos_table;      // [max_positions][d / 2] float32 or null: no rotation
-  const float* sin_table;
-  int max_positions;
-  const int* slot_mapping;     // [tokens] cache slot of each token's key and value, -1: none
-  long long num_slots;
-  bf16* k_cache;
-  bf16* v_cache;
 };
 
 // DMAX bounds the head size; with EXACT the head size is DMAX itself. FUSED: the query rows and
@@ -732,8 +521,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   }
 }
 
-#include "attention_decode_once.cuh"
-
 // Bytes of dynamic shared memory: ring, Q buffers, merge area, and room to align the ring.
 size_t decode_smem_bytes(int d, int group) {
   const size_t nb = (d + BOX_COLS - 1) / BOX_COLS;
@@ -757,16 +544,6 @@ int ctas_per_sm(int d, int group) {
   const int by_smem = (int)(per_sm / per_cta);
   return by_smem >= 2 ? 2 : 1;                                       // registers allow two
 }
-
-// Shared memory of the one-round kernel with `segments` CTAs per cluster.
-size_t once_smem_bytes(int d, int group, int segments) {
-  const size_t nb = (d + BOX_COLS - 1) / BOX_COLS;
-  return 1024 + (size_t)CONSUMERS * RING * 2 * nb * BLOCK_BYTES + (size_t)16 * ((size_t)d * 2 + 16) +
-         (size_t)CONSUMERS * group * (d + 2) * sizeof(float) + (size_t)2 * d * 2 + 16 +
-         (size_t)segments * group * record_floats(d) * sizeof(float);
-}
-
-constexpr size_t ONCE_SMEM_CAP = 227 * 1024 - 2048;   // dynamic bytes a CTA may ask for: an SM's, less the static arrays
 
 int once_ctas_per_sm(int d, int group, int segments) {
   if (once_smem_bytes(d, group, segments) > ONCE_SMEM_CAP) return 0;
@@ -845,35 +622,6 @@ int once_segments(int count, int nkv, int d, int group, int max_kv_len, int page
     }
   }
   return best;
-}
-
-// How many clusters of `cluster` CTAs with `smem` bytes each the GPU can run at once (0: none, or
-// the size cannot be scheduled); asked once per (kernel, size, bytes).
-template <typename Kernel>
-int once_clusters_that_fit(Kernel kernel, int cluster, size_t smem) {
-  static std::unordered_map<uint64_t, int> known;
-  static std::mutex mutex;
-  std::lock_guard<std::mutex> lock(mutex);
-  const uint64_t key = ((uint64_t)smem << 8) | (uint64_t)cluster;
-  auto it = known.find(key);
-  if (it != known.end()) return it->second;
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((unsigned)cluster);
-  config.blockDim = dim3(THREADS);
-  config.dynamicSmemBytes = smem;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeClusterDimension;
-  attribute[0].val.clusterDim.x = (unsigned)cluster;
-  attribute[0].val.clusterDim.y = attribute[0].val.clusterDim.z = 1;
-  config.attrs = attribute;
-  config.numAttrs = 1;
-  int clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
-    (void)cudaGetLastError();
-    clusters = 0;
-  }
-  known.emplace(key, clusters);
-  return clusters;
 }
 
 int choose_segment_keys(int count, int nkv, int d, int group, int max_kv_len, int page_size = 0) {
@@ -976,49 +724,36 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, void*
     int once_keys = 0;
     const int once = once_segments(count, nkv, d, group, max_kv_len, page_size, &once_keys);
     if (once > 0) {
-      const size_t smem = once_smem_bytes(d, group, once);
-      const dim3 grid((unsigned)((int64_t)count * nkv * once));
-      bool launched = false;
-#define LAUNCH_ONCE_AS(DMAX, EXACT, FUSED)                                                                          \
-  do {                                                                                                              \
-    auto kernel = attention_decode_once_kernel<DMAX, EXACT, FUSED>;                                                 \
-    static bool configured = false;                                                                                 \
-    if (!configured) {                                                                                              \
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ONCE_SMEM_CAP);               \
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);                              \
-      configured = true;                                                                                            \
-    }                                                                                                               \
-    const int fit = once_clusters_that_fit(kernel, once, smem);                                                     \
-    if (once == 1 && smem <= ONCE_SMEM_CAP) {                                                                       \
-      /* no cluster to form: an ordinary launch, whose CTAs are spread over all SMs first */                        \
-      vosti_launch(kernel, grid, dim3(THREADS), smem, stream, map_k, map_v, (const bf16*)q, (bf16*)out, token_list,  \
-                   positions, request_of, block_table, max_pages, page_size, page_shift, num_pages, whole_rows, nq,  \
-                   nkv, d, once_keys, scale * LOG2E, window, status, fused);                                         \
-      launched = true;                                                                                              \
-    } else if (fit >= 1 && smem <= ONCE_SMEM_CAP) {                                                                 \
-      vosti_launch_clusters(kernel, grid, dim3(THREADS), (unsigned)once, smem, stream, map_k, map_v, (const bf16*)q, \
-                            (bf16*)out, token_list, positions, request_of, block_table, max_pages, page_size,       \
-                            page_shift, num_pages, whole_rows, nq, nkv, d, once_keys, scale * LOG2E, window, status, \
-                            fused);                                                                                 \
-      launched = true;                                                                                              \
-    }                                                                                                               \
-  } while (0)
-#define LAUNCH_ONCE(DMAX, EXACT)                                                                                    \
-  do {                                                                                                              \
-    if (fused.partial != nullptr) LAUNCH_ONCE_AS(DMAX, EXACT, true);                                                \
-    else LAUNCH_ONCE_AS(DMAX, EXACT, false);                                                                        \
-  } while (0)
-      if (d == 64) LAUNCH_ONCE(64, true);
-      else if (d == 128) LAUNCH_ONCE(128, true);
-      else if (d == 256) LAUNCH_ONCE(256, true);
-      else if (d < 64) LAUNCH_ONCE(64, false);
-      else if (d < 128) LAUNCH_ONCE(128, false);
-      else LAUNCH_ONCE(256, false);
-#undef LAUNCH_ONCE
-#undef LAUNCH_ONCE_AS
-      if (launched) {
+      OnceLaunch launch;
+      launch.map_k = map_k;
+      launch.map_v = map_v;
+      launch.q = (const bf16*)q;
+      launch.out = (bf16*)out;
+      launch.token_list = token_list;
+      launch.positions = positions;
+      launch.request_of = request_of;
+      launch.block_table = block_table;
+      launch.max_pages = max_pages;
+      launch.page_size = page_size;
+      launch.page_shift = page_shift;
+      launch.num_pages = num_pages;
+      launch.whole_rows = whole_rows;
+      launch.count = count;
+      launch.nq = nq;
+      launch.nkv = nkv;
+      launch.d = d;
+      launch.segments = once;
+      launch.segment_keys = once_keys;
+      launch.scale_log2 = scale * LOG2E;
+      launch.window = window;
+      launch.status = status;
+      launch.fused = fused;
+      launch.stream = stream;
+      const int launched = launch_once(launch);
+      if (launched < 0) return -launched;
+      if (launched > 0) {
         g_last_kernel = 2;
-        VOSTI_LAUNCH_CHECK();
+        return VOSTI_OK;
       }
     }
   }

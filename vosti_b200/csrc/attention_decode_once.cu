@@ -1,6 +1,7 @@
 // The decode attention with one CTA per (token, kv head, segment), the segments of a (token, kv
-// head) forming a thread-block cluster. Included by attention_decode.cu (it uses that file's tile
-// arithmetic, merge and constants).
+// head) forming a thread-block cluster. The tile arithmetic, the merge of segments and the
+// constants are those of the persistent kernel (attention_decode_common.cuh); the rule that says
+// which launch takes which kernel is in attention_decode.cu.
 //
 // With few tokens the persistent kernel's time is mostly its ends: the producer describing the
 // item to the consumers, and at the far end three trips through global memory (the partial
@@ -18,7 +19,14 @@
 // Needs pages of a multiple of 16 tokens and segments of at most 4096 keys. The fused form (query
 // rows and the token's own key and value from the projection's partial sums) is as in the
 // persistent kernel.
-#pragma once
+#include <mutex>
+#include <unordered_map>
+
+#include "attention_decode_common.cuh"
+
+namespace {
+
+using namespace decode_attention;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -76,7 +84,6 @@ __device__ __forceinline__ int load_now(const int* p) {
   return v;
 }
 
-constexpr int ONCE_MAX_SEGMENTS = 16;     // CTAs per cluster (above 8 the kernel opts in to non-portable sizes)
 
 template <int DMAX, bool EXACT, bool FUSED>
 __global__ void __launch_bounds__(THREADS, DMAX <= 128 ? 2 : 1)
@@ -388,3 +395,93 @@ attention_decode_once_kernel(const __grid_constant__ CUtensorMap map_k, const __
   for (int row = cw; row < group; row += CONSUMERS)
     merge_segments<false>(records + (int64_t)row * segments * grec, out + ((int64_t)t * nq + g * group + row) * d, p_first, p_last, d);
 }
+
+// How many clusters of `cluster` CTAs with `smem` bytes each the GPU can run at once (0: none, or
+// the size cannot be scheduled); asked once per (kernel, size, bytes).
+template <typename Kernel>
+int clusters_that_fit(Kernel kernel, int cluster, size_t smem) {
+  static std::unordered_map<uint64_t, int> known;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  const uint64_t key = ((uint64_t)smem << 8) | (uint64_t)cluster;
+  auto it = known.find(key);
+  if (it != known.end()) return it->second;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)cluster);
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = (unsigned)cluster;
+  attribute[0].val.clusterDim.y = attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
+    (void)cudaGetLastError();
+    clusters = 0;
+  }
+  known.emplace(key, clusters);
+  return clusters;
+}
+
+template <int DMAX, bool EXACT, bool FUSED>
+int launch_as(const OnceLaunch& a, size_t smem) {
+  auto kernel = attention_decode_once_kernel<DMAX, EXACT, FUSED>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ONCE_SMEM_CAP);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    configured = true;
+  }
+  const dim3 grid((unsigned)((int64_t)a.count * a.nkv * a.segments));
+  cudaError_t e;
+  if (a.segments == 1) {
+    // no cluster to form: an ordinary launch, whose CTAs are spread over all SMs first
+    e = vosti_launch(kernel, grid, dim3(THREADS), smem, a.stream, a.map_k, a.map_v, a.q, a.out, a.token_list, a.positions,
+                     a.request_of, a.block_table, a.max_pages, a.page_size, a.page_shift, a.num_pages, a.whole_rows, a.nq, a.nkv,
+                     a.d, a.segment_keys, a.scale_log2, a.window, a.status, a.fused);
+  } else {
+    if (clusters_that_fit(kernel, a.segments, smem) < 1) return 0;
+    e = vosti_launch_clusters(kernel, grid, dim3(THREADS), (unsigned)a.segments, smem, a.stream, a.map_k, a.map_v, a.q, a.out,
+                              a.token_list, a.positions, a.request_of, a.block_table, a.max_pages, a.page_size, a.page_shift,
+                              a.num_pages, a.whole_rows, a.nq, a.nkv, a.d, a.segment_keys, a.scale_log2, a.window, a.status,
+                              a.fused);
+  }
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    vosti_set_error("attention_decode (one CTA per item): %s", cudaGetErrorString(e));
+    return -(int)e;
+  }
+  return 1;
+}
+
+template <int DMAX, bool EXACT>
+int launch_form(const OnceLaunch& a, size_t smem) {
+  return a.fused.partial != nullptr ? launch_as<DMAX, EXACT, true>(a, smem) : launch_as<DMAX, EXACT, false>(a, smem);
+}
+
+}  // namespace
+
+namespace decode_attention {
+
+size_t once_smem_bytes(int d, int group, int segments) {
+  const size_t nb = (d + BOX_COLS - 1) / BOX_COLS;
+  return 1024 + (size_t)CONSUMERS * RING * 2 * nb * BLOCK_BYTES + (size_t)16 * ((size_t)d * 2 + 16) +
+         (size_t)CONSUMERS * group * (d + 2) * sizeof(float) + (size_t)2 * d * 2 + 16 +
+         (size_t)segments * group * record_floats(d) * sizeof(float);
+}
+
+int launch_once(const OnceLaunch& a) {
+  const int d = a.d;
+  const size_t smem = once_smem_bytes(d, a.nq / a.nkv, a.segments);
+  if (smem > ONCE_SMEM_CAP) return 0;
+  if (d == 64) return launch_form<64, true>(a, smem);
+  if (d == 128) return launch_form<128, true>(a, smem);
+  if (d == 256) return launch_form<256, true>(a, smem);
+  if (d < 64) return launch_form<64, false>(a, smem);
+  if (d < 128) return launch_form<128, false>(a, smem);
+  return launch_form<256, false>(a, smem);
+}
+
+}  // namespace decode_attention
