@@ -847,10 +847,10 @@ def test_one_round_decode_attention_gives_the_bits_of_the_persistent_kernel(dev,
     memory; with many it walks over its items and merges through global memory. At the same segment
     length both give the same bits, in the plain form and in the fused one, whatever the lengths
     (one key, one segment, a window that hides the first segments); and the rule takes the
-    one-round kernel exactly where it says."""
+    kernel with one CTA per item exactly where it says."""
     from vosti_b200 import ops
     lib = ops.library()
-    # few enough tokens for one round: clusters of more than 8 CTAs only serve up to 8 (token, kv head)
+    # few enough tokens for all CTAs to run at once: clusters of more than 8 CTAs only serve up to 8 (token, kv head)
     # pairs, and with head size 256 an SM holds one CTA, so that fewer clusters fit the GPU at once
     lengths = [2047, 300, 1, 1500, 17, 1024, 33, 640, 2000, 129, 64, 65, 1999, 5, 1025, 511]
     lens_k = lengths[: max(1, (8 if -(-2047 // segment) > 8 or d > 128 else 16) // nkv)]

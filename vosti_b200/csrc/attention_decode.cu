@@ -561,7 +561,7 @@ int once_ctas_per_sm(int d, int group, int segments) {
 //    the persistent CTAs in rounds; a round costs the segment's length plus a fixed share for
 //    starting and finishing an item.
 int g_pinned_segment = 0;           // vosti_set_decode_segment: 0 lets every launch choose
-thread_local int g_last_kernel = 0; // which kernel this thread's last launch took: 1 persistent, 2 one-round
+thread_local int g_last_kernel = 0; // which kernel this thread's last launch took: 1 persistent, 2 one CTA per item
 int g_once_enabled = -1;            // vosti_set_decode_once; -1: from VOSTI_DECODE_ONCE (default on)
 
 bool once_enabled() {
@@ -659,14 +659,14 @@ VOSTI_API int vosti_set_decode_segment(int keys) {
   return VOSTI_OK;
 }
 
-// The one-round kernel on (1, the default) or off (0) for every later launch of this process.
+// The kernel with one CTA per item on (1, the default) or off (0) for every later launch of this process.
 VOSTI_API int vosti_set_decode_once(int enabled) {
   g_once_enabled = enabled ? 1 : 0;
   return VOSTI_OK;
 }
 
 // Which kernel this thread's last decode-attention launch took: 1 the persistent one, 2 the
-// one-round one, 0 none yet (for tests of the rule above).
+// one with one CTA per item, 0 none yet (for tests of the rule above).
 VOSTI_API int vosti_attention_decode_last_kernel() { return g_last_kernel; }
 
 // Keys per segment, and so (max_kv_len + keys - 1) / keys partial records per token and
@@ -676,12 +676,12 @@ VOSTI_API int vosti_attention_decode_segment_keys(int count, int nq, int nkv, in
 }
 
 // float32 scratch elements a launch of this shape may need: count * nq * segments * (d + 4) for the
-// persistent kernel's records (the one-round kernel needs none; with pages of no multiple of 16
-// tokens the persistent kernel runs where the segment rule above names the one-round kernel's
+// persistent kernel's records (the kernel with one CTA per item needs none; with pages of no multiple of 16
+// tokens the persistent kernel runs where the segment rule above names the other kernel's
 // length, so the larger of the two is returned).
 VOSTI_API int64_t vosti_attention_decode_scratch(int count, int nq, int nkv, int d, int max_kv_len) {
   const int keys = vosti_attention_decode_segment_keys(count, nq, nkv, d, max_kv_len);
-  const int other = choose_segment_keys(count, nkv, d, nq / nkv, max_kv_len, 1);      // page size 1: never the one-round kernel
+  const int other = choose_segment_keys(count, nkv, d, nq / nkv, max_kv_len, 1);      // page size 1: never the other kernel's rule
   const int shorter = keys < other ? keys : other;
   return (int64_t)count * nq * ((max_kv_len + shorter - 1) / shorter) * record_floats(d);
 }
@@ -720,7 +720,7 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, void*
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
   {
-    // ---- one round: a cluster of CTAs per (token, kv head)
+    // ---- one CTA per item: a cluster of CTAs per (token, kv head)
     int once_keys = 0;
     const int once = once_segments(count, nkv, d, group, max_kv_len, page_size, &once_keys);
     if (once > 0) {
@@ -758,7 +758,7 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, void*
     }
   }
   g_last_kernel = 1;
-  // ---- the persistent kernel (page size 1 in the rule: never the one-round kernel's length)
+  // ---- the persistent kernel (page size 1 in the rule: never the other kernel's length)
   const int segment_keys = choose_segment_keys(count, nkv, d, group, max_kv_len, 1);
   const int segments = (max_kv_len + segment_keys - 1) / segment_keys;
   VOSTI_REQUIRE(arrivals != nullptr, "attention_decode: the arrival counters are missing");

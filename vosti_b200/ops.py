@@ -468,7 +468,7 @@ BATCH_INVARIANT_SEGMENT = 576    # keys per decode-attention segment when the le
 
 
 def set_decode_once(enabled: bool) -> None:
-    """The decode attention's one-round kernel (a cluster of CTAs per token and kv head) on or off
+    """The decode attention's kernel with one CTA per item (a cluster of CTAs per token and kv head) on or off
     for every later launch of this process; off, every launch takes the persistent kernel."""
     _check(library().vosti_set_decode_once(1 if enabled else 0), "set_decode_once", kernels=0)
 
