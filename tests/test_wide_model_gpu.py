@@ -183,3 +183,31 @@ def test_wide_bits_do_not_depend_on_the_cut_in_fixed_order(name, wide_dirs, tmp_
             for kind in ("tail", "portion", "mixed"):
                 assert np.array_equal(whole, rows[(f"{kind}-{rid}", position)]), \
                     f"{rid} position {position}: {kind} differs from whole"
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+@pytest.mark.parametrize("name", ["w", "x"])
+def test_wide_random_mixes_in_the_default_mode(name, seed, wide_dirs, wide_plain, tmp_path):
+    """Other random mixes of portions and decoded tokens of up to four live requests, in bfloat16
+    with every fast path on (split products, fused decode attention with its clusters, graphs
+    off in replay): every logit row against the plain implementation, within the bound the
+    reference's own rounding points give."""
+    import plain_qwen3 as plain
+    path, config, page = wide_dirs[name]
+    lengths = [LENGTHS[name][(seed + i) % len(LENGTHS[name])] + 3 * i + seed % 7 for i in range(5)]
+    requests = {f"m{i}": R.random_tokens(config["vocab_size"], n, seed=seed * 100 + i) for i, n in enumerate(lengths)}
+    steps = R.number(R.mixed_steps(requests, seed=seed))
+    max_tokens = R.max_live_tokens(steps)
+    assert max_tokens < sum(R.roundup64(len(t)) for t in requests.values())          # pages are used again
+    R.run_in_process(path, "bfloat16", steps, max_tokens, page, tmp_path)
+    rows = R.collect(steps, tmp_path, config["vocab_size"])
+    assert len(rows) == sum(len(t) for t in requests.values())
+    worst = R.compare_with_plain(rows, requests, wide_plain[name], "bfloat16")
+    cfg, W = wide_plain[name]
+    emulated = 0.0
+    for tokens in requests.values():
+        exact = plain.forward_logits(cfg, W, tokens).numpy()
+        rounded = plain.forward_logits(cfg, W, tokens, round_to=torch.bfloat16).numpy()
+        emulated = max(emulated, float(np.abs(rounded - exact).max()) / max(1.0, float(np.abs(exact).max())))
+    print(f"{name} seed {seed}: worst {worst:.3e}, the reference's rounding points {emulated:.3e}")
+    assert worst <= 1.5 * emulated
