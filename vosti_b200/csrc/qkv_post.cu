@@ -9,6 +9,7 @@
 // float32 there and rounds once at the store.
 #include "common.cuh"
 #include "head_post.cuh"
+#include "mma_util.cuh"
 
 namespace {
 constexpr int MAX_PAIRS_PER_LANE = HEAD_MAX_PAIRS;  // head_dim <= 512
@@ -146,67 +147,113 @@ qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ partial, in
   }
 }
 
-// The same pass for many tokens (prompts), bfloat16, head sizes 64, 128 and 256: one block per
-// token, a warp takes every eighth head and six heads at a time, so that the loads of all are
-// in flight together; a lane holds VE consecutive elements of each half of the head and moves
-// them as one 2-, 4- or 8-byte word.
-template <int VE>
-__global__ void __launch_bounds__(256)
-qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
-                     bf16* __restrict__ v_cache, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
-                     int norm_w_is_f32, float eps, const float* __restrict__ cos_table,
-                     const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
-                     const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv,
-                     unsigned* status) {
-  constexpr int HALF = 32 * VE, D = 2 * HALF;
-  struct alignas(2 * VE) Word { bf16 v[VE]; };
-  const int t = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// The same pass for many tokens (prompts), bfloat16, head sizes 64, 128 and 256, as a stream: a
+// block walks over tokens; a token's row of the projection and its rows of the rotation tables come
+// by bulk copies into a ring of `stages` buffers in shared memory (what a block has in flight
+// costs no registers, so four blocks to an SM keep well over 100 KB on their way), the threads
+// read 16-byte words from there (D / 16 lanes share a head: 8 consecutive elements of each half per
+// lane) and write 16-byte words to q and the caches. (A block per token with 2- to 8-byte words
+// per lane moved 2.7 TB/s at 8,192 tokens of the 8B sizes, with 16-byte words from global memory
+// into registers 3.3.)
+template <int D>
+__global__ void __launch_bounds__(256, 4)
+qkv_post_stream_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
+                       bf16* __restrict__ v_cache, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
+                       int norm_w_is_f32, float eps, const float* __restrict__ cos_table,
+                       const float* __restrict__ sin_table, int max_positions, const int* __restrict__ positions,
+                       const int* __restrict__ slot_mapping, int64_t num_slots, int page_size, int nq, int nkv, int tokens,
+                       int stages, unsigned* status) {
+  constexpr int HALF = D / 2, LANES_PER_HEAD = D / 16, E = 8, MAX_STAGES = 4;
+  extern __shared__ __align__(16) uint8_t stream_smem[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+  __shared__ float wq_s[D], wk_s[D];
   const int heads = nq + 2 * nkv;
-  const bf16* row = qkv + (int64_t)t * heads * D;
-  int pos = positions ? positions[t] : 0;
-  if (cos_table && (pos < 0 || pos >= max_positions)) {
-    if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
-    pos = 0;
+  const uint32_t row_bytes = (uint32_t)heads * D * 2, table_bytes = HALF * 4;
+  const uint32_t stage_bytes = row_bytes + 2 * table_bytes;      // the row, then the cosines, then the sines
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LANES_PER_HEAD;                         // this lane's elements: sub * 8 .. sub * 8 + 7 of each half
+  const int mine = (int)blockIdx.x < tokens ? (tokens - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < MAX_STAGES; ++i) mb_init(smem_addr(&full_bar[i]), 1);
+    mb_fence_init();
   }
-  int64_t slot = -1;
-  if (nkv > 0 && slot_mapping) {
-    slot = slot_mapping[t];
+  for (int i = threadIdx.x; i < D; i += 256) {
+    wq_s[i] = q_norm_w ? load_flex(q_norm_w, norm_w_is_f32, i) : 1.f;
+    wk_s[i] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i) : 1.f;
+  }
+  __syncthreads();
+  pdl_wait();                      // the projection comes from the kernel before this one
+  pdl_launch_dependents();
+
+  // token number i of this block, whose position is `pos`, into buffer i % stages (thread 0)
+  auto token_of = [&](int i) { return (int)blockIdx.x + i * (int)gridDim.x; };
+  auto position_of = [&](int i) { return (positions && i < mine) ? positions[token_of(i)] : 0; };
+  auto issue = [&](int i, int pos) {
+    const int t = token_of(i);
+    uint8_t* stage = stream_smem + (size_t)(i % stages) * stage_bytes;
+    const uint32_t bar = smem_addr(&full_bar[i % stages]);
+    if (cos_table && (pos < 0 || pos >= max_positions)) {
+      raise_fault(status, VOSTI_FAULT_POSITION_RANGE);
+      pos = 0;
+    }
+    mb_expect_tx(bar, row_bytes + (cos_table ? 2 * table_bytes : 0));
+    bulk_copy_g2s(smem_addr(stage), qkv + (int64_t)t * heads * D, row_bytes, bar);
+    if (cos_table) {
+      bulk_copy_g2s(smem_addr(stage + row_bytes), cos_table + (int64_t)pos * HALF, table_bytes, bar);
+      bulk_copy_g2s(smem_addr(stage + row_bytes + table_bytes), sin_table + (int64_t)pos * HALF, table_bytes, bar);
+    }
+  };
+  if (threadIdx.x == 0)
+    for (int i = 0; i < mine && i < stages - 1; ++i) issue(i, position_of(i));
+  // what the next copy and the next token's stores need is read a token ahead
+  int pos_ahead = threadIdx.x == 0 ? position_of(stages - 1) : 0;
+  auto slot_of = [&](int i) -> int64_t { return (nkv > 0 && slot_mapping && i < mine) ? (int64_t)slot_mapping[token_of(i)] : -1; };
+  int64_t slot_ahead = slot_of(0);
+
+  const int items = heads * LANES_PER_HEAD;                      // (head, lane of the head) pairs of a token
+  for (int i = 0; i < mine; ++i) {
+    const int t = token_of(i);
+    // every thread is done with the buffer the next copy goes to (it held token i - 1)
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (i + stages - 1 < mine) issue(i + stages - 1, pos_ahead);
+      pos_ahead = position_of(i + stages);
+    }
+    int64_t slot = slot_ahead;
+    slot_ahead = slot_of(i + 1);
     if (slot >= num_slots || slot < -1) {
       if (threadIdx.x == 0) raise_fault(status, VOSTI_FAULT_SLOT_RANGE);
       slot = -1;
     }
-  }
-  // this lane's rotation factors and norm weights serve every head
-  float c[VE], sn[VE], wq1[VE], wq2[VE], wk1[VE], wk2[VE];
-#pragma unroll
-  for (int e = 0; e < VE; ++e) {
-    const int i = lane * VE + e;
-    c[e] = cos_table ? cos_table[(int64_t)pos * HALF + i] : 1.f;
-    sn[e] = sin_table ? sin_table[(int64_t)pos * HALF + i] : 0.f;
-    wq1[e] = q_norm_w ? load_flex(q_norm_w, norm_w_is_f32, i) : 1.f;
-    wq2[e] = q_norm_w ? load_flex(q_norm_w, norm_w_is_f32, i + HALF) : 1.f;
-    wk1[e] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i) : 1.f;
-    wk2[e] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i + HALF) : 1.f;
-  }
-  pdl_wait();                      // everything above was written before the step began
-  pdl_launch_dependents();
-  constexpr int UNROLL = 6;
-  for (int h0 = warp; h0 < heads; h0 += 8 * UNROLL) {
-    Word a[UNROLL], b[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int h = h0 + 8 * u;
-      if (h < heads) {
-        a[u] = *reinterpret_cast<const Word*>(row + (int64_t)h * D + lane * VE);
-        b[u] = *reinterpret_cast<const Word*>(row + (int64_t)h * D + HALF + lane * VE);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int h = h0 + 8 * u;
-      if (h >= heads) continue;
+    const uint8_t* stage = stream_smem + (size_t)(i % stages) * stage_bytes;
+    if (!mb_wait(smem_addr(&full_bar[i % stages]), (uint32_t)(i / stages) & 1, status)) return;
+    const float* c_s = reinterpret_cast<const float*>(stage + row_bytes);
+    const float* sn_s = c_s + HALF;
+    for (int base = warp * 32; base < items; base += 256) {      // (a warp's lanes stay together: shuffles below)
+      const int item = base + lane;
+      const bool live = item < items;
+      const int h = item / LANES_PER_HEAD;
       const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+      uint4 a = make_uint4(0, 0, 0, 0), b = a;
+      if (live) {
+        a = *reinterpret_cast<const uint4*>(stage + ((size_t)h * D + sub * E) * 2);
+        b = *reinterpret_cast<const uint4*>(stage + ((size_t)h * D + HALF + sub * E) * 2);
+      }
+      float x1[E], x2[E], ss = 0.f;
+      const bf16* av = reinterpret_cast<const bf16*>(&a);
+      const bf16* bv = reinterpret_cast<const bf16*>(&b);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        x1[e] = to_f32(av[e]);
+        x2[e] = to_f32(bv[e]);
+        ss += x1[e] * x1[e] + x2[e] * x2[e];
+      }
+      // the head's sum of squares over the lanes that share it (every lane of the warp takes part)
+#pragma unroll
+      for (int o = 1; o < LANES_PER_HEAD; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (!live) continue;
       bf16* dst;
       if (is_q) {
         dst = q_out + ((int64_t)t * nq + h) * D;
@@ -216,33 +263,37 @@ qkv_post_wide_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf1
         dst = (is_k ? k_cache : v_cache) + (((slot / page_size) * nkv + g) * page_size + slot % page_size) * D;
       }
       if (is_q || is_k) {
-        float x1[VE], x2[VE], ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < VE; ++e) {
-          x1[e] = to_f32(a[u].v[e]);
-          x2[e] = to_f32(b[u].v[e]);
-          ss += x1[e] * x1[e] + x2[e] * x2[e];
-        }
         const bool normed = is_q ? q_norm_w != nullptr : k_norm_w != nullptr;
-        const float rrms = normed ? rsqrtf(warp_sum(ss) / (float)D + eps) : 1.f;
+        const float rrms = normed ? rsqrtf(ss / (float)D + eps) : 1.f;
+        const float* w = is_q ? wq_s : wk_s;
+        uint32_t pa[E / 2], pb[E / 2];
 #pragma unroll
-        for (int e = 0; e < VE; ++e) {
-          float p = x1[e], r = x2[e];
-          if (normed) {
-            p = p * rrms * (is_q ? wq1[e] : wk1[e]);
-            r = r * rrms * (is_q ? wq2[e] : wk2[e]);
+        for (int e = 0; e < E; e += 2) {
+          float p[2], r[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            p[j] = x1[e + j];
+            r[j] = x2[e + j];
+            if (normed) {
+              p[j] = p[j] * rrms * w[sub * E + e + j];
+              r[j] = r[j] * rrms * w[HALF + sub * E + e + j];
+            }
+            if (cos_table) {
+              const float cs = c_s[sub * E + e + j], sj = sn_s[sub * E + e + j];
+              const float ra = p[j] * cs - r[j] * sj, rb = r[j] * cs + p[j] * sj;
+              p[j] = ra;
+              r[j] = rb;
+            }
           }
-          if (cos_table) {
-            const float ra = p * c[e] - r * sn[e], rb = r * c[e] + p * sn[e];
-            p = ra;
-            r = rb;
-          }
-          a[u].v[e] = from_f32<bf16>(p);
-          b[u].v[e] = from_f32<bf16>(r);
+          __nv_bfloat162 va = __floats2bfloat162_rn(p[0], p[1]), vb = __floats2bfloat162_rn(r[0], r[1]);
+          pa[e / 2] = *reinterpret_cast<uint32_t*>(&va);
+          pb[e / 2] = *reinterpret_cast<uint32_t*>(&vb);
         }
+        a = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+        b = make_uint4(pb[0], pb[1], pb[2], pb[3]);
       }
-      *reinterpret_cast<Word*>(dst + lane * VE) = a[u];
-      *reinterpret_cast<Word*>(dst + HALF + lane * VE) = b[u];
+      *reinterpret_cast<uint4*>(dst + sub * E) = a;
+      *reinterpret_cast<uint4*>(dst + HALF + sub * E) = b;
     }
   }
 }
@@ -354,16 +405,32 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
                    max_positions, positions, slot_mapping, num_slots, page_size, nq, nkv, d, rotary_dim, interleaved, status);
     VOSTI_LAUNCH_CHECK();
   }
-  if (!is_f32 && partial == nullptr && tokens >= 64 && !g_vosti_fixed_order && (d == 64 || d == 128 || d == 256)) {
-    // many tokens: a block per token, vector accesses
-#define LAUNCH_QKV_POST_WIDE(VE)                                                                                   \
-    vosti_launch(qkv_post_wide_kernel<VE>, dim3(tokens), dim3(256), 0, stream, (const bf16*)qkv, (bf16*)q_out,     \
-        (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table,              \
-        max_positions, positions, slot_mapping, num_slots, page_size, nq, nkv, status)
-    if (d == 64) LAUNCH_QKV_POST_WIDE(1);
-    else if (d == 128) LAUNCH_QKV_POST_WIDE(2);
-    else LAUNCH_QKV_POST_WIDE(4);
-#undef LAUNCH_QKV_POST_WIDE
+  // many tokens: the streaming kernel, if two buffers of a token's row fit a block's share of an SM
+  const size_t stream_stage = (size_t)heads * d * 2 + (size_t)d * 4;          // the row and its two table rows
+  if (!is_f32 && partial == nullptr && tokens >= 64 && !g_vosti_fixed_order && (d == 64 || d == 128 || d == 256) &&
+      2 * stream_stage <= 100 * 1024 && ((uintptr_t)qkv % 16 == 0) && ((size_t)heads * d * 2) % 16 == 0 &&
+      (cos_table == nullptr || ((uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0))) {
+    // four blocks to an SM where the buffers allow it; up to four buffers each
+    int stages = (int)((54 * 1024) / stream_stage);
+    stages = stages > 4 ? 4 : stages < 2 ? 2 : stages;
+    const size_t smem = (size_t)stages * stream_stage;
+    const int per_sm = smem <= 54 * 1024 ? 4 : 2;
+    const int blocks = tokens < 148 * per_sm ? tokens : 148 * per_sm;
+#define LAUNCH_QKV_POST_STREAM(D)                                                                                 \
+    do {                                                                                                           \
+      static bool configured = false;                                                                              \
+      if (!configured) {                                                                                           \
+        cudaFuncSetAttribute(qkv_post_stream_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);   \
+        configured = true;                                                                                         \
+      }                                                                                                            \
+      vosti_launch(qkv_post_stream_kernel<D>, dim3(blocks), dim3(256), smem, stream, (const bf16*)qkv, (bf16*)q_out, \
+          (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table,            \
+          max_positions, positions, slot_mapping, num_slots, page_size, nq, nkv, tokens, stages, status);          \
+    } while (0)
+    if (d == 64) LAUNCH_QKV_POST_STREAM(64);
+    else if (d == 128) LAUNCH_QKV_POST_STREAM(128);
+    else LAUNCH_QKV_POST_STREAM(256);
+#undef LAUNCH_QKV_POST_STREAM
     VOSTI_LAUNCH_CHECK();
   }
   const dim3 grid(tokens, (heads + 3) / 4);                          // a warp per (token, head)
