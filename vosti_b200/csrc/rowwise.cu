@@ -120,10 +120,21 @@ rmsnorm_vec_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual
       uint4 ov, hv;
       bf16* oe = reinterpret_cast<bf16*>(&ov);
       bf16* he = reinterpret_cast<bf16*>(&hv);
+      // the chunk's eight weights as 16-byte words (the weight tensor is 16-byte aligned: checked by the launcher)
+      float w[8];
+      if (weight_is_f32) {
+        const float4 w0 = reinterpret_cast<const float4*>(weight)[idx * 2], w1 = reinterpret_cast<const float4*>(weight)[idx * 2 + 1];
+        w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+      } else {
+        const uint4 wv = reinterpret_cast<const uint4*>(weight)[idx];
+        const bf16* we = reinterpret_cast<const bf16*>(&wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = to_f32(we[e]);
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         he[e] = from_f32<bf16>(h[c][e]);
-        oe[e] = from_f32<bf16>(h[c][e] * rrms * load_flex(weight, weight_is_f32, idx * 8 + e));
+        oe[e] = from_f32<bf16>(h[c][e] * rrms * w[e]);
       }
       if (residual_out) *reinterpret_cast<uint4*>(residual_out + base + idx * 8) = hv;
       *reinterpret_cast<uint4*>(out + base + idx * 8) = ov;
@@ -143,7 +154,7 @@ VOSTI_API int vosti_rmsnorm(const void* x, const void* residual, const void* wei
   VOSTI_REQUIRE(out != x && out != residual && out != residual_out, "rmsnorm: out must not alias another operand");
   const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!is_f32 && width % 8 == 0 && width <= 256 * 8 * 4 && aligned(x) && aligned(residual) && aligned(out) &&
-      aligned(residual_out)) {
+      aligned(residual_out) && aligned(weight)) {
     vosti_launch(rmsnorm_vec_kernel<256, 4>, dim3(rows), dim3(256), 0, stream, (const bf16*)x, (const bf16*)residual,
                  weight, weight_is_f32, (bf16*)out, (bf16*)residual_out, width, eps);
     VOSTI_LAUNCH_CHECK();
