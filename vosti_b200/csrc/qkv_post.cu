@@ -166,7 +166,7 @@ qkv_post_stream_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, b
   constexpr int HALF = D / 2, LANES_PER_HEAD = D / 16, E = 8, MAX_STAGES = 4;
   extern __shared__ __align__(16) uint8_t stream_smem[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
-  __shared__ float wq_s[D], wk_s[D];
+  __shared__ __align__(16) float wq_s[D], wk_s[D];
   const int heads = nq + 2 * nkv;
   const uint32_t row_bytes = (uint32_t)heads * D * 2, table_bytes = HALF * 4;
   const uint32_t stage_bytes = row_bytes + 2 * table_bytes;      // the row, then the cosines, then the sines
@@ -178,7 +178,7 @@ qkv_post_stream_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, b
     for (int i = 0; i < MAX_STAGES; ++i) mb_init(smem_addr(&full_bar[i]), 1);
     mb_fence_init();
   }
-  for (int i = threadIdx.x; i < D; i += 256) {
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
     wq_s[i] = q_norm_w ? load_flex(q_norm_w, norm_w_is_f32, i) : 1.f;
     wk_s[i] = k_norm_w ? load_flex(k_norm_w, norm_w_is_f32, i) : 1.f;
   }
@@ -231,7 +231,7 @@ qkv_post_stream_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, b
     if (!mb_wait(smem_addr(&full_bar[i % stages]), (uint32_t)(i / stages) & 1, status)) return;
     const float* c_s = reinterpret_cast<const float*>(stage + row_bytes);
     const float* sn_s = c_s + HALF;
-    for (int base = warp * 32; base < items; base += 256) {      // (a warp's lanes stay together: shuffles below)
+    for (int base = warp * 32; base < items; base += (int)blockDim.x) {   // (a warp's lanes stay together: shuffles below)
       const int item = base + lane;
       const bool live = item < items;
       const int h = item / LANES_PER_HEAD;
@@ -266,6 +266,15 @@ qkv_post_stream_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, b
         const bool normed = is_q ? q_norm_w != nullptr : k_norm_w != nullptr;
         const float rrms = normed ? rsqrtf(ss / (float)D + eps) : 1.f;
         const float* w = is_q ? wq_s : wk_s;
+        // this lane's eight weights of each half and its eight rotation factors, as 16-byte words
+        float w1[E], w2[E], cs[E], sj[E];
+#pragma unroll
+        for (int v = 0; v < E / 4; ++v) {
+          *reinterpret_cast<float4*>(w1 + 4 * v) = *reinterpret_cast<const float4*>(w + sub * E + 4 * v);
+          *reinterpret_cast<float4*>(w2 + 4 * v) = *reinterpret_cast<const float4*>(w + HALF + sub * E + 4 * v);
+          *reinterpret_cast<float4*>(cs + 4 * v) = *reinterpret_cast<const float4*>(c_s + sub * E + 4 * v);
+          *reinterpret_cast<float4*>(sj + 4 * v) = *reinterpret_cast<const float4*>(sn_s + sub * E + 4 * v);
+        }
         uint32_t pa[E / 2], pb[E / 2];
 #pragma unroll
         for (int e = 0; e < E; e += 2) {
@@ -275,12 +284,11 @@ qkv_post_stream_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, b
             p[j] = x1[e + j];
             r[j] = x2[e + j];
             if (normed) {
-              p[j] = p[j] * rrms * w[sub * E + e + j];
-              r[j] = r[j] * rrms * w[HALF + sub * E + e + j];
+              p[j] = p[j] * rrms * w1[e + j];
+              r[j] = r[j] * rrms * w2[e + j];
             }
             if (cos_table) {
-              const float cs = c_s[sub * E + e + j], sj = sn_s[sub * E + e + j];
-              const float ra = p[j] * cs - r[j] * sj, rb = r[j] * cs + p[j] * sj;
+              const float ra = p[j] * cs[e + j] - r[j] * sj[e + j], rb = r[j] * cs[e + j] + p[j] * sj[e + j];
               p[j] = ra;
               r[j] = rb;
             }
@@ -416,6 +424,9 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
     const size_t smem = (size_t)stages * stream_stage;
     const int per_sm = smem <= 54 * 1024 ? 4 : 2;
     const int blocks = tokens < 148 * per_sm ? tokens : 148 * per_sm;
+    // as many threads as share a token's (head, lane of the head) pairs evenly in whole warps
+    const int items = heads * (d / 16), passes = (items + 255) / 256;
+    const int threads = ((items + passes - 1) / passes + 31) / 32 * 32;
 #define LAUNCH_QKV_POST_STREAM(D)                                                                                 \
     do {                                                                                                           \
       static bool configured = false;                                                                              \
@@ -423,7 +434,7 @@ VOSTI_API int vosti_qkv_post(const void* qkv, const float* partial, int splits, 
         cudaFuncSetAttribute(qkv_post_stream_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);   \
         configured = true;                                                                                         \
       }                                                                                                            \
-      vosti_launch(qkv_post_stream_kernel<D>, dim3(blocks), dim3(256), smem, stream, (const bf16*)qkv, (bf16*)q_out, \
+      vosti_launch(qkv_post_stream_kernel<D>, dim3(blocks), dim3(threads), smem, stream, (const bf16*)qkv, (bf16*)q_out, \
           (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, norm_w_is_f32, eps, cos_table, sin_table,            \
           max_positions, positions, slot_mapping, num_slots, page_size, nq, nkv, tokens, stages, status);          \
     } while (0)
